@@ -1,0 +1,118 @@
+/*
+ * thorfp4_b200.h -- C ABI of libthorfp4_b200.so, the sm_100a NVFP4 linear-layer engine.
+ *
+ * Drop-in for the entry points the thor-fp4 Python binding loads with ctypes
+ * (src/thor_fp4/_ext.py:36-94 of that project): same names, argument order,
+ * argument meaning and error convention (0 on success, a negative code and one
+ * line on stderr otherwise).  Every pointer is a raw device pointer owned by
+ * the caller; `stream` is a cudaStream_t passed as void*; calls only enqueue
+ * work on that stream and never synchronise.  Buffers are sized with the
+ * *_bytes helpers (rows padded to 128, scale columns to 4).
+ *
+ * Error codes: -1 CUDA runtime, -2 driver entry point / tensor-map encode,
+ * -3 bad K, -4 no kernel configuration, -5 launch failed, -6 bad M or N,
+ * -7 bad pointer / alignment / enum, -8 an earlier GEMM on this device ran
+ * into its bounded wait (see tfp4_status).
+ */
+#ifndef THORFP4_B200_H
+#define THORFP4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* in_dtype: 0 f32, 1 f16, 2 bf16.   out_dtype: 0 f16, 1 bf16, 2 f32. */
+
+/* Replaces tfp4_init (csrc/thor_fp4_core.cu:524-531).  Resolves the driver entry
+ * point and the per-device state of the current device; ws_bytes is accepted and
+ * ignored (no library workspace exists). */
+int tfp4_init(size_t ws_bytes);
+
+/* Replaces tfp4_cublaslt_version (csrc/thor_fp4_core.cu:533).  No cuBLASLt is
+ * linked; returns the build id of this library (1000000 + 100*major + minor). */
+size_t tfp4_cublaslt_version(void);
+
+/* Buffer sizing, identical to csrc/thor_fp4_core.cu:535-550. */
+int64_t tfp4_pad_rows(int64_t R);
+int64_t tfp4_packed_bytes(int64_t R, int64_t K);
+int64_t tfp4_scale_bytes(int64_t R, int64_t K);
+int64_t tfp4_mx_packed_bytes(int64_t R, int64_t K, int kind);
+int64_t tfp4_mx_scale_bytes(int64_t R, int64_t K);
+
+/* Replaces tfp4_quant (csrc/thor_fp4_core.cu:555-578): row-major (R,K) -> e2m1 codes
+ * + UE4M3 scale bytes in the 128x4 tile layout, bit-exact with the reference.  One
+ * fused kernel, no scratch.  Rows R..pad(R) of both outputs are written as zeros.
+ * x must be 16-byte aligned (32 for f32). */
+int tfp4_quant(const void* x, int64_t R, int64_t K, int in_dtype, float ts,
+               uint8_t* packed, uint8_t* sblk, void* stream);
+
+/* Replaces tfp4_quant_mx (csrc/thor_fp4_core.cu:581-602): kind 0 = MXFP4 (e2m1),
+ * kind 1 = MXFP8 (e4m3); UE8M0 scale per 32. */
+int tfp4_quant_mx(const void* x, int64_t R, int64_t K, int in_dtype, int kind,
+                  uint8_t* packed, uint8_t* sblk, void* stream);
+
+/* Replaces tfp4_mx8_mul (csrc/thor_fp4_core.cu:657-675): h = a*b on MXFP8 tensors,
+ * ceil-power-of-two scales; K % 128 == 0. */
+int tfp4_mx8_mul(const void* ap, const void* as, const void* bp, const void* bs,
+                 void* op, void* os, int64_t R, int64_t K, void* stream);
+
+/* Replaces tfp4_gemm (csrc/thor_fp4_core.cu:697-757): out (M,N) row-major =
+ * (tsA*tsB) * A(M,K) @ B(N,K)^T on NVFP4 buffers, FP32 accumulation in tensor
+ * memory, computed as (B @ A^T) with no transpose.  M >= 1, N >= 8, N % 8 == 0,
+ * K % 64 == 0.  Code buffers 32-byte, scale buffers 16-byte aligned. */
+int tfp4_gemm(const void* packedA, const void* sblkA, float tsA,
+              const void* packedB, const void* sblkB, float tsB,
+              void* out, int64_t M, int64_t N, int64_t K, int out_dtype, void* stream);
+
+/* Addition over the reference ABI: the same GEMM with the bias add and the cast
+ * fused into the epilogue, out = cast(alpha*acc + bias[n]) with one rounding
+ * (the reference adds the bias afterwards in the output dtype,
+ * src/thor_fp4/linear.py:264-265).  bias: N floats or NULL. */
+int tfp4_gemm_bias(const void* packedA, const void* sblkA, float tsA,
+                   const void* packedB, const void* sblkB, float tsB,
+                   const float* bias, void* out, int64_t M, int64_t N, int64_t K,
+                   int out_dtype, void* stream);
+
+/* Replaces tfp4_gemv (csrc/thor_fp4_core.cu:796-840): exact activations (M <= 8)
+ * against NVFP4 weights, FP32 accumulation; sgemvB from tfp4_scales_gemv. */
+int tfp4_gemv(const void* x, int64_t M, int64_t K, int in_dtype,
+              const uint8_t* packedB, const uint8_t* sgemvB, float tsB,
+              void* out, int64_t N, int out_dtype, void* stream);
+
+/* Replaces tfp4_scales_gemv (csrc/thor_fp4_core.cu:782-790). */
+int tfp4_scales_gemv(const uint8_t* sblk, int64_t R, int64_t K, uint8_t* out, void* stream);
+
+/* Replaces tfp4_dequant_f32 (csrc/thor_fp4_core.cu:761-768). */
+int tfp4_dequant_f32(const uint8_t* packed, const uint8_t* sblk, float ts,
+                     int64_t R, int64_t K, float* out, void* stream);
+
+/* Replaces tfp4_scales_f32 (csrc/thor_fp4_core.cu:771-778). */
+int tfp4_scales_f32(const uint8_t* sblk, int64_t R, int64_t K, float* out, void* stream);
+
+/* Replaces the optional second library's registry (csrc/cutlass_kernels.cu:229-263):
+ * the same variant names resolve to the one tcgen05 kernel of this library (the
+ * tile numbers in a name only pick the token-tile width).  tfc4_gemm: D (M,N) bf16 =
+ * alpha * A @ B^T; "nvfp4_*" variants take NVFP4 operands, "mxfp8xfp4_*" variants
+ * MXFP8 activations (A) and MXFP4 weights (B), K % 128 == 0. */
+int tfc4_n_variants(void);
+const char* tfc4_variant_name(int i);
+int tfc4_variant_index(const char* name);
+int tfc4_gemm(int variant, const void* A, const void* SA, const void* B, const void* SB,
+              void* D, int64_t M, int64_t N, int64_t K, float alpha, void* stream);
+
+/* Additions: status word of the current device (0 = healthy; otherwise the role
+ * whose bounded wait expired: 1 producer, 2 accumulator hand-back, 3 operands,
+ * 4 epilogue), its reset, plan-cache counters, and a test hook that pins the
+ * token-tile width (0 = automatic; 32, 64, 128 or 256). */
+int tfp4_status(void);
+void tfp4_clear_status(void);
+void tfp4_plan_stats(uint64_t* hits, uint64_t* misses);
+void tfp4_set_token_tile(int bn);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

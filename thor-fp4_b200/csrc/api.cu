@@ -1,0 +1,112 @@
+// api.cu -- the extern "C" surface of libthorfp4_b200.so (see include/thorfp4_b200.h).
+#include <cstring>
+
+#include "common.cuh"
+#include "../../include/thorfp4_b200.h"
+
+namespace tfp4 {
+int quant_nvfp4(const void*, int64_t, int64_t, int, float, uint8_t*, uint8_t*, cudaStream_t);
+int quant_mx(const void*, int64_t, int64_t, int, int, uint8_t*, uint8_t*, cudaStream_t);
+int mx8_mul(const void*, const void*, const void*, const void*, void*, void*, int64_t, int64_t, cudaStream_t);
+int dequant_f32(const uint8_t*, const uint8_t*, float, int64_t, int64_t, float*, cudaStream_t);
+int scales_f32(const uint8_t*, int64_t, int64_t, float*, cudaStream_t);
+int scales_gemv(const uint8_t*, int64_t, int64_t, uint8_t*, cudaStream_t);
+int gemv(const void*, int64_t, int64_t, int, const uint8_t*, const uint8_t*, float, void*, int64_t, int, cudaStream_t);
+int gemm_block_scaled(int, const void*, const void*, const void*, const void*, float, const float*, void*,
+                      int64_t, int64_t, int64_t, int, cudaStream_t);
+void gemm_set_token_tile(int);
+int gemm_status_word();
+void gemm_clear_status();
+void gemm_plan_stats(uint64_t*, uint64_t*);
+int gemm_warm();
+}  // namespace tfp4
+
+namespace {
+struct Variant { const char* name; int kind; };
+// names of csrc/cutlass_kernels.cu:191-219 in the reference project (its MXFP4 x MXFP4
+// entries compute garbage there and are not offered)
+const Variant kVariants[] = {
+    {"nvfp4_128x128x256_c1", 0},      {"nvfp4_128x128x256_c1_a32", 0},  {"nvfp4_128x128x256_c2x1", 0},
+    {"nvfp4_128x256x256_c2x1", 0},    {"nvfp4_128x128x128_c1", 0},      {"nvfp4_128x128x64_c1", 0},
+    {"mxfp8xfp4_128x128x256_c1", 1},  {"mxfp8xfp4_128x128x256_c2x1", 1}, {"mxfp8xfp4_128x256x256_c2x1", 1},
+    {"mxfp8xfp4_128x128x128_c1", 1},  {"mxfp8xfp4_128x128x128_c2x1", 1}, {"mxfp8xfp4_128x256x128_c2x1", 1},
+    {"mxfp8xfp4_256x128x256_c2x1", 1},
+};
+constexpr int kNVariants = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
+inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+}  // namespace
+
+extern "C" {
+
+int tfp4_init(size_t) { return tfp4::gemm_warm(); }
+size_t tfp4_cublaslt_version(void) { return 1000000u + 100u * 0u + 1u; }
+
+int64_t tfp4_pad_rows(int64_t R) { return tfp4::pad128(R); }
+int64_t tfp4_packed_bytes(int64_t R, int64_t K) { return tfp4::pad128(R) * K / 2; }
+int64_t tfp4_scale_bytes(int64_t R, int64_t K) { return tfp4::pad128(R) * ((K / 16 + 3) / 4 * 4); }
+int64_t tfp4_mx_packed_bytes(int64_t R, int64_t K, int kind) { return tfp4::pad128(R) * (kind == 0 ? K / 2 : K); }
+int64_t tfp4_mx_scale_bytes(int64_t R, int64_t K) { return tfp4::pad128(R) * ((K / 32 + 3) / 4 * 4); }
+
+int tfp4_quant(const void* x, int64_t R, int64_t K, int in_dtype, float ts, uint8_t* packed, uint8_t* sblk,
+               void* stream) {
+    return tfp4::quant_nvfp4(x, R, K, in_dtype, ts, packed, sblk, S(stream));
+}
+int tfp4_quant_mx(const void* x, int64_t R, int64_t K, int in_dtype, int kind, uint8_t* packed, uint8_t* sblk,
+                  void* stream) {
+    return tfp4::quant_mx(x, R, K, in_dtype, kind, packed, sblk, S(stream));
+}
+int tfp4_mx8_mul(const void* ap, const void* as, const void* bp, const void* bs, void* op, void* os, int64_t R,
+                 int64_t K, void* stream) {
+    return tfp4::mx8_mul(ap, as, bp, bs, op, os, R, K, S(stream));
+}
+int tfp4_gemm(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB, void* out,
+              int64_t M, int64_t N, int64_t K, int out_dtype, void* stream) {
+    if ((K % 64) != 0) {
+        fprintf(stderr, "thor_fp4: K must be a multiple of 64 (got %ld)\n", (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    return tfp4::gemm_block_scaled(0, pA, sA, pB, sB, tsA * tsB, nullptr, out, M, N, K, out_dtype, S(stream));
+}
+int tfp4_gemm_bias(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB,
+                   const float* bias, void* out, int64_t M, int64_t N, int64_t K, int out_dtype, void* stream) {
+    return tfp4::gemm_block_scaled(0, pA, sA, pB, sB, tsA * tsB, bias, out, M, N, K, out_dtype, S(stream));
+}
+int tfp4_gemv(const void* x, int64_t M, int64_t K, int in_dtype, const uint8_t* pB, const uint8_t* sg, float tsB,
+              void* out, int64_t N, int out_dtype, void* stream) {
+    return tfp4::gemv(x, M, K, in_dtype, pB, sg, tsB, out, N, out_dtype, S(stream));
+}
+int tfp4_scales_gemv(const uint8_t* sblk, int64_t R, int64_t K, uint8_t* out, void* stream) {
+    return tfp4::scales_gemv(sblk, R, K, out, S(stream));
+}
+int tfp4_dequant_f32(const uint8_t* packed, const uint8_t* sblk, float ts, int64_t R, int64_t K, float* out,
+                     void* stream) {
+    return tfp4::dequant_f32(packed, sblk, ts, R, K, out, S(stream));
+}
+int tfp4_scales_f32(const uint8_t* sblk, int64_t R, int64_t K, float* out, void* stream) {
+    return tfp4::scales_f32(sblk, R, K, out, S(stream));
+}
+
+int tfc4_n_variants(void) { return kNVariants; }
+const char* tfc4_variant_name(int i) { return (i >= 0 && i < kNVariants) ? kVariants[i].name : nullptr; }
+int tfc4_variant_index(const char* name) {
+    if (!name) return -1;
+    for (int i = 0; i < kNVariants; ++i)
+        if (strcmp(name, kVariants[i].name) == 0) return i;
+    return -1;
+}
+int tfc4_gemm(int variant, const void* A, const void* SA, const void* B, const void* SB, void* D, int64_t M,
+              int64_t N, int64_t K, float alpha, void* stream) {
+    if (variant < 0 || variant >= kNVariants) {
+        fprintf(stderr, "thor_fp4: bad variant %d (0..%d)\n", variant, kNVariants - 1);
+        return TFP4_ERR_CUDA;
+    }
+    return tfp4::gemm_block_scaled(kVariants[variant].kind, A, SA, B, SB, alpha, nullptr, D, M, N, K,
+                                   tfp4::OUT_BF16, S(stream));
+}
+
+int tfp4_status(void) { return tfp4::gemm_status_word(); }
+void tfp4_clear_status(void) { tfp4::gemm_clear_status(); }
+void tfp4_plan_stats(uint64_t* hits, uint64_t* misses) { tfp4::gemm_plan_stats(hits, misses); }
+void tfp4_set_token_tile(int bn) { tfp4::gemm_set_token_tile(bn); }
+
+}  // extern "C"

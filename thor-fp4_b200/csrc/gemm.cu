@@ -1,0 +1,608 @@
+// gemm.cu -- hand-written tcgen05 block-scaled GEMM for sm_100a.
+//
+//   out[m, n] = cast( alpha * sum_k deq(act)[m, k] * deq(W)[n, k] + bias[n] )
+//
+// computed as (W @ act^T): the 128-row MMA "M" side is a tile of WEIGHT rows
+// (output features) and the MMA "N" side is a tile of BN tokens, so any batch
+// M >= 1 only pads the narrow side and the accumulator lane index is the output
+// column n.  This replaces the reference's cuBLASLt call
+// (csrc/thor_fp4_core.cu:697-757) and its CUTLASS variants
+// (csrc/cutlass_kernels.cu:191-224).
+//
+// Pipeline per CTA (persistent over output tiles, 192 threads):
+//   warp 0      producer: per 128-byte K block one TMA tile of W codes, one of
+//               act codes (128B-swizzled) and the matching 512-byte scale atoms
+//               (plain bulk copies - atoms of one K block are contiguous),
+//               all completing on the stage's "full" mbarrier;
+//   warp 1      MMA issuer: tcgen05.cp moves the scale atoms shared -> tensor
+//               memory, then 4 tcgen05.mma.block_scale per stage accumulate in
+//               tensor memory; tcgen05.commit releases the stage / publishes the
+//               accumulator;
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns, alpha / bias / cast,
+//               row-major stores; with BN <= 128 two accumulators alternate so the
+//               epilogue of tile i overlaps the main loop of tile i+1.
+//
+// KIND 0: NVFP4 x NVFP4   (kind::mxf4nvf4, UE4M3 scale per 16, 256 elements per K block)
+// KIND 1: MXFP8 act x MXFP4 weight (kind::mxf8f6f4, UE8M0 scale per 32, 128 elements per
+//         K block; the 4-bit weights are expanded by TMA to one byte per element)
+//
+// Every wait is bounded: on expiry the CTA raises an abort flag, records a
+// status word the host reads, drains and frees its tensor memory.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace tfp4 {
+
+namespace {
+
+constexpr int BM = 128;             // weight rows per tile (MMA M)
+constexpr int KB_BYTES = 128;       // bytes of K per stage and row (one swizzle span)
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_SFW_COL = 256;   // 16 columns: weight-side scales of one stage
+constexpr int TMEM_SFA_COL = 272;   // up to 32 columns: token-side scales of one stage
+constexpr long long WAIT_CYCLES = 2000000000ll;   // ~1 s at 2 GHz
+
+struct GemmParams {
+    const uint8_t* sfW;      // weight scales (tile layout)
+    const uint8_t* sfA;      // activation scales (tile layout)
+    void* out;
+    const float* bias;       // may be null
+    float alpha;
+    int64_t M, N, K;
+    int64_t m_tiles, n_tiles;
+    int64_t sf_tile_stride;  // bytes between consecutive 128-row scale tiles = (S/4)*512
+    int32_t rows_w_tiles;    // number of 128-row scale tiles of W
+    int32_t rows_a_tiles;    // number of 128-row scale tiles of act
+    int32_t out_dtype;
+    int32_t k_blocks;
+    int32_t last_atoms;      // NVFP4: 64-element MMAs in the last K block (1..4); MX: 32-element ones
+    int32_t stages;
+    int* status;             // host-visible status word (0 = ok)
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait: false if the abort flag is up or the time limit passed
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_CYCLES) {
+                *abort_flag = code;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    if (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// shared-memory matrix descriptor, K-major operand tile whose rows are one
+// 128-byte swizzle span: 8-row groups 1024 bytes apart, SWIZZLE_128B, version 1
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// descriptor of one 512-byte scale atom: 32 rows of 16 bytes, no swizzle,
+// 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3fffu) | (8ull << 32) | (1ull << 46);
+}
+
+template <int KIND, int BN>
+struct Cfg {
+    static constexpr int ACC_STAGES = (BN <= 128) ? 2 : 1;
+    static constexpr int SF_TILES = (BN + 127) / 128;                 // 128-row scale tiles on the token side
+    static constexpr int ATOMS = (KIND == 0) ? 4 : 1;                 // scale atoms per 128 rows per stage
+    static constexpr int W_BYTES = BM * KB_BYTES;                     // 16 KB
+    static constexpr int A_BYTES = BN * KB_BYTES;
+    static constexpr int SFW_BYTES = ATOMS * 512;
+    static constexpr int SFA_BYTES = SF_TILES * ATOMS * 512;
+    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + SFW_BYTES + SFA_BYTES;   // multiple of 1024? see static_assert
+    static_assert((W_BYTES % 1024) == 0 && (A_BYTES % 1024) == 0, "operand tiles must keep 1024-byte alignment");
+    // instruction descriptor (block-scaled form): formats, N>>3 at bit 17, scale format at 23, M>>4 at 24
+    static constexpr uint32_t IDESC =
+        (KIND == 0 ? ((1u << 7) | (1u << 10)) : ((5u << 7) | (0u << 10))) |
+        ((uint32_t)(BN >> 3) << 17) | ((KIND == 0 ? 0u : 1u) << 23) | ((uint32_t)(BM >> 4) << 24);
+};
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+               const GemmParams p) {
+    using C = Cfg<KIND, BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte aligned carve-up: [stages x (W | act | sfW | sfA)] [barriers]
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int stages = p.stages;
+    uint8_t* sW = smem;
+    uint8_t* sA = sW + (size_t)stages * C::W_BYTES;
+    uint8_t* sSFW = sA + (size_t)stages * C::A_BYTES;
+    uint8_t* sSFA = sSFW + (size_t)stages * C::SFW_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSFA + (size_t)stages * C::SFA_BYTES);
+    uint64_t* full_bar = bars;                       // [stages]
+    uint64_t* empty_bar = bars + stages;             // [stages]
+    uint64_t* tfull_bar = bars + 2 * stages;         // [ACC_STAGES]
+    uint64_t* tempty_bar = tfull_bar + C::ACC_STAGES;  // [ACC_STAGES]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::ACC_STAGES);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < C::ACC_STAGES; ++a) {
+            mbar_init(smem_u32(&tfull_bar[a]), 1);
+            mbar_init(smem_u32(&tempty_bar[a]), 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t total_tiles = p.m_tiles * p.n_tiles;
+    const int k_blocks = p.k_blocks;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+                const int n0 = (int)(nt * BM), m0 = (int)(mt * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = (int)(it % (uint32_t)stages);
+                    const uint32_t ph = (it / (uint32_t)stages) & 1u;
+                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+                    const int atoms = (kb == k_blocks - 1) ? ((KIND == 0) ? p.last_atoms : 1) : C::ATOMS;
+                    const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+                    int a_tiles = 0;
+#pragma unroll
+                    for (int t = 0; t < C::SF_TILES; ++t)
+                        if (mt * C::SF_TILES + t < p.rows_a_tiles) ++a_tiles;
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(bar, (uint32_t)(C::W_BYTES + C::A_BYTES) + sf_bytes * (uint32_t)(1 + a_tiles));
+                    tma_load_2d(smem_u32(sW + (size_t)s * C::W_BYTES), &tmW, kb * (KIND == 0 ? KB_BYTES : KB_BYTES), n0, bar);
+                    tma_load_2d(smem_u32(sA + (size_t)s * C::A_BYTES), &tmA, kb * KB_BYTES, m0, bar);
+                    const int64_t sf_k_off = (int64_t)kb * C::ATOMS * 512;
+                    bulk_load(smem_u32(sSFW + (size_t)s * C::SFW_BYTES),
+                              p.sfW + nt * p.sf_tile_stride + sf_k_off, sf_bytes, bar);
+#pragma unroll
+                    for (int t = 0; t < C::SF_TILES; ++t) {
+                        if (mt * C::SF_TILES + t < p.rows_a_tiles)
+                            bulk_load(smem_u32(sSFA + (size_t)s * C::SFA_BYTES + (size_t)t * C::ATOMS * 512),
+                                      p.sfA + (mt * C::SF_TILES + t) * p.sf_tile_stride + sf_k_off, sf_bytes, bar);
+                    }
+                }
+            }
+            if (!ok) {
+                // let copies already issued land before the CTA's shared memory goes away
+                for (int s = 0; s < stages; ++s) {
+                    const long long t0 = clock64();
+                    while (clock64() - t0 < 2000000ll) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+                const int acc = (int)(tcount % C::ACC_STAGES);
+                const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_flag, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = (int)(it % (uint32_t)stages);
+                    const uint32_t ph = (it / (uint32_t)stages) & 1u;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const int n_mma = (kb == k_blocks - 1) ? p.last_atoms : 4;
+                    const int atoms = (KIND == 0) ? n_mma : 1;
+                    const uint32_t sfw_s = smem_u32(sSFW + (size_t)s * C::SFW_BYTES);
+                    const uint32_t sfa_s = smem_u32(sSFA + (size_t)s * C::SFA_BYTES);
+                    for (int j = 0; j < atoms; ++j) {
+                        tc_cp_sf(tmem_base + TMEM_SFW_COL + 4 * j, desc_sf_atom(sfw_s + 512 * j));
+#pragma unroll
+                        for (int t = 0; t < C::SF_TILES; ++t)
+                            tc_cp_sf(tmem_base + TMEM_SFA_COL + 4 * (j * C::SF_TILES + t),
+                                     desc_sf_atom(sfa_s + (t * C::ATOMS + j) * 512));
+                    }
+                    const uint32_t w_s = smem_u32(sW + (size_t)s * C::W_BYTES);
+                    const uint32_t a_s = smem_u32(sA + (size_t)s * C::A_BYTES);
+                    for (int j = 0; j < n_mma; ++j) {
+                        const uint64_t adesc = desc_sw128(w_s + 32 * j);
+                        const uint64_t bdesc = desc_sw128(a_s + 32 * j);
+                        uint32_t idesc = C::IDESC, sfw_t, sfa_t;
+                        if (KIND == 0) {
+                            sfw_t = tmem_base + TMEM_SFW_COL + 4 * j;
+                            sfa_t = tmem_base + TMEM_SFA_COL + 4 * j * C::SF_TILES;
+                        } else {
+                            // one scale byte per row per MMA: byte j of the 4-byte column
+                            idesc |= ((uint32_t)j << 29) | ((uint32_t)j << 4);
+                            sfw_t = (tmem_base + TMEM_SFW_COL) | ((uint32_t)j << 30);
+                            sfa_t = (tmem_base + TMEM_SFA_COL) | ((uint32_t)j << 30);
+                        }
+                        tc_mma<KIND>(d_tmem, adesc, bdesc, idesc, sfw_t, sfa_t, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&empty_bar[s]));
+                }
+                if (ok) tc_commit(smem_u32(&tfull_bar[acc]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int ew = warp & 3;                       // tensor-memory lane quarter this warp may read
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+            const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+            const int acc = (int)(tcount % C::ACC_STAGES);
+            const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
+            if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
+            tc_fence_after();
+            const int64_t n = nt * BM + ew * 32 + lane;
+            const int64_t m0 = mt * BN;
+            const bool n_ok = n < p.N;
+            const float bias_n = (p.bias != nullptr && n_ok) ? p.bias[n] : 0.f;
+            const float alpha = p.alpha;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN + c0);
+                tc_ld32(taddr, v);
+                tc_wait_ld();
+                if (m0 + c0 < p.M && n_ok) {
+                    if (p.out_dtype == OUT_BF16) {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (m0 + c0) * p.N + n;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (m0 + c0 + i < p.M) o[(int64_t)i * p.N] = __float2bfloat16_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
+                    } else if (p.out_dtype == OUT_F16) {
+                        __half* o = reinterpret_cast<__half*>(p.out) + (m0 + c0) * p.N + n;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (m0 + c0 + i < p.M) o[(int64_t)i * p.N] = __float2half_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
+                    } else {
+                        float* o = reinterpret_cast<float*>(p.out) + (m0 + c0) * p.N + n;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (m0 + c0 + i < p.M) o[(int64_t)i * p.N] = fmaf(alpha, __uint_as_float(v[i]), bias_n);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_flag);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+    int sm_count = 0;
+    int max_smem = 0;
+    int* status_host = nullptr;   // pinned, mapped
+    int* status_dev = nullptr;
+    bool attr_set[2][4] = {{false, false, false, false}, {false, false, false, false}};
+};
+
+std::mutex g_mu;
+EncodeTiledFn g_encode = nullptr;
+std::map<int, DeviceState> g_dev;
+uint64_t g_plan_hits = 0, g_plan_misses = 0;
+
+struct PlanKey {
+    const void* pA; const void* pB; int64_t M, N, K; int kind; int bn; int dev;
+    bool operator<(const PlanKey& o) const {
+        return std::tie(pA, pB, M, N, K, kind, bn, dev) < std::tie(o.pA, o.pB, o.M, o.N, o.K, o.kind, o.bn, o.dev);
+    }
+};
+struct Plan {
+    CUtensorMap tmW, tmA;
+};
+std::map<PlanKey, Plan> g_plans;
+
+int ensure_driver() {
+    if (g_encode) return TFP4_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+        fprintf(stderr, "thor_fp4_b200: cuTensorMapEncodeTiled not available (%s)\n", cudaGetErrorString(e));
+        return TFP4_ERR_DRIVER;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return TFP4_OK;
+}
+
+int ensure_device(DeviceState** out) {
+    int dev = 0;
+    TFP4_CK(cudaGetDevice(&dev));
+    auto it = g_dev.find(dev);
+    if (it == g_dev.end()) {
+        DeviceState st;
+        TFP4_CK(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        TFP4_CK(cudaDeviceGetAttribute(&st.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), sizeof(int), cudaHostAllocMapped));
+        *st.status_host = 0;
+        TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0));
+        it = g_dev.emplace(dev, st).first;
+    }
+    *out = &it->second;
+    return TFP4_OK;
+}
+
+// rows x row_bytes byte matrix, box = 128 bytes x box_rows, 128-byte swizzle
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner_elems,
+               uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows) {
+    cuuint64_t dims[2] = {inner_elems, rows};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        fprintf(stderr, "thor_fp4_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r);
+        return TFP4_ERR_DRIVER;
+    }
+    return TFP4_OK;
+}
+
+template <int KIND, int BN>
+int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaStream_t stream) {
+    using C = Cfg<KIND, BN>;
+    const int bar_bytes = 256;
+    int stages = (st->max_smem - 1024 - bar_bytes) / C::STAGE_BYTES;
+    if (stages > 8) stages = 8;
+    if (stages > p.k_blocks * 2 && p.k_blocks * 2 >= 2) stages = p.k_blocks * 2;
+    if (stages < 2) return TFP4_ERR_NO_PLAN;
+    p.stages = stages;
+    // keep one CTA per SM: each CTA allocates all 512 tensor-memory columns
+    size_t smem = (size_t)stages * C::STAGE_BYTES + bar_bytes + 1024;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+    if (!st->attr_set[KIND][bn_slot]) {
+        TFP4_CK(cudaFuncSetAttribute(gemm_bs_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     st->max_smem));
+        st->attr_set[KIND][bn_slot] = true;
+    }
+    const int64_t tiles = p.m_tiles * p.n_tiles;
+    const unsigned grid = (unsigned)(tiles < st->sm_count ? tiles : st->sm_count);
+    gemm_bs_kernel<KIND, BN><<<grid, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "thor_fp4_b200: GEMM launch failed: %s\n", cudaGetErrorString(e));
+        return TFP4_ERR_LAUNCH;
+    }
+    return TFP4_OK;
+}
+
+int g_force_bn = 0;
+
+}  // namespace
+
+// kind 0: NVFP4 x NVFP4 ; kind 1: MXFP8 activations x MXFP4 weights
+int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const void* packedB,
+                      const void* sblkB, float alpha, const float* bias, void* out, int64_t M, int64_t N,
+                      int64_t K, int out_dtype, cudaStream_t stream) {
+    if (M < 1 || N < 8 || (N % 8) != 0) {
+        fprintf(stderr, "thor_fp4: gemm needs M >= 1, N >= 8, N %% 8 == 0 (got M=%ld N=%ld)\n", (long)M, (long)N);
+        return TFP4_ERR_BAD_M;
+    }
+    const int64_t kq = kind == 0 ? 64 : 128;
+    if (K <= 0 || (K % kq) != 0) {
+        fprintf(stderr, "thor_fp4: gemm needs K %% %ld == 0 (got %ld)\n", (long)kq, (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    if (!packedA || !sblkA || !packedB || !sblkB || !out || out_dtype < 0 || out_dtype > 2 ||
+        (reinterpret_cast<uintptr_t>(packedA) & 31) || (reinterpret_cast<uintptr_t>(packedB) & 31) ||
+        (reinterpret_cast<uintptr_t>(sblkA) & 15) || (reinterpret_cast<uintptr_t>(sblkB) & 15)) {
+        fprintf(stderr, "thor_fp4: gemm bad argument (code buffers 32-byte, scale buffers 16-byte aligned)\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = ensure_driver();
+    if (rc) return rc;
+    DeviceState* st = nullptr;
+    rc = ensure_device(&st);
+    if (rc) return rc;
+    if (*st->status_host != 0) {
+        fprintf(stderr, "thor_fp4_b200: an earlier GEMM gave up waiting on the device (code %d)\n", *st->status_host);
+        return TFP4_ERR_DEVICE_TIMEOUT;
+    }
+    int bn = g_force_bn;
+    if (bn == 0) bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    PlanKey key{packedA, packedB, M, N, K, kind, bn, dev};
+    auto it = g_plans.find(key);
+    if (it == g_plans.end()) {
+        ++g_plan_misses;
+        Plan pl;
+        const uint64_t rowsW = (uint64_t)pad128(N), rowsA = (uint64_t)pad128(M);
+        if (kind == 0) {
+            rc = encode_map(&pl.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedB, (uint64_t)K / 2, rowsW, (uint64_t)K / 2, 128, BM);
+            if (rc) return rc;
+            rc = encode_map(&pl.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedA, (uint64_t)K / 2, rowsA, (uint64_t)K / 2, 128, (uint32_t)bn);
+            if (rc) return rc;
+        } else {
+            // 4-bit weights, expanded by TMA to 16 codes per 16 bytes of shared memory
+            rc = encode_map(&pl.tmW, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, packedB, (uint64_t)K, rowsW, (uint64_t)K / 2, 128, BM);
+            if (rc) return rc;
+            rc = encode_map(&pl.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedA, (uint64_t)K, rowsA, (uint64_t)K, 128, (uint32_t)bn);
+            if (rc) return rc;
+        }
+        if (g_plans.size() > 4096) g_plans.clear();
+        it = g_plans.emplace(key, pl).first;
+    } else {
+        ++g_plan_hits;
+    }
+    GemmParams p;
+    p.sfW = static_cast<const uint8_t*>(sblkB);
+    p.sfA = static_cast<const uint8_t*>(sblkA);
+    p.out = out;
+    p.bias = bias;
+    p.alpha = alpha;
+    p.M = M; p.N = N; p.K = K;
+    p.m_tiles = (M + bn - 1) / bn;
+    p.n_tiles = (N + BM - 1) / BM;
+    const int64_t S = kind == 0 ? K / 16 : K / 32;
+    p.sf_tile_stride = (S / 4) * 512;
+    p.rows_w_tiles = (int32_t)(pad128(N) / 128);
+    p.rows_a_tiles = (int32_t)(pad128(M) / 128);
+    p.out_dtype = out_dtype;
+    const int64_t kb_elems = kind == 0 ? 256 : 128;
+    p.k_blocks = (int32_t)((K + kb_elems - 1) / kb_elems);
+    const int64_t rem = K - (int64_t)(p.k_blocks - 1) * kb_elems;
+    p.last_atoms = (int32_t)(kind == 0 ? rem / 64 : rem / 32);
+    p.stages = 0;
+    p.status = st->status_dev;
+    const Plan& pl = it->second;
+#define TFP4_GO(KINDV)                                                          \
+    switch (bn) {                                                               \
+        case 32: return launch<KINDV, 32>(st, pl, p, 0, stream);                \
+        case 64: return launch<KINDV, 64>(st, pl, p, 1, stream);                \
+        case 128: return launch<KINDV, 128>(st, pl, p, 2, stream);              \
+        default: return launch<KINDV, 256>(st, pl, p, 3, stream);               \
+    }
+    if (kind == 0) { TFP4_GO(0) } else { TFP4_GO(1) }
+#undef TFP4_GO
+}
+
+int gemm_warm() {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = ensure_driver();
+    if (rc) return rc;
+    DeviceState* st = nullptr;
+    return ensure_device(&st);
+}
+
+void gemm_set_token_tile(int bn) { g_force_bn = (bn == 32 || bn == 64 || bn == 128 || bn == 256) ? bn : 0; }
+
+int gemm_status_word() {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState* st = nullptr;
+    if (ensure_device(&st)) return -1;
+    return *st->status_host;
+}
+
+void gemm_clear_status() {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState* st = nullptr;
+    if (ensure_device(&st) == 0) *st->status_host = 0;
+}
+
+void gemm_plan_stats(uint64_t* hits, uint64_t* misses) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    *hits = g_plan_hits;
+    *misses = g_plan_misses;
+}
+
+}  // namespace tfp4

@@ -1,0 +1,437 @@
+// quant.cu -- fused activation / weight quantizers for sm_100a.
+//
+// One kernel per call (the reference runs two and round-trips the scales through
+// an f32 scratch array, csrc/thor_fp4_core.cu:127-217,555-578): each CTA owns a
+// 128-row x 256-column tile, i.e. whole 512-byte scale atoms, reads its input
+// with 128-bit loads, reduces the per-block amax with warp shuffles, writes the
+// e2m1 codes straight to their row-major place and stages the scale bytes in
+// shared memory so that every atom leaves as one contiguous 512-byte store.
+// Rows past R inside the last 128-row tile are written as zeros.
+//
+// Bit-exactness with the reference arithmetic
+//   sc = ue4m3(amax * (1/6) / ts), ds = dec(sc) * ts, code = e2m1_ties_up(x / ds)
+// is kept without an IEEE division per element:
+//
+//   EXACT16 path (16-bit input, ts == 1).  ds is an e4m3 value (<= 4 significant
+//   bits) and the rounding thresholds t are {.25,.75,1.25,1.75,2.5,3.5,5}
+//   (<= 3 bits), so t*ds is exactly representable in bf16, f16 and f32.  For an
+//   f32 quotient q = RN(x/ds):  q >= t  <=>  x >= t*ds, because no f32 lies in
+//   [t*ds*(1-2^-25), t*ds).  With x and t*ds both numbers of the 16-bit input
+//   format, x < t*ds implies x <= t*ds*(1-2^-11).  Hence y = x * rb with
+//   rb = RN(1/ds)*(1+2^-21) satisfies y > t when x >= t*ds and y < t otherwise
+//   (the bias 2^-21 dominates the three roundings, 3*2^-24, and is far below the
+//   2^-11 gap), so the hardware round-to-nearest-EVEN conversion of y returns the
+//   reference's ties-UP code: y never sits on a midpoint.  y = fma(x, rb, +0)
+//   turns -0 into +0 (the reference's sign is (q < 0)); 0*inf = NaN and +-inf map
+//   to magnitude 6 exactly as the reference's x/0 does; NaN -> +6.
+//
+//   BRACKET path (f32 input, or ts != 1).  y_lo = x*r*(1-2^-20) and
+//   y_hi = x*r*(1+2^-20) strictly bracket RN(x/ds).  If both convert to the same
+//   code no rounding midpoint lies between them and that code is the reference's;
+//   otherwise (probability ~1e-5 per element) the lane recomputes its 8 codes with
+//   the literal IEEE division and compare chain.  Lanes holding a non-zero
+//   |x| < 2^-100 (the quotient may underflow to -0, whose sign the reference
+//   drops) and calls with an out-of-range ts also take the literal route.
+#include "common.cuh"
+
+namespace tfp4 {
+
+namespace {
+
+constexpr int QT_ROWS = 128;   // rows per CTA tile = one scale-atom height
+constexpr int QT_COLS = 256;   // columns per CTA tile = 8 elements x 32 lanes
+constexpr int QT_THREADS = 256;
+constexpr int QT_UNROLL = 4;   // rows in flight per warp
+
+__device__ __forceinline__ uint32_t pack_codes_rne(const float (&y)[8]) {
+    uint32_t b0 = f32x2_to_e2m1x2_rne(y[0], y[1]);
+    uint32_t b1 = f32x2_to_e2m1x2_rne(y[2], y[3]);
+    uint32_t b2 = f32x2_to_e2m1x2_rne(y[4], y[5]);
+    uint32_t b3 = f32x2_to_e2m1x2_rne(y[6], y[7]);
+    return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+}
+
+__device__ __noinline__ uint32_t pack_codes_literal(const float (&f)[8], float ds) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w |= e2m1_ties_up(__fdiv_rn(f[i], ds)) << (4 * i);
+    return w;
+}
+
+__device__ __forceinline__ float fma_pz(float a, float b) {  // a*b + (+0): maps -0 to +0
+    float d;
+    asm("fma.rn.f32 %0, %1, %2, 0f00000000;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
+// MODE 0: EXACT16 (16-bit input, ts == 1); 1: BRACKET; 2: LITERAL (always divide)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(QT_THREADS)
+quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
+                   uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
+    __shared__ __align__(16) uint8_t s_sf[4 * 512];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS;
+    const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
+    const int64_t col = c0 + lane * 8;
+    const bool col_ok = col < K;
+    const int64_t Rpad = pad128(R);
+
+    reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
+    __syncthreads();
+
+    // warp w handles tile rows w, w+8, ..., w+120
+#pragma unroll 1
+    for (int it = 0; it < QT_ROWS / 8; it += QT_UNROLL) {
+        float f[QT_UNROLL][8];
+        bool live[QT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < QT_UNROLL; ++u) {
+            const int64_t r = r0 + warp + 8 * (it + u);
+            live[u] = col_ok && r < R;
+            if (live[u]) {
+                load8<T>(x + r * K + col, f[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[u][i] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < QT_UNROLL; ++u) {
+            const int rl = warp + 8 * (it + u);
+            const int64_t r = r0 + rl;
+            uint32_t codes = 0;
+            if (r < R) {   // warp-uniform: every lane takes part in the shuffles
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[u][i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                float pre = amax * (1.0f / 6.0f);
+                if (MODE != 0) pre = __fdiv_rn(pre, ts);
+                const uint32_t sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
+                const float sf = e4m3_to_f32(sc);
+                const float ds = (MODE != 0) ? sf * ts : sf;
+                if ((lane & 1) == 0 && col_ok) {
+                    const int sl = lane >> 1;   // scale column inside the tile, 0..15
+                    s_sf[(sl >> 2) * 512 + 16 * (rl & 31) + 4 * (rl >> 5) + (sl & 3)] = (uint8_t)sc;
+                }
+                if (MODE == 0) {
+                    const float rb = __frcp_rn(ds) * 1.000000476837158203125f;   // * (1 + 2^-21)
+                    float y[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
+                    codes = pack_codes_rne(y);
+                } else if (MODE == 1) {
+                    const float rr = __frcp_rn(ds);
+                    const float r_hi = rr * 1.00000095367431640625f;   // 1 + 2^-20
+                    const float r_lo = rr * 0.99999904632568359375f;   // 1 - 2^-20
+                    float yh[8], yl[8];
+                    bool tiny = false;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        yh[i] = fma_pz(f[u][i], r_hi);
+                        yl[i] = fma_pz(f[u][i], r_lo);
+                        // 0 < |x| < 2^-100 (bits 0x0d800000): quotient may underflow
+                        tiny |= ((__float_as_uint(f[u][i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
+                    }
+                    codes = pack_codes_rne(yh);
+                    const uint32_t cl = pack_codes_rne(yl);
+                    if (cl != codes || tiny) codes = pack_codes_literal(f[u], ds);
+                } else {
+                    codes = pack_codes_literal(f[u], ds);
+                }
+            }
+            if (col_ok && r < Rpad)
+                *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
+        }
+    }
+    __syncthreads();
+    // whole atoms out: 512 contiguous bytes each
+    const int64_t D = K >> 6;                          // atoms per row tile
+    const int64_t d0 = c0 >> 6;
+    const int n_atoms = (int)((K - c0 >= QT_COLS) ? 4 : ((K - c0) >> 6));
+    const int atom = threadIdx.x >> 6;                 // 64 threads x 8 bytes per atom
+    if (atom < n_atoms) {
+        uint2 v = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
+        uint8_t* dst = sblk + ((int64_t)blockIdx.y * D + d0 + atom) * 512 + (threadIdx.x & 63) * 8;
+        *reinterpret_cast<uint2*>(dst) = v;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// MX quantizer: UE8M0 (power-of-two) scale per 32 elements; kind 0 = e2m1 codes
+// (ties up, as the NVFP4 path), kind 1 = e4m3 codes (hardware RNE, saturating).
+// Follows csrc/thor_fp4_core.cu:224-309.  Dividing by the power-of-two scale is
+// done as an exact multiplication by its reciprocal (same correctly rounded
+// result as the reference's x / ds, including sub-normal quotients).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ue8m0_nearest(float v) {
+    // nearest power of two, midpoint ties up; !(v > 0) -> 0; csrc/thor_fp4_core.cu:105-113
+    if (!(v > 0.f)) return 0u;
+    const uint32_t u = __float_as_uint(v);
+    uint32_t b;
+    if ((u >> 23) == 0u) b = (u >= 0x00600000u) ? 1u : 0u;   // sub-normal v
+    else b = (u + 0x00400000u) >> 23;
+    return b > 254u ? 254u : b;
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(QT_THREADS)
+quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
+                uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
+    __shared__ __align__(16) uint8_t s_sf[2 * 512];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS;
+    const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
+    const int64_t col = c0 + lane * 8;
+    const bool col_ok = col < K;
+    const int64_t Rpad = pad128(R);
+    const int64_t S = K >> 5;
+    const bool whole_atoms = (S & 3) == 0;   // K % 128 == 0
+
+    if (threadIdx.x < 128) reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
+    __syncthreads();
+
+#pragma unroll 1
+    for (int it = 0; it < QT_ROWS / 8; it += QT_UNROLL) {
+        float f[QT_UNROLL][8];
+#pragma unroll
+        for (int u = 0; u < QT_UNROLL; ++u) {
+            const int64_t r = r0 + warp + 8 * (it + u);
+            if (col_ok && r < R) {
+                load8<T>(x + r * K + col, f[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[u][i] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < QT_UNROLL; ++u) {
+            const int rl = warp + 8 * (it + u);
+            const int64_t r = r0 + rl;
+            uint32_t w0 = 0, w1 = 0;
+            if (r < R) {   // warp-uniform: every lane takes part in the shuffles
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[u][i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const uint32_t scb = ue8m0_nearest(__fdiv_rn(amax, KIND == 0 ? 6.0f : 448.0f));
+                // 1/ds = 2^(127 - scb), exactly representable for scb in [0, 254]
+                const int e = 127 - (int)scb;
+                const float inv = e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23)
+                                            : __uint_as_float(0x00400000u);   // 2^-127
+                if ((lane & 3) == 0 && col_ok) {
+                    const int sl = lane >> 2;   // 0..7
+                    if (whole_atoms) {
+                        s_sf[(sl >> 2) * 512 + 16 * (rl & 31) + 4 * (rl >> 5) + (sl & 3)] = (uint8_t)scb;
+                    } else {
+                        sblk[sf_index(r, (c0 >> 5) + sl, S)] = (uint8_t)scb;
+                    }
+                }
+                if (KIND == 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) w0 |= e2m1_ties_up(f[u][i] * inv) << (4 * i);
+                } else {
+                    w0 = f32x2_to_e4m3x2(f[u][0] * inv, f[u][1] * inv) |
+                         (f32x2_to_e4m3x2(f[u][2] * inv, f[u][3] * inv) << 16);
+                    w1 = f32x2_to_e4m3x2(f[u][4] * inv, f[u][5] * inv) |
+                         (f32x2_to_e4m3x2(f[u][6] * inv, f[u][7] * inv) << 16);
+                }
+            }
+            if (col_ok && r < Rpad) {
+                if (KIND == 0) *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = w0;
+                else *reinterpret_cast<uint2*>(packed + r * K + col) = make_uint2(w0, w1);
+            }
+        }
+    }
+    __syncthreads();
+    if (whole_atoms) {
+        const int64_t D = S >> 2;
+        const int64_t d0 = c0 >> 7;
+        const int n_atoms = (int)((K - c0 >= QT_COLS) ? 2 : ((K - c0) >> 7));
+        const int atom = threadIdx.x >> 6;
+        if (atom < n_atoms) {
+            uint2 v = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
+            uint8_t* dst = sblk + ((int64_t)blockIdx.y * D + d0 + atom) * 512 + (threadIdx.x & 63) * 8;
+            *reinterpret_cast<uint2*>(dst) = v;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// MXFP8 elementwise product with ceil-power-of-two scales
+// (csrc/thor_fp4_core.cu:612-652): one lane = 8 elements, 4 lanes = one block.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ue8m0_ceil(float v) {
+    if (!(v > 0.f)) return 0u;
+    const uint32_t u = __float_as_uint(v);
+    uint32_t b;
+    if ((u >> 23) == 0u) b = (u > 0x00400000u) ? 1u : 0u;   // sub-normal: ceil(log2 v) <= -126
+    else b = (u >> 23) + ((u & 0x007fffffu) ? 1u : 0u);
+    return b > 254u ? 254u : b;
+}
+
+__device__ __forceinline__ float pow2_from_ue8m0(uint32_t b) {   // 2^(b-127), b in [0,254]
+    return b ? __uint_as_float(b << 23) : __uint_as_float(0x00400000u);
+}
+
+__global__ void __launch_bounds__(QT_THREADS)
+mx8_mul_kernel(const uint8_t* __restrict__ ap, const uint8_t* __restrict__ as,
+               const uint8_t* __restrict__ bp, const uint8_t* __restrict__ bs,
+               uint8_t* __restrict__ op, uint8_t* __restrict__ os, int64_t R, int64_t K) {
+    __shared__ __align__(16) uint8_t s_sf[2 * 512];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS;
+    const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
+    const int64_t col = c0 + lane * 8;
+    const bool col_ok = col < K;
+    const int64_t S = K >> 5;
+    if (threadIdx.x < 128) reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
+    __syncthreads();
+#pragma unroll 1
+    for (int it = 0; it < QT_ROWS / 8; ++it) {
+        const int rl = warp + 8 * it;
+        const int64_t r = r0 + rl;
+        if (r >= R) continue;   // warp-uniform
+        float fa = 1.f, fb = 1.f;
+        uint2 av = make_uint2(0u, 0u), bv = make_uint2(0u, 0u);
+        if (col_ok) {
+            const int64_t si = sf_index(r, col >> 5, S);
+            fa = pow2_from_ue8m0(as[si]);
+            fb = pow2_from_ue8m0(bs[si]);
+            av = __ldg(reinterpret_cast<const uint2*>(ap + r * K + col));
+            bv = __ldg(reinterpret_cast<const uint2*>(bp + r * K + col));
+        }
+        const uint32_t aw[2] = {av.x, av.y}, bw[2] = {bv.x, bv.y};
+        float f[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float a = e4m3_to_f32((aw[i >> 2] >> (8 * (i & 3))) & 0xffu);
+            const float b = e4m3_to_f32((bw[i >> 2] >> (8 * (i & 3))) & 0xffu);
+            f[i] = __fmul_rn(__fmul_rn(__fmul_rn(a, fa), b), fb);
+            amax = fmaxf(amax, fabsf(f[i]));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint32_t scb = ue8m0_ceil(__fmul_rn(amax, 1.0f / 448.0f));
+        const int e = 127 - (int)scb;
+        const float inv = e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23)
+                                    : __uint_as_float(0x00400000u);
+        if ((lane & 3) == 0 && col_ok) {
+            const int sl = lane >> 2;
+            s_sf[(sl >> 2) * 512 + 16 * (rl & 31) + 4 * (rl >> 5) + (sl & 3)] = (uint8_t)scb;
+        }
+        const uint32_t w0 = f32x2_to_e4m3x2(f[0] * inv, f[1] * inv) | (f32x2_to_e4m3x2(f[2] * inv, f[3] * inv) << 16);
+        const uint32_t w1 = f32x2_to_e4m3x2(f[4] * inv, f[5] * inv) | (f32x2_to_e4m3x2(f[6] * inv, f[7] * inv) << 16);
+        if (col_ok) *reinterpret_cast<uint2*>(op + r * K + col) = make_uint2(w0, w1);
+    }
+    __syncthreads();
+    const int64_t D = S >> 2;
+    const int64_t d0 = c0 >> 7;
+    const int n_atoms = (int)((K - c0 >= QT_COLS) ? 2 : ((K - c0) >> 7));
+    const int atom = threadIdx.x >> 6;
+    if (atom < n_atoms) {
+        uint2 v = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
+        uint8_t* dst = os + ((int64_t)blockIdx.y * D + d0 + atom) * 512 + (threadIdx.x & 63) * 8;
+        *reinterpret_cast<uint2*>(dst) = v;
+    }
+}
+
+template <typename T>
+int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* packed,
+                       uint8_t* sblk, cudaStream_t stream) {
+    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)((R + QT_ROWS - 1) / QT_ROWS));
+    const bool ts_sane = (ts >= 0x1p-100f) && (ts <= 0x1p30f);   // false for NaN too
+    const T* xp = static_cast<const T*>(x);
+    if (!ts_sane) {
+        quant_nvfp4_kernel<T, 2><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+    } else if (sizeof(T) == 2 && ts == 1.0f) {
+        quant_nvfp4_kernel<T, 0><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+    } else {
+        quant_nvfp4_kernel<T, 1><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+    }
+    TFP4_CK(cudaGetLastError());
+    return TFP4_OK;
+}
+
+template <typename T>
+int launch_quant_mx(const void* x, int64_t R, int64_t K, int kind, uint8_t* packed, uint8_t* sblk,
+                    cudaStream_t stream) {
+    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)((R + QT_ROWS - 1) / QT_ROWS));
+    const T* xp = static_cast<const T*>(x);
+    if (kind == 0) quant_mx_kernel<T, 0><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, packed, sblk);
+    else quant_mx_kernel<T, 1><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, packed, sblk);
+    TFP4_CK(cudaGetLastError());
+    return TFP4_OK;
+}
+
+bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
+
+}  // namespace
+
+int quant_nvfp4(const void* x, int64_t R, int64_t K, int in_dtype, float ts, uint8_t* packed,
+                uint8_t* sblk, cudaStream_t stream) {
+    if (K <= 0 || (K % 64) != 0) {
+        fprintf(stderr, "thor_fp4: K must be a multiple of 64 (got %ld)\n", (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    if (R <= 0) return TFP4_OK;
+    if (!x || !packed || !sblk || in_dtype < 0 || in_dtype > 2) {
+        fprintf(stderr, "thor_fp4: tfp4_quant bad argument\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    if (misaligned(x, in_dtype == IN_F32 ? 32 : 16) || misaligned(packed, 4) || misaligned(sblk, 8)) {
+        fprintf(stderr, "thor_fp4: tfp4_quant needs x 16-byte (f32: 32-byte) aligned, packed 4, sblk 8\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    switch (in_dtype) {
+        case IN_F32: return launch_quant_nvfp4<float>(x, R, K, ts, packed, sblk, stream);
+        case IN_F16: return launch_quant_nvfp4<__half>(x, R, K, ts, packed, sblk, stream);
+        default: return launch_quant_nvfp4<__nv_bfloat16>(x, R, K, ts, packed, sblk, stream);
+    }
+}
+
+int quant_mx(const void* x, int64_t R, int64_t K, int in_dtype, int kind, uint8_t* packed,
+             uint8_t* sblk, cudaStream_t stream) {
+    if (K <= 0 || (K % 64) != 0) {
+        fprintf(stderr, "thor_fp4: K must be a multiple of 64 (got %ld)\n", (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    if (R <= 0) return TFP4_OK;
+    if (!x || !packed || !sblk || in_dtype < 0 || in_dtype > 2 || kind < 0 || kind > 1) {
+        fprintf(stderr, "thor_fp4: tfp4_quant_mx bad argument\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    if (misaligned(x, in_dtype == IN_F32 ? 32 : 16) || misaligned(packed, 8) || misaligned(sblk, 8)) {
+        fprintf(stderr, "thor_fp4: tfp4_quant_mx needs x 16-byte (f32: 32-byte) aligned, packed/sblk 8\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    switch (in_dtype) {
+        case IN_F32: return launch_quant_mx<float>(x, R, K, kind, packed, sblk, stream);
+        case IN_F16: return launch_quant_mx<__half>(x, R, K, kind, packed, sblk, stream);
+        default: return launch_quant_mx<__nv_bfloat16>(x, R, K, kind, packed, sblk, stream);
+    }
+}
+
+int mx8_mul(const void* ap, const void* as, const void* bp, const void* bs, void* op, void* os,
+            int64_t R, int64_t K, cudaStream_t stream) {
+    if (K <= 0 || (K % 128) != 0) {
+        fprintf(stderr, "thor_fp4: mx8_mul needs K %% 128 == 0 (got %ld)\n", (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    if (R <= 0) return TFP4_OK;
+    if (misaligned(ap, 8) || misaligned(bp, 8) || misaligned(op, 8) || misaligned(os, 8)) {
+        fprintf(stderr, "thor_fp4: mx8_mul needs 8-byte aligned buffers\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)((R + QT_ROWS - 1) / QT_ROWS));
+    mx8_mul_kernel<<<grid, QT_THREADS, 0, stream>>>(
+        (const uint8_t*)ap, (const uint8_t*)as, (const uint8_t*)bp, (const uint8_t*)bs,
+        (uint8_t*)op, (uint8_t*)os, R, K);
+    TFP4_CK(cudaGetLastError());
+    return TFP4_OK;
+}
+
+}  // namespace tfp4

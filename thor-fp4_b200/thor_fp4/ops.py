@@ -1,0 +1,241 @@
+"""Functional NVFP4 / MX ops over the C ABI (interface of src/thor_fp4/ops.py:16-246
+in the reference project).
+
+All buffers are torch-owned uint8 tensors sized by the *_bytes helpers (rows
+padded to 128, scale columns to 4).  The quantizers write the padding rows of
+the last 128-row tile as zeros themselves, so buffers may come from
+torch.empty as well as torch.zeros; steady-state calls allocate nothing and
+can be captured into CUDA graphs.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _ext
+
+__all__ = [
+    "pad_rows", "packed_bytes", "scale_bytes", "mx_packed_bytes", "mx_scale_bytes",
+    "quantize_nvfp4", "quantize_mx", "mx8_mul", "dequantize_nvfp4", "block_scales",
+    "gemm", "gemm_mx", "gemv", "NVFP4Tensor", "MXTensor",
+]
+
+
+def pad_rows(R: int) -> int:
+    return int(_ext.core().tfp4_pad_rows(R))
+
+
+def packed_bytes(R: int, K: int) -> int:
+    return int(_ext.core().tfp4_packed_bytes(R, K))
+
+
+def scale_bytes(R: int, K: int) -> int:
+    return int(_ext.core().tfp4_scale_bytes(R, K))
+
+
+def mx_packed_bytes(R: int, K: int, kind: str) -> int:
+    return int(_ext.core().tfp4_mx_packed_bytes(R, K, 0 if kind == "mxfp4" else 1))
+
+
+def mx_scale_bytes(R: int, K: int) -> int:
+    return int(_ext.core().tfp4_mx_scale_bytes(R, K))
+
+
+def _check_2d_cuda(x: torch.Tensor):
+    assert x.ndim == 2 and x.is_cuda and x.is_contiguous(), "expected a contiguous 2-D cuda tensor"
+
+
+def quantize_nvfp4(x: torch.Tensor, tensor_scale: float = 1.0,
+                   packed: torch.Tensor | None = None,
+                   sblk: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Row-major (R, K) f32/f16/bf16 cuda tensor -> (packed codes, tile-layout scale bytes)."""
+    L = _ext.device_lib()
+    _check_2d_cuda(x)
+    R, K = x.shape
+    assert K % 64 == 0, f"K={K} must be a multiple of 64 (scale tiles are 4 scale columns wide)"
+    if packed is None:
+        packed = torch.zeros(packed_bytes(R, K), dtype=torch.uint8, device=x.device)
+    if sblk is None:
+        sblk = torch.zeros(scale_bytes(R, K), dtype=torch.uint8, device=x.device)
+    rc = L.tfp4_quant(x.data_ptr(), R, K, _ext.IN_DTYPE[x.dtype], float(tensor_scale),
+                      packed.data_ptr(), sblk.data_ptr(), _ext.stream())
+    assert rc == 0, f"tfp4_quant rc={rc}"
+    return packed, sblk
+
+
+def quantize_mx(x: torch.Tensor, kind: str = "mxfp4",
+                packed: torch.Tensor | None = None,
+                sblk: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """MX quantize: 'mxfp4' (e2m1 codes) or 'mxfp8' (e4m3 codes), UE8M0 scale per 32."""
+    L = _ext.device_lib()
+    assert kind in ("mxfp4", "mxfp8")
+    _check_2d_cuda(x)
+    R, K = x.shape
+    assert K % 64 == 0, f"K={K} must be a multiple of 64"
+    if packed is None:
+        packed = torch.zeros(mx_packed_bytes(R, K, kind), dtype=torch.uint8, device=x.device)
+    if sblk is None:
+        sblk = torch.zeros(mx_scale_bytes(R, K), dtype=torch.uint8, device=x.device)
+    rc = L.tfp4_quant_mx(x.data_ptr(), R, K, _ext.IN_DTYPE[x.dtype], 0 if kind == "mxfp4" else 1,
+                         packed.data_ptr(), sblk.data_ptr(), _ext.stream())
+    assert rc == 0, f"tfp4_quant_mx rc={rc}"
+    return packed, sblk
+
+
+def mx8_mul(a, b, packed: torch.Tensor | None = None, sblk: torch.Tensor | None = None):
+    """h = a * b for two MXFP8 tensors of the same (R, K), K % 128 == 0; ceil-pow2 scales."""
+    L = _ext.device_lib()
+    R, K = a.shape
+    assert tuple(b.shape) == (R, K), f"mx8_mul shape mismatch {a.shape} vs {b.shape}"
+    assert K % 128 == 0, f"K={K} must be a multiple of 128 (atom alignment)"
+    dev = a.packed.device
+    if packed is None:
+        packed = torch.zeros(mx_packed_bytes(R, K, "mxfp8"), dtype=torch.uint8, device=dev)
+    if sblk is None:
+        sblk = torch.zeros(mx_scale_bytes(R, K), dtype=torch.uint8, device=dev)
+    rc = L.tfp4_mx8_mul(a.packed.data_ptr(), a.sblk.data_ptr(), b.packed.data_ptr(), b.sblk.data_ptr(),
+                        packed.data_ptr(), sblk.data_ptr(), R, K, _ext.stream())
+    assert rc == 0, f"tfp4_mx8_mul rc={rc}"
+    return packed, sblk
+
+
+def dequantize_nvfp4(packed: torch.Tensor, sblk: torch.Tensor, tensor_scale: float,
+                     R: int, K: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """NVFP4 buffers -> plain f32 (R, K) (operand builder of verify()'s reference path)."""
+    L = _ext.device_lib()
+    if out is None:
+        out = torch.empty(R, K, dtype=torch.float32, device=packed.device)
+    rc = L.tfp4_dequant_f32(packed.data_ptr(), sblk.data_ptr(), float(tensor_scale), R, K,
+                            out.data_ptr(), _ext.stream())
+    assert rc == 0, f"tfp4_dequant_f32 rc={rc}"
+    return out
+
+
+def block_scales(sblk: torch.Tensor, R: int, K: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tile-layout UE4M3 bytes -> decoded f32 (R, K/16), without the per-tensor scale."""
+    L = _ext.device_lib()
+    if out is None:
+        out = torch.empty(R, K // 16, dtype=torch.float32, device=sblk.device)
+    rc = L.tfp4_scales_f32(sblk.data_ptr(), R, K, out.data_ptr(), _ext.stream())
+    assert rc == 0, f"tfp4_scales_f32 rc={rc}"
+    return out
+
+
+_TORCH_NAME = {"f16": "float16", "bf16": "bfloat16", "f32": "float32"}
+
+
+def gemm(packedA: torch.Tensor, sblkA: torch.Tensor, tsA: float,
+         packedB: torch.Tensor, sblkB: torch.Tensor, tsB: float,
+         out: torch.Tensor, M: int, N: int, K: int, out_dtype: str = "f16",
+         bias: torch.Tensor | None = None) -> None:
+    """out (M, N) row-major = (tsA*tsB) * A(M, K) @ B(N, K)^T (+ bias[n]), NVFP4 operands.
+
+    `bias` (f32, N elements) is an addition over the reference signature: it is added
+    to the FP32 accumulator before the single cast to `out_dtype`."""
+    L = _ext.device_lib()
+    assert out.is_contiguous() and out.numel() == M * N and str(out.dtype).endswith(_TORCH_NAME[out_dtype])
+    if bias is None:
+        rc = L.tfp4_gemm(packedA.data_ptr(), sblkA.data_ptr(), float(tsA),
+                         packedB.data_ptr(), sblkB.data_ptr(), float(tsB),
+                         out.data_ptr(), M, N, K, _ext.OUT_DTYPE[out_dtype], _ext.stream())
+    else:
+        assert bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous()
+        rc = L.tfp4_gemm_bias(packedA.data_ptr(), sblkA.data_ptr(), float(tsA),
+                              packedB.data_ptr(), sblkB.data_ptr(), float(tsB), bias.data_ptr(),
+                              out.data_ptr(), M, N, K, _ext.OUT_DTYPE[out_dtype], _ext.stream())
+    assert rc == 0, f"tfp4_gemm rc={rc}"
+
+
+def gemm_mx(variant: int, packedA: torch.Tensor, sblkA: torch.Tensor,
+            packedB: torch.Tensor, sblkB: torch.Tensor, out: torch.Tensor,
+            M: int, N: int, K: int, alpha: float = 1.0) -> None:
+    """tfc4_gemm: bf16 out = alpha * A @ B^T through a named variant (NVFP4 or MXFP8 x MXFP4)."""
+    L = _ext.device_lib()
+    assert out.is_contiguous() and out.numel() == M * N and out.dtype == torch.bfloat16
+    rc = L.tfc4_gemm(variant, packedA.data_ptr(), sblkA.data_ptr(), packedB.data_ptr(), sblkB.data_ptr(),
+                     out.data_ptr(), M, N, K, float(alpha), _ext.stream())
+    assert rc == 0, f"tfc4_gemm rc={rc}"
+
+
+def gemv(x: torch.Tensor, w: "NVFP4Tensor", out_dtype: str = "f32",
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """out (M, N) = x (M, K) @ dequant(w)^T for M <= 8: exact activations, FP32 accumulation."""
+    L = _ext.device_lib()
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    _check_2d_cuda(x)
+    assert 1 <= M <= 8, f"gemv serves M <= 8 (got {M})"
+    if out is None:
+        out = torch.empty(M, N, dtype=_ext.OUT_TORCH[out_dtype], device=x.device)
+    rc = L.tfp4_gemv(x.data_ptr(), M, K, _ext.IN_DTYPE[x.dtype],
+                     w.packed.data_ptr(), w.gemv_scales().data_ptr(), float(w.tensor_scale),
+                     out.data_ptr(), N, _ext.OUT_DTYPE[out_dtype], _ext.stream())
+    assert rc == 0, f"tfp4_gemv rc={rc}"
+    return out
+
+
+class NVFP4Tensor:
+    """A row-major (R, K) tensor resident in NVFP4: codes + block scales + per-tensor scale."""
+
+    def __init__(self, packed: torch.Tensor, sblk: torch.Tensor, tensor_scale: float,
+                 shape: tuple[int, int]):
+        self.packed, self.sblk = packed, sblk
+        self.tensor_scale, self.shape = float(tensor_scale), tuple(shape)
+        self._gemv_scales: torch.Tensor | None = None
+
+    def gemv_scales(self) -> torch.Tensor:
+        """Block scales un-scattered to plain (R, K/16) bytes (cached)."""
+        if self._gemv_scales is None:
+            R, K = self.shape
+            out = torch.empty(R, K // 16, dtype=torch.uint8, device=self.packed.device)
+            rc = _ext.device_lib().tfp4_scales_gemv(self.sblk.data_ptr(), R, K, out.data_ptr(), _ext.stream())
+            assert rc == 0, f"tfp4_scales_gemv rc={rc}"
+            self._gemv_scales = out
+        return self._gemv_scales
+
+    @classmethod
+    def from_float(cls, x: torch.Tensor, tensor_scale: float | None = None):
+        """tensor_scale=None: two-level recipe amax/(6*448) (floor 1e-30); 1.0: block scales only."""
+        assert x.ndim == 2 and x.is_contiguous()
+        x = x.float() if x.dtype != torch.float32 else x
+        if tensor_scale is None:
+            tensor_scale = max(x.abs().amax().item() / (6.0 * 448.0), 1e-30)
+        packed, sblk = quantize_nvfp4(x, tensor_scale)
+        return cls(packed, sblk, tensor_scale, tuple(x.shape))
+
+    def dequantize(self) -> torch.Tensor:
+        R, K = self.shape
+        return dequantize_nvfp4(self.packed, self.sblk, self.tensor_scale, R, K)
+
+    def matmul_t(self, w: "NVFP4Tensor", out_dtype: str = "f16",
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+        """(M, K) @ (N, K)^T -> (M, N); self is the activation-side operand."""
+        M, K = self.shape
+        N, K2 = w.shape
+        assert K == K2
+        if out is None:
+            out = torch.empty(M, N, dtype=_ext.OUT_TORCH[out_dtype], device=self.packed.device)
+        gemm(self.packed, self.sblk, self.tensor_scale, w.packed, w.sblk, w.tensor_scale,
+             out, M, N, K, out_dtype)
+        return out
+
+    def nbytes(self) -> int:
+        R, K = self.shape
+        return R * K // 2 + R * (K // 16)
+
+
+class MXTensor:
+    """A row-major (R, K) tensor in an MX format ('mxfp4' or 'mxfp8')."""
+
+    def __init__(self, packed: torch.Tensor, sblk: torch.Tensor, kind: str, shape):
+        self.packed, self.sblk, self.kind, self.shape = packed, sblk, kind, tuple(shape)
+
+    @classmethod
+    def from_float(cls, x: torch.Tensor, kind: str = "mxfp4"):
+        assert x.ndim == 2 and x.is_contiguous()
+        packed, sblk = quantize_mx(x.float(), kind)
+        return cls(packed, sblk, kind, x.shape)
+
+    def nbytes(self) -> int:
+        R, K = self.shape
+        return R * (K // 2 if self.kind == "mxfp4" else K) + R * (K // 32)
