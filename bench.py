@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 linear-layer hot path (activation quantizer + tcgen05 GEMM).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload linear|quant|gemm|mlp] [--M ..] [--N ..] [--K ..]
+
+Default workload: thor_fp4.Linear(8192, 8192, bias=False, out_dtype='bf16') on a
+bf16 activation [8192, 8192] ~N(0,1) (M = N = K = 8192, the shape the headline
+metric is quoted on); one step = quantize the activation + block-scaled GEMM.
+Inputs rotate over buffers larger than L2.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "thor-fp4_b200"))
+sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quant", "gemm", "mlp"])
+    ap.add_argument("--M", type=int, default=8192)
+    ap.add_argument("--N", type=int, default=8192)
+    ap.add_argument("--K", type=int, default=8192)
+    ap.add_argument("--inter", type=int, default=28672, help="mlp workload: intermediate size")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16": d["bf16_tflops"], "bf16_sustained": d.get("bf16_tflops_sustained"),
+                "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "src": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU legs
+METRIC = "NVFP4 Linear TFLOPS at M=N=K=8192 (% FP4 peak); act-quantize GB/s (% HBM)"
+DTYPE = "nvfp4 (e2m1 codes, ue4m3 block scales), f32 accumulate"
+
+
+class CpuLinear:
+    """The reference's CPU emulation of one NVFP4 linear layer (fake-quantize the activation,
+    FP32 matmul against the dequantized quantized weight: src/thor_fp4/quant.py:32-53 and
+    src/thor_fp4/verify.py:91-100 in the reference project), through the oracle port.  The
+    weight is quantized once outside the timed step, as the reference caches it."""
+
+    def __init__(self, N: int, K: int, threads: int):
+        from oracle import oracle as orc
+        self.orc, self.threads, self.N, self.K = orc, threads, N, K
+        rng = np.random.default_rng(0)
+        w = (rng.random((N, K), dtype=np.float32) * 2 - 1) * np.float32(1.0 / np.sqrt(K))   # Kaiming-uniform(a=sqrt 5)
+        ts = orc.two_level_scale(w)
+        p, s = orc.quantize_nvfp4(w, ts, threads)
+        self.wd_t = np.ascontiguousarray(orc.dequantize_nvfp4(p, s, ts, N, K, threads).T)
+        self.rng = rng
+
+    def make_input(self, M: int):
+        x = self.rng.standard_normal((M, self.K), dtype=np.float32)
+        return (x.view(np.uint32) & 0xFFFF0000).view(np.float32)      # bf16-representable
+
+    def step(self, x):
+        orc = self.orc
+        p, s = orc.quantize_nvfp4(x, 1.0, self.threads)
+        xd = orc.dequantize_nvfp4(p, s, 1.0, x.shape[0], self.K, self.threads)
+        return xd @ self.wd_t
+
+
+def cpu_baseline(args, sample_rows: int = 2048):
+    from oracle import oracle as orc
+    threads = orc.host_threads()
+    M = min(args.M, sample_rows)
+    lin = CpuLinear(args.N, args.K, threads)
+    x = lin.make_input(M)
+    lin.step(x[:64])
+    t0 = time.perf_counter()
+    lin.step(x)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * M * args.N * args.K / dt / 1e12, "unit": "TFLOPS", "cores": threads, "kind": "port",
+            "sample": f"oracle port (C quantize + dequantize, numpy FP32 matmul) on {M} of {args.M} activation rows, "
+                      f"N={args.N}, K={args.K}; weight quantized once outside the timed step; {dt:.2f} s"}
+
+
+def run_reference(args):
+    """--impl reference: the reference's own CPU emulation of the path on all host threads
+    (oracle port: the reference's torch code cannot travel to the GPU box); each step is a
+    bounded slab of activation rows of the same layer."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    threads = orc.host_threads()
+    M = min(args.M, 1024)
+    steps, warm = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
+    lin = CpuLinear(args.N, args.K, threads)
+    x = lin.make_input(M)
+    for _ in range(warm):
+        lin.step(x)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        lin.step(x)
+    dt = (time.perf_counter() - t0) / steps
+    val = 2.0 * M * args.N * args.K / dt / 1e12
+    sample = f"{M} of {args.M} activation rows per step, oracle port, weight quantized once"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": {"workload": workload_name(args)},
+        "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_name(args):
+    return (f"thor_fp4.Linear({args.K},{args.N},bias=False,out_dtype=bf16), activation bf16 [{args.M},{args.K}] ~N(0,1), "
+            "weight Kaiming-uniform fp32 quantized once (two-level NVFP4); step = activation quantize + block-scaled GEMM")
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+    import thor_fp4
+    from thor_fp4 import _ext, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    M, N, K = args.M, args.N, args.K
+    pk = peaks()
+    torch.manual_seed(1234 + rank)
+    lin = thor_fp4.Linear(K, N, bias=False, out_dtype="bf16").to(dev)
+    lin.refresh_weight()
+    w = lin._weight_fp4
+    # inputs larger than L2 (126 MB): rotate over buffers totalling > 256 MB
+    n_in = max(2, int(np.ceil(300e6 / (M * K * 2))))
+    xs = [torch.randn(M, K, device=dev).bfloat16() for _ in range(n_in)]
+    packed = torch.zeros(ops.packed_bytes(M, K), dtype=torch.uint8, device=dev)
+    sblk = torch.zeros(ops.scale_bytes(M, K), dtype=torch.uint8, device=dev)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+    def step(i, ev=None):
+        x = xs[i % n_in]
+        if ev is not None:
+            ev[0].record()
+        ops.quantize_nvfp4(x, 1.0, packed, sblk)
+        if ev is not None:
+            ev[1].record()
+        ops.gemm(packed, sblk, 1.0, w.packed, w.sblk, w.tensor_scale, out, M, N, K, "bf16")
+        if ev is not None:
+            ev[2].record()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record()
+    for i in range(args.steps):
+        step(i, evs[i])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_begin.elapsed_time(t_end)
+    q_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
+    g_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
+    if _ext.status() != 0:
+        raise RuntimeError(f"device status word {_ext.status()}: a GEMM wait expired")
+
+    # ---------------- end to end through the public API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        hx = [torch.randn(M, K).bfloat16().pin_memory() for _ in range(2)]
+        hy = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+        dx = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        n_e2e = max(3, min(args.steps, 10))
+
+        def e2e_step(i):
+            dx.copy_(hx[i % 2], non_blocking=True)
+            y = lin(dx)
+            hy.copy_(y, non_blocking=True)
+        for i in range(2):
+            e2e_step(i)
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n_e2e):
+            e2e_step(i)
+        b.record()
+        barrier()
+        e2e_ms = a.elapsed_time(b) / n_e2e
+    else:
+        e2e_ms = None
+
+    t = torch.tensor([total_ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_max = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_step = total_ms / args.steps
+    flop = 2.0 * M * N * K
+    value = world * flop / (ms_step * 1e-3) / 1e12
+    gemm_tflops = flop / (g_ms * 1e-3) / 1e12
+    q_bytes = M * K * (2 + 0.5 + 1.0 / 16)
+    q_gbs = q_bytes / (q_ms * 1e-3) / 1e9
+    fp4_peak = 4.0 * pk["bf16"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": {"workload": workload_name(args), "replicas": world,
+                   "l2": f"inputs rotate over {n_in} buffers of {M * K * 2 / 1e6:.0f} MB (> 126 MB L2)"},
+        "roofline": {"bound": "tensor", "kernel": "gemm_bs_kernel (tcgen05 NVFP4 block-scaled GEMM)",
+                     "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
+                     "peak_note": f"4 x {pk['src']} bf16 burst ({pk['bf16']}); no FP4 peak is measured on this pool",
+                     "frac_of_nominal_9000": gemm_tflops / 9000.0, "traffic": None,
+                     "avg_launch_ms": g_ms},
+        "roofline_quantizer": {"bound": "hbm", "kernel": "quant_nvfp4_kernel", "achieved": q_gbs,
+                               "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": q_gbs / pk["hbm_gbs"],
+                               "peak_note": f"{pk['src']} copy bandwidth", "traffic": None, "avg_launch_ms": q_ms,
+                               "algorithmic_bytes_per_launch": q_bytes},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if e2e_ms is not None:
+        line["e2e"] = {"value": world * flop / (e2e_max * 1e-3) / 1e12, "unit": "TFLOPS",
+                       "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                       "ms_per_step": e2e_max, "api": "thor_fp4.Linear.forward, pinned host buffers"}
+    if not args.no_cpu and world >= 1:
+        line["cpu_baseline"] = cpu_baseline(args)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the engine has no CPU fallback (use --impl reference for the CPU arm)")
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

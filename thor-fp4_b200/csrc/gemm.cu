@@ -42,10 +42,10 @@ namespace {
 
 constexpr int BM = 128;             // weight rows per tile (MMA M)
 constexpr int KB_BYTES = 128;       // bytes of K per stage and row (one swizzle span)
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;   // producer, MMA issuer, 4 epilogue warps, 4 scale-loader warps
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_SFW_COL = 256;   // 16 columns: weight-side scales of one stage
-constexpr int TMEM_SFA_COL = 272;   // up to 32 columns: token-side scales of one stage
+constexpr int TMEM_SF_SLOT_COLS = 48;   // 16 columns of weight-side scales + up to 32 of token-side scales
+constexpr int TMEM_SFA_OFF = 16;
 constexpr long long WAIT_CYCLES = 2000000000ll;   // ~1 s at 2 GHz
 
 struct GemmParams {
@@ -63,7 +63,9 @@ struct GemmParams {
     int32_t k_blocks;
     int32_t last_atoms;      // NVFP4: 64-element MMAs in the last K block (1..4); MX: 32-element ones
     int32_t stages;
+    int32_t debug;           // test hook: bit0 no stores, bit1 no scale copies, bit2 no MMA, bit3 no loads, bit4 no tmem loads
     int* status;             // host-visible status word (0 = ok)
+    unsigned long long* stats;   // host-visible per-CTA cycle counters (debug bit 1024), 4 per CTA
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -84,6 +86,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// non-blocking poll (try_wait may park the thread for a while when the phase is not complete)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -169,14 +183,18 @@ __device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
 
 template <int KIND, int BN>
 struct Cfg {
-    static constexpr int ACC_STAGES = (BN <= 128) ? 2 : 1;
+    static constexpr int ACC_STAGES = (2 * BN + 2 * TMEM_SF_SLOT_COLS <= TMEM_COLS) ? 2 : 1;
+    static constexpr int SF_COL = ACC_STAGES * BN;                    // scale slots follow the accumulators
     static constexpr int SF_TILES = (BN + 127) / 128;                 // 128-row scale tiles on the token side
     static constexpr int ATOMS = (KIND == 0) ? 4 : 1;                 // scale atoms per 128 rows per stage
     static constexpr int W_BYTES = BM * KB_BYTES;                     // 16 KB
     static constexpr int A_BYTES = BN * KB_BYTES;
     static constexpr int SFW_BYTES = ATOMS * 512;
     static constexpr int SFA_BYTES = SF_TILES * ATOMS * 512;
-    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + SFW_BYTES + SFA_BYTES;   // multiple of 1024? see static_assert
+    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + SFW_BYTES + SFA_BYTES;
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 1024 - 256;      // alignment slack + barriers
+    static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
+    static_assert(STAGES >= 3, "pipeline too shallow");
     static_assert((W_BYTES % 1024) == 0 && (A_BYTES % 1024) == 0, "operand tiles must keep 1024-byte alignment");
     // instruction descriptor (block-scaled form): formats, N>>3 at bit 17, scale format at 23, M>>4 at 24
     static constexpr uint32_t IDESC =
@@ -184,31 +202,83 @@ struct Cfg {
         ((uint32_t)(BN >> 3) << 17) | ((KIND == 0 ? 0u : 1u) << 23) | ((uint32_t)(BM >> 4) << 24);
 };
 
+// tcgen05 instructions guarded by a predicate held in a register: the issuing warp keeps
+// warp-uniform control flow (so that descriptors stay in uniform registers) and exactly one
+// lane has `on` set.
+__device__ __forceinline__ void tc_cp_sf_if(uint32_t on, uint32_t taddr, uint64_t sdesc) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+        "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}"
+        ::"r"(taddr), "l"(sdesc), "r"(on) : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t on, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(on) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma_if(uint32_t on, uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    if (KIND == 0) {
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb), "r"(on)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb), "r"(on)
+            : "memory");
+    }
+}
+
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t* v) {
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr) : "memory");
+}
+// store N consecutive 32-bit columns of this warp's 32 tensor-memory lanes (lane i <- thread i)
+template <int N>
+__device__ __forceinline__ void tc_st(uint32_t taddr, const uint32_t* v);
+template <>
+__device__ __forceinline__ void tc_st<4>(uint32_t taddr, const uint32_t* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+}
+template <>
+__device__ __forceinline__ void tc_st<16>(uint32_t taddr, const uint32_t* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+
 template <int KIND, int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                const GemmParams p) {
     using C = Cfg<KIND, BN>;
+    constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte aligned carve-up: [stages x (W | act | sfW | sfA)] [barriers]
+    // 1024-byte aligned carve-up: [STAGES x W] [STAGES x act] [STAGES x sfW] [STAGES x sfA] [barriers]
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int stages = p.stages;
     uint8_t* sW = smem;
-    uint8_t* sA = sW + (size_t)stages * C::W_BYTES;
-    uint8_t* sSFW = sA + (size_t)stages * C::A_BYTES;
-    uint8_t* sSFA = sSFW + (size_t)stages * C::SFW_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sSFA + (size_t)stages * C::SFA_BYTES);
-    uint64_t* full_bar = bars;                       // [stages]
-    uint64_t* empty_bar = bars + stages;             // [stages]
-    uint64_t* tfull_bar = bars + 2 * stages;         // [ACC_STAGES]
+    uint8_t* sA = sW + (size_t)STAGES * C::W_BYTES;
+    uint8_t* sSFW = sA + (size_t)STAGES * C::A_BYTES;
+    uint8_t* sSFA = sSFW + (size_t)STAGES * C::SFW_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSFA + (size_t)STAGES * C::SFA_BYTES);
+    uint64_t* full_bar = bars;                         // [STAGES]
+    uint64_t* empty_bar = bars + STAGES;               // [STAGES]
+    uint64_t* tfull_bar = bars + 2 * STAGES;           // [ACC_STAGES]
     uint64_t* tempty_bar = tfull_bar + C::ACC_STAGES;  // [ACC_STAGES]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::ACC_STAGES);
+    uint64_t* sffull_bar = tempty_bar + C::ACC_STAGES; // [2] scale slot filled (one arrival per loader warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sffull_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
@@ -216,6 +286,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             mbar_init(smem_u32(&tfull_bar[a]), 1);
             mbar_init(smem_u32(&tempty_bar[a]), 4);   // one arrival per epilogue warp
         }
+        mbar_init(smem_u32(&sffull_bar[0]), 4);
+        mbar_init(smem_u32(&sffull_bar[1]), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -231,105 +303,141 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     const int64_t total_tiles = p.m_tiles * p.n_tiles;
     const int k_blocks = p.k_blocks;
+    const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
                 const int n0 = (int)(nt * BM), m0 = (int)(mt * BN);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = (int)(it % (uint32_t)stages);
-                    const uint32_t ph = (it / (uint32_t)stages) & 1u;
-                    if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, 1)) { ok = false; break; }
-                    const int atoms = (kb == k_blocks - 1) ? ((KIND == 0) ? p.last_atoms : 1) : C::ATOMS;
-                    const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-                    int a_tiles = 0;
+                const int64_t a_tile0 = (mt * BN) >> 7;     // first 128-row scale tile of this token tile
+                int a_tiles = 0;
 #pragma unroll
-                    for (int t = 0; t < C::SF_TILES; ++t)
-                        if (mt * C::SF_TILES + t < p.rows_a_tiles) ++a_tiles;
-                    const uint32_t bar = smem_u32(&full_bar[s]);
-                    mbar_expect_tx(bar, (uint32_t)(C::W_BYTES + C::A_BYTES) + sf_bytes * (uint32_t)(1 + a_tiles));
-                    tma_load_2d(smem_u32(sW + (size_t)s * C::W_BYTES), &tmW, kb * (KIND == 0 ? KB_BYTES : KB_BYTES), n0, bar);
-                    tma_load_2d(smem_u32(sA + (size_t)s * C::A_BYTES), &tmA, kb * KB_BYTES, m0, bar);
-                    const int64_t sf_k_off = (int64_t)kb * C::ATOMS * 512;
-                    bulk_load(smem_u32(sSFW + (size_t)s * C::SFW_BYTES),
-                              p.sfW + nt * p.sf_tile_stride + sf_k_off, sf_bytes, bar);
+                for (int t = 0; t < C::SF_TILES; ++t)
+                    if (a_tile0 + t < p.rows_a_tiles) ++a_tiles;
+                const uint8_t* sfw_g = p.sfW + nt * p.sf_tile_stride;
+                const uint8_t* sfa_g = p.sfA + a_tile0 * p.sf_tile_stride;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+                    const uint32_t bar = full0 + 8 * s;
+                    if (p.debug & 8) {
+                        mbar_arrive(bar);
+                    } else {
+                        const int atoms = (kb == k_blocks - 1) ? ((KIND == 0) ? p.last_atoms : 1) : C::ATOMS;
+                        const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+                        mbar_expect_tx(bar, (uint32_t)(C::W_BYTES + C::A_BYTES) + sf_bytes * (uint32_t)(1 + a_tiles));
+                        tma_load_2d(smem_u32(sW) + s * C::W_BYTES, &tmW, kb * KB_BYTES, n0, bar);
+                        tma_load_2d(smem_u32(sA) + s * C::A_BYTES, &tmA, kb * KB_BYTES, m0, bar);
+                        const int64_t sf_k_off = (int64_t)kb * C::ATOMS * 512;
+                        bulk_load(smem_u32(sSFW) + s * C::SFW_BYTES, sfw_g + sf_k_off, sf_bytes, bar);
 #pragma unroll
-                    for (int t = 0; t < C::SF_TILES; ++t) {
-                        if (mt * C::SF_TILES + t < p.rows_a_tiles)
-                            bulk_load(smem_u32(sSFA + (size_t)s * C::SFA_BYTES + (size_t)t * C::ATOMS * 512),
-                                      p.sfA + (mt * C::SF_TILES + t) * p.sf_tile_stride + sf_k_off, sf_bytes, bar);
+                        for (int t = 0; t < C::SF_TILES; ++t) {
+                            if (t < a_tiles)
+                                bulk_load(smem_u32(sSFA) + s * C::SFA_BYTES + t * C::ATOMS * 512,
+                                          sfa_g + t * p.sf_tile_stride + sf_k_off, sf_bytes, bar);
+                        }
                     }
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
             if (!ok) {
                 // let copies already issued land before the CTA's shared memory goes away
-                for (int s = 0; s < stages; ++s) {
-                    const long long t0 = clock64();
-                    while (clock64() - t0 < 2000000ll) {}
-                }
+                const long long t0 = clock64();
+                while (clock64() - t0 < 4000000ll) {}
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
-            bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const int acc = (int)(tcount % C::ACC_STAGES);
-                const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
-                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_flag, 2)) { ok = false; break; }
+        // The whole warp walks the loop (uniform control flow); lane 0 alone issues.
+        const uint32_t on = (lane == 0) ? 1u : 0u;
+        uint32_t s = 0, ph = 0, tcount = 0, it = 0;
+        bool ok = true, peek_full = false, peek_sf = false;
+        long long c_full = 0, c_cp = 0, c_mma = 0;
+        const bool prof = (p.debug & 1024) != 0;
+        const long long c_begin = clock64();
+        const uint32_t w_base = smem_u32(sW), a_base = smem_u32(sA);
+        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+            const uint32_t acc = tcount % C::ACC_STAGES;
+            const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
+            if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_flag, 2)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            // token tiles of 192 start at row 0 or 64 of a 128-row scale atom: rows 32c..32c+31 of
+            // an atom sit in scale column c, so the token-side scale address moves by 0 or 2 columns
+            const uint32_t sf_off = (BN == 192) ? (uint32_t)((((tile % p.m_tiles) * BN) & 127) >> 5) : 0u;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+                if (prof) c0 = clock64();
+                // the barriers of this K block were polled once while the previous block's MMAs were
+                // being issued; spin only if that poll failed
+                const uint32_t slot = it & 1u;
+                if (!(peek_full || mbar_wait(full0 + 8 * s, ph, abort_flag, 3))) { ok = false; break; }
+                if (prof) c1 = clock64();
+                if (!(peek_sf || mbar_wait(smem_u32(&sffull_bar[slot]), (it >> 1) & 1u, abort_flag, 5))) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = (int)(it % (uint32_t)stages);
-                    const uint32_t ph = (it / (uint32_t)stages) & 1u;
-                    if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, 3)) { ok = false; break; }
-                    tc_fence_after();
-                    const int n_mma = (kb == k_blocks - 1) ? p.last_atoms : 4;
-                    const int atoms = (KIND == 0) ? n_mma : 1;
-                    const uint32_t sfw_s = smem_u32(sSFW + (size_t)s * C::SFW_BYTES);
-                    const uint32_t sfa_s = smem_u32(sSFA + (size_t)s * C::SFA_BYTES);
-                    for (int j = 0; j < atoms; ++j) {
-                        tc_cp_sf(tmem_base + TMEM_SFW_COL + 4 * j, desc_sf_atom(sfw_s + 512 * j));
-#pragma unroll
-                        for (int t = 0; t < C::SF_TILES; ++t)
-                            tc_cp_sf(tmem_base + TMEM_SFA_COL + 4 * (j * C::SF_TILES + t),
-                                     desc_sf_atom(sfa_s + (t * C::ATOMS + j) * 512));
+                const int n_mma = (kb == k_blocks - 1) ? p.last_atoms : 4;
+                const uint32_t sfw_c = tmem_base + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
+                const uint32_t sfa_c = sfw_c + TMEM_SFA_OFF + sf_off;
+                {   // poll the next K block's barriers now; the result is consumed next iteration
+                    const uint32_t s_n = (s + 1 == STAGES) ? 0u : s + 1;
+                    const uint32_t ph_n = (s + 1 == STAGES) ? ph ^ 1u : ph;
+                    if (!(p.debug & 32)) {
+                        peek_full = mbar_test_wait(full0 + 8 * s_n, ph_n);
+                        peek_sf = mbar_test_wait(smem_u32(&sffull_bar[slot ^ 1u]), ((it + 1) >> 1) & 1u);
                     }
-                    const uint32_t w_s = smem_u32(sW + (size_t)s * C::W_BYTES);
-                    const uint32_t a_s = smem_u32(sA + (size_t)s * C::A_BYTES);
-                    for (int j = 0; j < n_mma; ++j) {
-                        const uint64_t adesc = desc_sw128(w_s + 32 * j);
-                        const uint64_t bdesc = desc_sw128(a_s + 32 * j);
-                        uint32_t idesc = C::IDESC, sfw_t, sfa_t;
-                        if (KIND == 0) {
-                            sfw_t = tmem_base + TMEM_SFW_COL + 4 * j;
-                            sfa_t = tmem_base + TMEM_SFA_COL + 4 * j * C::SF_TILES;
-                        } else {
-                            // one scale byte per row per MMA: byte j of the 4-byte column
-                            idesc |= ((uint32_t)j << 29) | ((uint32_t)j << 4);
-                            sfw_t = (tmem_base + TMEM_SFW_COL) | ((uint32_t)j << 30);
-                            sfa_t = (tmem_base + TMEM_SFA_COL) | ((uint32_t)j << 30);
-                        }
-                        tc_mma<KIND>(d_tmem, adesc, bdesc, idesc, sfw_t, sfa_t, (kb > 0 || j > 0) ? 1u : 0u);
-                    }
-                    tc_commit(smem_u32(&empty_bar[s]));
                 }
-                if (ok) tc_commit(smem_u32(&tfull_bar[acc]));
+                if (prof) c2 = clock64();
+                const uint64_t adesc0 = desc_sw128(w_base + s * C::W_BYTES);
+                const uint64_t bdesc0 = desc_sw128(a_base + s * C::A_BYTES);
+                if (!(p.debug & 4)) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (j < n_mma) {
+                            uint32_t idesc = C::IDESC, sfw_t, sfa_t;
+                            if (KIND == 0) {
+                                sfw_t = sfw_c + 4 * j;
+                                sfa_t = sfa_c + 4 * j * C::SF_TILES;
+                            } else {
+                                // one scale byte per row per MMA: byte j of the 4-byte column
+                                idesc |= ((uint32_t)j << 29) | ((uint32_t)j << 4);
+                                sfw_t = sfw_c | ((uint32_t)j << 30);
+                                sfa_t = sfa_c | ((uint32_t)j << 30);
+                            }
+                            // advancing K by 64 (or 32) elements = 32 bytes inside the swizzle span
+                            tc_mma_if<KIND>(on, d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t,
+                                            (kb > 0 || j > 0) ? 1u : 0u);
+                        }
+                    }
+                }
+                tc_commit_if(on, empty0 + 8 * s);
+                if (prof) {
+                    c3 = clock64();
+                    c_full += c1 - c0;
+                    c_cp += c2 - c1;
+                    c_mma += c3 - c2;
+                }
+                ++it;
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
             }
+            if (ok) tc_commit_if(on, smem_u32(&tfull_bar[acc]));
         }
-    } else {
+        if (prof && lane == 0 && p.stats != nullptr && blockIdx.x < 256) {
+            p.stats[blockIdx.x * 4 + 0] = (unsigned long long)(clock64() - c_begin);
+            p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_full;
+            p.stats[blockIdx.x * 4 + 2] = (unsigned long long)c_cp;
+            p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_mma;
+        }
+    } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int ew = warp & 3;                       // tensor-memory lane quarter this warp may read
         uint32_t tcount = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
             const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
-            const int acc = (int)(tcount % C::ACC_STAGES);
+            const uint32_t acc = tcount % C::ACC_STAGES;
             const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
             if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
@@ -340,11 +448,12 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const float alpha = p.alpha;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (p.debug & 16) continue;
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN + c0);
                 tc_ld32(taddr, v);
                 tc_wait_ld();
-                if (m0 + c0 < p.M && n_ok) {
+                if (m0 + c0 < p.M && n_ok && !(p.debug & 1)) {
                     if (p.out_dtype == OUT_BF16) {
                         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (m0 + c0) * p.N + n;
 #pragma unroll
@@ -366,6 +475,55 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        }
+    } else {
+        // ------------------------------------------------------------ scale loaders (warps 6..9)
+        // tcgen05.cp would run in the MMA pipe (~70 cycles per 512-byte atom, 12 atoms per K
+        // block, more than the four MMAs themselves).  Instead each of these warps reads the
+        // atoms of a K block from shared memory - an atom is exactly 32 lanes x 16 bytes - and
+        // stores them into its own quarter of the tensor-memory lanes with tcgen05.st; the four
+        // warps together give the replication across lane quarters the MMA expects.
+        const int q = warp & 3;
+        uint32_t s = 0, ph = 0, it = 0;
+        // stage / phase of the K block two iterations back (whose MMAs must be done before
+        // its scale slot is overwritten)
+        uint32_t s2 = 0, ph2 = 0;
+        bool ok = true;
+        const uint32_t sfw_base = smem_u32(sSFW), sfa_base = smem_u32(sSFA);
+        for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 6)) { ok = false; break; }
+                if (it >= 2) {
+                    if (!mbar_wait(empty0 + 8 * s2, ph2, abort_flag, 7)) { ok = false; break; }
+                    if (++s2 == STAGES) { s2 = 0; ph2 ^= 1u; }
+                }
+                tc_fence_after();
+                const uint32_t slot = it & 1u;
+                const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
+                if (!(p.debug & 2)) {
+                    uint32_t v[C::ATOMS * 4];
+                    const uint32_t src_w = sfw_base + s * C::SFW_BYTES + lane * 16;
+#pragma unroll
+                    for (int j = 0; j < C::ATOMS; ++j) ld_shared_v4(src_w + 512 * j, &v[4 * j]);
+                    tc_st<C::ATOMS * 4>(t_base, v);
+#pragma unroll
+                    for (int t = 0; t < C::SF_TILES; ++t) {
+                        // token-side atom (j, t) goes to columns 16 + 4 * (j * SF_TILES + t)
+                        const uint32_t src_a = sfa_base + s * C::SFA_BYTES + t * C::ATOMS * 512 + lane * 16;
+#pragma unroll
+                        for (int j = 0; j < C::ATOMS; ++j) ld_shared_v4(src_a + 512 * j, &v[4 * j]);
+#pragma unroll
+                        for (int j = 0; j < C::ATOMS; ++j)
+                            tc_st<4>(t_base + TMEM_SFA_OFF + 4 * (j * C::SF_TILES + t), &v[4 * j]);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&sffull_bar[slot]));
+                ++it;
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
         }
     }
 
@@ -390,7 +548,9 @@ struct DeviceState {
     int max_smem = 0;
     int* status_host = nullptr;   // pinned, mapped
     int* status_dev = nullptr;
-    bool attr_set[2][4] = {{false, false, false, false}, {false, false, false, false}};
+    unsigned long long* stats_host = nullptr;
+    unsigned long long* stats_dev = nullptr;
+    bool attr_set[2][5] = {{false, false, false, false, false}, {false, false, false, false, false}};
 };
 
 std::mutex g_mu;
@@ -433,6 +593,8 @@ int ensure_device(DeviceState** out) {
         TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), sizeof(int), cudaHostAllocMapped));
         *st.status_host = 0;
         TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0));
+        TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.stats_host), 256 * 4 * sizeof(unsigned long long), cudaHostAllocMapped));
+        TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.stats_dev), st.stats_host, 0));
         it = g_dev.emplace(dev, st).first;
     }
     *out = &it->second;
@@ -459,15 +621,12 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint6
 template <int KIND, int BN>
 int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaStream_t stream) {
     using C = Cfg<KIND, BN>;
-    const int bar_bytes = 256;
-    int stages = (st->max_smem - 1024 - bar_bytes) / C::STAGE_BYTES;
-    if (stages > 8) stages = 8;
-    if (stages > p.k_blocks * 2 && p.k_blocks * 2 >= 2) stages = p.k_blocks * 2;
-    if (stages < 2) return TFP4_ERR_NO_PLAN;
-    p.stages = stages;
-    // keep one CTA per SM: each CTA allocates all 512 tensor-memory columns
-    size_t smem = (size_t)stages * C::STAGE_BYTES + bar_bytes + 1024;
+    // every CTA allocates all 512 tensor-memory columns: the shared-memory request also keeps
+    // the kernel at one CTA per SM
+    size_t smem = (size_t)C::STAGES * C::STAGE_BYTES + 256 + 1024;
     if (smem < 120 * 1024) smem = 120 * 1024;
+    if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
+    p.stages = C::STAGES;
     if (!st->attr_set[KIND][bn_slot]) {
         TFP4_CK(cudaFuncSetAttribute(gemm_bs_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      st->max_smem));
@@ -485,6 +644,7 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
 }
 
 int g_force_bn = 0;
+int g_debug = 0;
 
 }  // namespace
 
@@ -517,8 +677,22 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
         fprintf(stderr, "thor_fp4_b200: an earlier GEMM gave up waiting on the device (code %d)\n", *st->status_host);
         return TFP4_ERR_DEVICE_TIMEOUT;
     }
+    // token tiles narrower than a 128-row scale atom are used only when the whole batch fits
+    // one tile (the tile then starts at row 0 of its atom)
     int bn = g_force_bn;
-    if (bn == 0) bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    if (bn != 0 && bn < 128 && M > bn) bn = 0;
+    if (bn == 0) {
+        if (M <= 128) bn = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+        else if (M <= 192) bn = 192;
+        else if (M <= 256) bn = 256;
+        else {
+            // 192-token tiles leave room for two accumulators (the epilogue of one tile overlaps the
+            // main loop of the next); 256-token tiles do more work per MMA but drain serially.  The
+            // wider tile only pays when every CTA gets at most one tile.
+            const int64_t tiles256 = ((M + 255) / 256) * ((N + BM - 1) / BM);
+            bn = (tiles256 <= st->sm_count && (M % 256) == 0) ? 256 : 192;
+        }
+    }
     int dev = 0;
     cudaGetDevice(&dev);
     PlanKey key{packedA, packedB, M, N, K, kind, bn, dev};
@@ -563,13 +737,16 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     const int64_t rem = K - (int64_t)(p.k_blocks - 1) * kb_elems;
     p.last_atoms = (int32_t)(kind == 0 ? rem / 64 : rem / 32);
     p.stages = 0;
+    p.debug = g_debug;
     p.status = st->status_dev;
+    p.stats = st->stats_dev;
     const Plan& pl = it->second;
 #define TFP4_GO(KINDV)                                                          \
     switch (bn) {                                                               \
         case 32: return launch<KINDV, 32>(st, pl, p, 0, stream);                \
         case 64: return launch<KINDV, 64>(st, pl, p, 1, stream);                \
         case 128: return launch<KINDV, 128>(st, pl, p, 2, stream);              \
+        case 192: return launch<KINDV, 192>(st, pl, p, 4, stream);              \
         default: return launch<KINDV, 256>(st, pl, p, 3, stream);               \
     }
     if (kind == 0) { TFP4_GO(0) } else { TFP4_GO(1) }
@@ -584,7 +761,19 @@ int gemm_warm() {
     return ensure_device(&st);
 }
 
-void gemm_set_token_tile(int bn) { g_force_bn = (bn == 32 || bn == 64 || bn == 128 || bn == 256) ? bn : 0; }
+void gemm_set_debug(int d) { g_debug = d; }
+
+// per-CTA cycle counters of the MMA-issuing thread, written when debug bit 1024 is set:
+// {total, waiting for operands, waiting for the accumulator, issuing}
+int gemm_debug_stats(unsigned long long* out, int n_ctas) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState* st = nullptr;
+    if (ensure_device(&st)) return -1;
+    for (int i = 0; i < n_ctas * 4 && i < 256 * 4; ++i) out[i] = st->stats_host[i];
+    return 0;
+}
+
+void gemm_set_token_tile(int bn) { g_force_bn = (bn == 32 || bn == 64 || bn == 128 || bn == 192 || bn == 256) ? bn : 0; }
 
 int gemm_status_word() {
     std::lock_guard<std::mutex> lk(g_mu);

@@ -169,6 +169,7 @@ __device__ __forceinline__ uint32_t ue8m0_nearest(float v) {
     // nearest power of two, midpoint ties up; !(v > 0) -> 0; csrc/thor_fp4_core.cu:105-113
     if (!(v > 0.f)) return 0u;
     const uint32_t u = __float_as_uint(v);
+    if (u == 0x7f800000u) return 127u;   // the reference's frexpf(+inf) reports exponent 0 -> scale 1
     uint32_t b;
     if ((u >> 23) == 0u) b = (u >= 0x00600000u) ? 1u : 0u;   // sub-normal v
     else b = (u + 0x00400000u) >> 23;
