@@ -140,6 +140,52 @@ __device__ __forceinline__ void load8<__half>(const __half* p, float (&f)[8]) {
     }
 }
 
+// raw 8-element fetch (kept in registers while older rows are processed) and its widening
+template <typename T> struct Raw8 { uint4 a; };
+template <> struct Raw8<float> { uint4 a, b; };
+
+template <typename T>
+__device__ __forceinline__ Raw8<T> fetch8(const T* p) {
+    Raw8<T> r;
+    r.a = __ldg(reinterpret_cast<const uint4*>(p));
+    return r;
+}
+template <>
+__device__ __forceinline__ Raw8<float> fetch8<float>(const float* p) {
+    Raw8<float> r;
+    r.a = __ldg(reinterpret_cast<const uint4*>(p));
+    r.b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw8<T> zero8() {
+    Raw8<T> r;
+    r.a = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (sizeof(T) == 4) r.b = make_uint4(0u, 0u, 0u, 0u);
+    return r;
+}
+__device__ __forceinline__ void widen8(const Raw8<float>& r, float (&f)[8]) {
+    f[0] = __uint_as_float(r.a.x); f[1] = __uint_as_float(r.a.y); f[2] = __uint_as_float(r.a.z); f[3] = __uint_as_float(r.a.w);
+    f[4] = __uint_as_float(r.b.x); f[5] = __uint_as_float(r.b.y); f[6] = __uint_as_float(r.b.z); f[7] = __uint_as_float(r.b.w);
+}
+__device__ __forceinline__ void widen8(const Raw8<__nv_bfloat16>& r, float (&f)[8]) {
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void widen8(const Raw8<__half>& r, float (&f)[8]) {
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 ff = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = ff.x;
+        f[2 * i + 1] = ff.y;
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ T cast_out(float v);
 template <>

@@ -170,6 +170,11 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 // shared-memory matrix descriptor, K-major operand tile whose rows are one
 // 128-byte swizzle span: 8-row groups 1024 bytes apart, SWIZZLE_128B, version 1
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
@@ -381,14 +386,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const int n_mma = (kb == k_blocks - 1) ? p.last_atoms : 4;
                 const uint32_t sfw_c = tmem_base + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
                 const uint32_t sfa_c = sfw_c + TMEM_SFA_OFF + sf_off;
-                {   // poll the next K block's barriers now; the result is consumed next iteration
-                    const uint32_t s_n = (s + 1 == STAGES) ? 0u : s + 1;
-                    const uint32_t ph_n = (s + 1 == STAGES) ? ph ^ 1u : ph;
-                    if (!(p.debug & 32)) {
-                        peek_full = mbar_test_wait(full0 + 8 * s_n, ph_n);
-                        peek_sf = mbar_test_wait(smem_u32(&sffull_bar[slot ^ 1u]), ((it + 1) >> 1) & 1u);
-                    }
-                }
+                const uint32_t s_n = (s + 1 == STAGES) ? 0u : s + 1;
+                const uint32_t ph_n = (s + 1 == STAGES) ? ph ^ 1u : ph;
+                peek_full = false;
+                peek_sf = false;
                 if (prof) c2 = clock64();
                 const uint64_t adesc0 = desc_sw128(w_base + s * C::W_BYTES);
                 const uint64_t bdesc0 = desc_sw128(a_base + s * C::A_BYTES);
@@ -407,8 +408,20 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                 sfa_t = sfa_c | ((uint32_t)j << 30);
                             }
                             // advancing K by 64 (or 32) elements = 32 bytes inside the swizzle span
-                            tc_mma_if<KIND>(on, d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t,
-                                            (kb > 0 || j > 0) ? 1u : 0u);
+                            if (p.debug & 64) {
+                                if (elect_one()) tc_mma<KIND>(d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t, (kb > 0 || j > 0) ? 1u : 0u);
+                            } else {
+                                tc_mma_if<KIND>(on, d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t,
+                                                (kb > 0 || j > 0) ? 1u : 0u);
+                            }
+                        }
+                        if (j == 2 && !(p.debug & 32)) {
+                            // issuing an MMA returns only when the pipe takes it, i.e. while its predecessor
+                            // still runs: poll the next K block's barriers in that shadow (non-blocking),
+                            // so that nothing but the commit sits between this block's last MMA and the
+                            // next block's first
+                            peek_full = mbar_test_wait(full0 + 8 * s_n, ph_n);
+                            peek_sf = mbar_test_wait(smem_u32(&sffull_bar[slot ^ 1u]), ((it + 1) >> 1) & 1u);
                         }
                     }
                 }

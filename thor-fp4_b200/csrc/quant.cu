@@ -64,14 +64,19 @@ __device__ __forceinline__ float fma_pz(float a, float b) {  // a*b + (+0): maps
     return d;
 }
 
-// MODE 0: EXACT16 (16-bit input, ts == 1); 1: BRACKET; 2: LITERAL (always divide)
-template <typename T, int MODE>
+// MODE 0: EXACT16 (16-bit input, ts == 1); 1: BRACKET; 2: LITERAL (always divide);
+// 3: BRACKET without the tiny-input check (16-bit input and ts <= 128: the smallest non-zero
+// input, 2^-133, divided by the largest ds, 448 * 128, stays far above the 2^-150 underflow bound).
+// ROWS: rows per CTA, 128 (whole scale atoms) or 64 (half atoms; finer tiles for small grids).
+template <typename T, int MODE, int ROWS>
 __global__ void __launch_bounds__(QT_THREADS)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
     __shared__ __align__(16) uint8_t s_sf[4 * 512];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS;
+    const int64_t r0 = (int64_t)blockIdx.y * ROWS;
+    const int ra = (int)(r0 & 127);                    // first row of this CTA inside its scale atom
+    constexpr int UNROLL = (MODE == 0) ? 4 : 2;        // rows in flight per warp
     const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
     const int64_t col = c0 + lane * 8;
     const bool col_ok = col < K;
@@ -80,24 +85,25 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
     __syncthreads();
 
-    // warp w handles tile rows w, w+8, ..., w+120
-#pragma unroll 1
-    for (int it = 0; it < QT_ROWS / 8; it += QT_UNROLL) {
-        float f[QT_UNROLL][8];
-        bool live[QT_UNROLL];
+    // warp w handles tile rows w, w+8, ..., w+120, UNROLL rows per step; the raw loads of
+    // the next step are issued before the current step is processed (loads always in flight)
+    auto fetch_rows = [&](int it, Raw8<T> (&dst)[UNROLL]) {
 #pragma unroll
-        for (int u = 0; u < QT_UNROLL; ++u) {
+        for (int u = 0; u < UNROLL; ++u) {
             const int64_t r = r0 + warp + 8 * (it + u);
-            live[u] = col_ok && r < R;
-            if (live[u]) {
-                load8<T>(x + r * K + col, f[u]);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) f[u][i] = 0.f;
-            }
+            dst[u] = (col_ok && r < R) ? fetch8<T>(x + r * K + col) : zero8<T>();
         }
+    };
+    Raw8<T> cur[UNROLL], nxt[UNROLL];
+    fetch_rows(0, cur);
+#pragma unroll 1
+    for (int it = 0; it < ROWS / 8; it += UNROLL) {
+        if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, nxt);
+        float f[UNROLL][8];
 #pragma unroll
-        for (int u = 0; u < QT_UNROLL; ++u) {
+        for (int u = 0; u < UNROLL; ++u) widen8(cur[u], f[u]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
             const int rl = warp + 8 * (it + u);
             const int64_t r = r0 + rl;
             uint32_t codes = 0;
@@ -107,13 +113,13 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                 for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[u][i]));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                 float pre = amax * (1.0f / 6.0f);
-                if (MODE != 0) pre = __fdiv_rn(pre, ts);
+                if (MODE != 0) pre = __fdiv_rn(pre, ts);   // (amax * (1/6)) / ts, the reference's operand order
                 const uint32_t sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
                 const float sf = e4m3_to_f32(sc);
                 const float ds = (MODE != 0) ? sf * ts : sf;
                 if ((lane & 1) == 0 && col_ok) {
                     const int sl = lane >> 1;   // scale column inside the tile, 0..15
-                    s_sf[(sl >> 2) * 512 + 16 * (rl & 31) + 4 * (rl >> 5) + (sl & 3)] = (uint8_t)sc;
+                    s_sf[(sl >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (sl & 3)] = (uint8_t)sc;
                 }
                 if (MODE == 0) {
                     const float rb = __frcp_rn(ds) * 1.000000476837158203125f;   // * (1 + 2^-21)
@@ -121,7 +127,7 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
 #pragma unroll
                     for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
                     codes = pack_codes_rne(y);
-                } else if (MODE == 1) {
+                } else if (MODE == 1 || MODE == 3) {
                     const float rr = __frcp_rn(ds);
                     const float r_hi = rr * 1.00000095367431640625f;   // 1 + 2^-20
                     const float r_lo = rr * 0.99999904632568359375f;   // 1 - 2^-20
@@ -132,7 +138,7 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                         yh[i] = fma_pz(f[u][i], r_hi);
                         yl[i] = fma_pz(f[u][i], r_lo);
                         // 0 < |x| < 2^-100 (bits 0x0d800000): quotient may underflow
-                        tiny |= ((__float_as_uint(f[u][i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
+                        if (MODE == 1) tiny |= ((__float_as_uint(f[u][i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
                     }
                     codes = pack_codes_rne(yh);
                     const uint32_t cl = pack_codes_rne(yl);
@@ -144,17 +150,24 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
             if (col_ok && r < Rpad)
                 *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
         }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) cur[u] = nxt[u];
     }
     __syncthreads();
-    // whole atoms out: 512 contiguous bytes each
-    const int64_t D = K >> 6;                          // atoms per row tile
+    // scale bytes out: whole 512-byte atoms (ROWS == 128) or this CTA's half of each atom
+    const int64_t D = K >> 6;                          // atoms per 128-row tile
     const int64_t d0 = c0 >> 6;
     const int n_atoms = (int)((K - c0 >= QT_COLS) ? 4 : ((K - c0) >> 6));
-    const int atom = threadIdx.x >> 6;                 // 64 threads x 8 bytes per atom
-    if (atom < n_atoms) {
-        uint2 v = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
-        uint8_t* dst = sblk + ((int64_t)blockIdx.y * D + d0 + atom) * 512 + (threadIdx.x & 63) * 8;
-        *reinterpret_cast<uint2*>(dst) = v;
+    uint8_t* tile = sblk + ((r0 >> 7) * D + d0) * 512;
+    if (ROWS == 128) {
+        const int atom = threadIdx.x >> 6;             // 64 threads x 8 bytes per atom
+        if (atom < n_atoms)
+            *reinterpret_cast<uint2*>(tile + threadIdx.x * 8) = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
+    } else if (threadIdx.x < 128) {
+        // rows ra..ra+63 own bytes [8h, 8h+8) of every 16-byte lane row, h = ra / 64
+        const int atom = threadIdx.x >> 5, off = atom * 512 + 16 * (threadIdx.x & 31) + (ra >> 3);
+        if (atom < n_atoms)
+            *reinterpret_cast<uint2*>(tile + off) = *reinterpret_cast<const uint2*>(s_sf + off);
     }
 }
 
@@ -340,21 +353,34 @@ mx8_mul_kernel(const uint8_t* __restrict__ ap, const uint8_t* __restrict__ as,
     }
 }
 
-template <typename T>
-int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* packed,
-                       uint8_t* sblk, cudaStream_t stream) {
-    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)((R + QT_ROWS - 1) / QT_ROWS));
+template <typename T, int ROWS>
+int launch_quant_nvfp4_rows(const T* xp, int64_t R, int64_t K, float ts, uint8_t* packed, uint8_t* sblk,
+                            cudaStream_t stream) {
+    // the grid covers the padded rows so that the rows past R of the last 128-row tile get their zeros
+    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)(pad128(R) / ROWS));
     const bool ts_sane = (ts >= 0x1p-100f) && (ts <= 0x1p30f);   // false for NaN too
-    const T* xp = static_cast<const T*>(x);
     if (!ts_sane) {
-        quant_nvfp4_kernel<T, 2><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        quant_nvfp4_kernel<T, 2, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
     } else if (sizeof(T) == 2 && ts == 1.0f) {
-        quant_nvfp4_kernel<T, 0><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        quant_nvfp4_kernel<T, 0, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+    } else if (sizeof(T) == 2 && ts <= 128.0f) {
+        quant_nvfp4_kernel<T, 3, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
     } else {
-        quant_nvfp4_kernel<T, 1><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        quant_nvfp4_kernel<T, 1, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
     }
     TFP4_CK(cudaGetLastError());
     return TFP4_OK;
+}
+
+template <typename T>
+int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* packed,
+                       uint8_t* sblk, cudaStream_t stream) {
+    // 128-row tiles (whole scale atoms) measured faster than 64-row ones at every benchmarked size;
+    // the half-atom variant is kept for grids that would otherwise leave most SMs idle
+    const int64_t tiles128 = ((K + QT_COLS - 1) / QT_COLS) * (pad128(R) / 128);
+    const T* xp = static_cast<const T*>(x);
+    if (tiles128 < 148) return launch_quant_nvfp4_rows<T, 64>(xp, R, K, ts, packed, sblk, stream);
+    return launch_quant_nvfp4_rows<T, 128>(xp, R, K, ts, packed, sblk, stream);
 }
 
 template <typename T>
