@@ -40,7 +40,8 @@ def _fro(got, ref):
 @pytest.mark.parametrize("shape", [(1, 128, 64), (3, 136, 192), (17, 512, 1024), (128, 128, 256),
                                    (255, 384, 832), (300, 264, 2048), (512, 1024, 4096)])
 @pytest.mark.parametrize("bn", [0, 32, 64, 128, 192, 256])
-def test_gemm_matches_oracle_f32(shape, bn):
+@pytest.mark.parametrize("pair", [0, 1])
+def test_gemm_matches_oracle_f32(shape, bn, pair):
     import thor_fp4
     from thor_fp4 import _ext
     M, N, K = shape
@@ -48,11 +49,13 @@ def test_gemm_matches_oracle_f32(shape, bn):
     a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
     b = thor_fp4.NVFP4Tensor.from_float(w, None)
     _ext.core().tfp4_set_token_tile(bn)
+    _ext.core().tfp4_set_pair_mode(pair)
     try:
         out = a.matmul_t(b, out_dtype="f32")
         torch.cuda.synchronize()
     finally:
         _ext.core().tfp4_set_token_tile(0)
+        _ext.core().tfp4_set_pair_mode(-1)
     assert _ext.status() == 0
     assert _fro(out.cpu().numpy(), _oracle_out(a, b)) < TOL
 

@@ -16,6 +16,7 @@ int gemm_block_scaled(int, const void*, const void*, const void*, const void*, f
                       int64_t, int64_t, int64_t, int, cudaStream_t);
 void gemm_set_token_tile(int);
 void gemm_set_debug(int);
+void gemm_set_pair_mode(int);
 int gemm_debug_stats(unsigned long long*, int);
 int gemm_status_word();
 void gemm_clear_status();
@@ -111,6 +112,7 @@ void tfp4_clear_status(void) { tfp4::gemm_clear_status(); }
 void tfp4_plan_stats(uint64_t* hits, uint64_t* misses) { tfp4::gemm_plan_stats(hits, misses); }
 void tfp4_set_token_tile(int bn) { tfp4::gemm_set_token_tile(bn); }
 void tfp4_set_debug(int bits) { tfp4::gemm_set_debug(bits); }
+void tfp4_set_pair_mode(int mode) { tfp4::gemm_set_pair_mode(mode); }
 int tfp4_debug_stats(unsigned long long* out, int n_ctas) { return tfp4::gemm_debug_stats(out, n_ctas); }
 
 }  // extern "C"

@@ -104,8 +104,25 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// bounded wait: false if the abort flag is up or the time limit passed
+// bounded wait: false if the abort flag is up or the time limit passed.  Polls with the
+// non-blocking test_wait: try_wait parks the thread and wakes it late, which costs more than the
+// issue slots of the handful of waiting warps.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_CYCLES) {
+                *abort_flag = code;
+                return false;
+            }
+        }
+    }
+}
+// the same, parking between polls (for warps that wait long and should not take issue slots)
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
@@ -186,20 +203,94 @@ __device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3fffu) | (8ull << 32) | (1ull << 46);
 }
 
+// Epilogue of one tile, run by the four epilogue warps (128 threads) of a CTA.  The accumulator
+// holds output feature n on lane n and token m in column m, the transpose of the row-major
+// output; 32-token chunks are therefore turned around in shared memory ([token][feature],
+// two 16 KB buffers) and leave as 16-byte stores that cover whole output rows of the tile
+// (256 or 512 contiguous bytes per token row) instead of 2-byte stores 2*N bytes apart.
+constexpr int EPI_STAGE_BYTES = 2 * 16384;
+template <int BN>
+__device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t tmem_acc, int ew, int lane,
+                                           int64_t n_base, int64_t m0, uint8_t* stage) {
+    const int64_t n = n_base + ew * 32 + lane;
+    const float bias_n = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
+    const float alpha = p.alpha;
+    const int esize = (p.out_dtype == OUT_F32) ? 4 : 2;
+    const int row_bytes = BM * esize;                 // one token row of the tile
+    const int tid = ew * 32 + lane;
+    if (p.debug & 16) return;
+    const uint32_t t_lane = tmem_acc + ((uint32_t)(ew * 32) << 16);
+    const int per_row = row_bytes >> 4;               // 16-byte pieces per token row
+    const int pieces = 32 * per_row;
+    uint8_t* out = reinterpret_cast<uint8_t*>(p.out);
+    auto emit = [&](const uint32_t (&v)[32], int c0) {
+        if ((p.debug & 1) || m0 + c0 >= p.M) return;  // uniform across the four warps
+        uint8_t* buf = stage + ((c0 >> 5) & 1) * 16384;
+        uint8_t* mine = buf + tid * esize;
+        if (p.out_dtype == OUT_BF16) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                *reinterpret_cast<__nv_bfloat16*>(mine + i * row_bytes) = __float2bfloat16_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
+        } else if (p.out_dtype == OUT_F16) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                *reinterpret_cast<__half*>(mine + i * row_bytes) = __float2half_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                *reinterpret_cast<float*>(mine + i * row_bytes) = fmaf(alpha, __uint_as_float(v[i]), bias_n);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps only
+        for (int idx = tid; idx < pieces; idx += 128) {
+            const int row = idx / per_row, piece = idx - row * per_row;
+            const int64_t m = m0 + c0 + row;
+            const int64_t nn = n_base + (int64_t)piece * (16 / esize);
+            if (m < p.M && nn < p.N) {
+                const uint4 val = *reinterpret_cast<const uint4*>(buf + row * row_bytes + piece * 16);
+                *reinterpret_cast<uint4*>(out + (m * p.N + nn) * esize) = val;
+            }
+        }
+    };
+    // the tensor-memory read of the next 32 columns is in flight while the current ones are emitted
+    uint32_t va[32], vb[32];
+    tc_ld32(t_lane, va);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 64) {
+        tc_wait_ld();
+        if (c0 + 32 < BN) tc_ld32(t_lane + (uint32_t)(c0 + 32), vb);
+        emit(va, c0);
+        if (c0 + 32 < BN) {
+            tc_wait_ld();
+            if (c0 + 64 < BN) tc_ld32(t_lane + (uint32_t)(c0 + 64), va);
+            emit(vb, c0 + 32);
+        }
+    }
+}
+
 template <int KIND, int BN>
 struct Cfg {
     static constexpr int ACC_STAGES = (2 * BN + 2 * TMEM_SF_SLOT_COLS <= TMEM_COLS) ? 2 : 1;
-    static constexpr int SF_COL = ACC_STAGES * BN;                    // scale slots follow the accumulators
+    static constexpr int SF_COL = ACC_STAGES * BN;
+    // scale slots in tensor memory: as many as fit behind the accumulators (at most 4)
+    static constexpr int NSLOT_FIT = (TMEM_COLS - ACC_STAGES * BN) / TMEM_SF_SLOT_COLS;                    // scale slots follow the accumulators
     static constexpr int SF_TILES = (BN + 127) / 128;                 // 128-row scale tiles on the token side
     static constexpr int ATOMS = (KIND == 0) ? 4 : 1;                 // scale atoms per 128 rows per stage
     static constexpr int W_BYTES = BM * KB_BYTES;                     // 16 KB
+    // bytes the W tile load credits to its mbarrier: the 4-bit weights of the mixed kind are expanded
+    // to one byte per code in shared memory, but the copy is accounted at its packed global size
+    static constexpr int W_TX_BYTES = (KIND == 0) ? W_BYTES : W_BYTES / 2;
     static constexpr int A_BYTES = BN * KB_BYTES;
     static constexpr int SFW_BYTES = ATOMS * 512;
     static constexpr int SFA_BYTES = SF_TILES * ATOMS * 512;
     static constexpr int STAGE_BYTES = W_BYTES + A_BYTES + SFW_BYTES + SFA_BYTES;
-    static constexpr int SMEM_BUDGET = 227 * 1024 - 1024 - 256;      // alignment slack + barriers
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 1024 - 256 - EPI_STAGE_BYTES;   // alignment slack, barriers, epilogue staging
     static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
     static_assert(STAGES >= 3, "pipeline too shallow");
+    // scale slots in tensor memory: at most 4, and never more than pipeline stages (a loader
+    // waits on the stage barrier of the K block NSLOT iterations back; with more slots than stages
+    // that barrier could run two phases ahead of the waiter)
+    static constexpr int NSLOT = NSLOT_FIT < (STAGES < 4 ? STAGES : 4) ? NSLOT_FIT : (STAGES < 4 ? STAGES : 4);
+    static_assert(NSLOT >= 2, "need two scale slots");
     static_assert((W_BYTES % 1024) == 0 && (A_BYTES % 1024) == 0, "operand tiles must keep 1024-byte alignment");
     // instruction descriptor (block-scaled form): formats, N>>3 at bit 17, scale format at 23, M>>4 at 24
     static constexpr uint32_t IDESC =
@@ -277,8 +368,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     uint64_t* tfull_bar = bars + 2 * STAGES;           // [ACC_STAGES]
     uint64_t* tempty_bar = tfull_bar + C::ACC_STAGES;  // [ACC_STAGES]
     uint64_t* sffull_bar = tempty_bar + C::ACC_STAGES; // [2] scale slot filled (one arrival per loader warp)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sffull_bar + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sffull_bar + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* epi_stage = reinterpret_cast<uint8_t*>(bars) + 256;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -291,8 +383,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             mbar_init(smem_u32(&tfull_bar[a]), 1);
             mbar_init(smem_u32(&tempty_bar[a]), 4);   // one arrival per epilogue warp
         }
-        mbar_init(smem_u32(&sffull_bar[0]), 4);
-        mbar_init(smem_u32(&sffull_bar[1]), 4);
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sffull_bar[i]), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -312,43 +403,50 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0) {
+        // The whole warp walks the loop; the copies of one K block are issued by different lanes
+        // of the same instruction (lane 0: W tile, lane 1: token tile, lanes 2..: scale atoms), so a
+        // stage costs one issue slot per copy kind instead of five back-to-back issues by one thread.
+        {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
-                const int n0 = (int)(nt * BM), m0 = (int)(mt * BN);
                 const int64_t a_tile0 = (mt * BN) >> 7;     // first 128-row scale tile of this token tile
                 int a_tiles = 0;
 #pragma unroll
                 for (int t = 0; t < C::SF_TILES; ++t)
                     if (a_tile0 + t < p.rows_a_tiles) ++a_tiles;
-                const uint8_t* sfw_g = p.sfW + nt * p.sf_tile_stride;
-                const uint8_t* sfa_g = p.sfA + a_tile0 * p.sf_tile_stride;
+                // per-lane copy description
+                const CUtensorMap* my_map = (lane == 0) ? &tmW : &tmA;
+                const int my_y = (lane == 0) ? (int)(nt * BM) : (int)(mt * BN);
+                const uint32_t my_tile_dst = (lane == 0) ? smem_u32(sW) : smem_u32(sA);
+                const uint32_t my_tile_bytes = (lane == 0) ? (uint32_t)C::W_BYTES : (uint32_t)C::A_BYTES;
+                const uint8_t* my_sf_src = (lane == 2) ? p.sfW + nt * p.sf_tile_stride
+                                                       : p.sfA + (a_tile0 + (lane - 3)) * p.sf_tile_stride;
+                const uint32_t my_sf_dst = (lane == 2) ? smem_u32(sSFW) : smem_u32(sSFA) + (uint32_t)(lane - 3) * C::ATOMS * 512;
+                const uint32_t my_sf_stage = (lane == 2) ? (uint32_t)C::SFW_BYTES : (uint32_t)C::SFA_BYTES;
+                const bool sf_lane = lane >= 2 && lane < 3 + a_tiles;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * s;
                     if (p.debug & 8) {
-                        mbar_arrive(bar);
+                        if (lane == 0) mbar_arrive(bar);
                     } else {
                         const int atoms = (kb == k_blocks - 1) ? ((KIND == 0) ? p.last_atoms : 1) : C::ATOMS;
                         const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-                        mbar_expect_tx(bar, (uint32_t)(C::W_BYTES + C::A_BYTES) + sf_bytes * (uint32_t)(1 + a_tiles));
-                        tma_load_2d(smem_u32(sW) + s * C::W_BYTES, &tmW, kb * KB_BYTES, n0, bar);
-                        tma_load_2d(smem_u32(sA) + s * C::A_BYTES, &tmA, kb * KB_BYTES, m0, bar);
-                        const int64_t sf_k_off = (int64_t)kb * C::ATOMS * 512;
-                        bulk_load(smem_u32(sSFW) + s * C::SFW_BYTES, sfw_g + sf_k_off, sf_bytes, bar);
-#pragma unroll
-                        for (int t = 0; t < C::SF_TILES; ++t) {
-                            if (t < a_tiles)
-                                bulk_load(smem_u32(sSFA) + s * C::SFA_BYTES + t * C::ATOMS * 512,
-                                          sfa_g + t * p.sf_tile_stride + sf_k_off, sf_bytes, bar);
+                        if (lane == 0)
+                            mbar_expect_tx(bar, (uint32_t)(C::W_TX_BYTES + C::A_BYTES) + sf_bytes * (uint32_t)(1 + a_tiles));
+                        __syncwarp();
+                        if (lane < 2) {
+                            tma_load_2d(my_tile_dst + s * my_tile_bytes, my_map, kb * KB_BYTES, my_y, bar);
+                        } else if (sf_lane) {
+                            bulk_load(my_sf_dst + s * my_sf_stage, my_sf_src + (int64_t)kb * C::ATOMS * 512, sf_bytes, bar);
                         }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // let copies already issued land before the CTA's shared memory goes away
                 const long long t0 = clock64();
                 while (clock64() - t0 < 4000000ll) {}
@@ -378,10 +476,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (prof) c0 = clock64();
                 // the barriers of this K block were polled once while the previous block's MMAs were
                 // being issued; spin only if that poll failed
-                const uint32_t slot = it & 1u;
+                const uint32_t slot = it % C::NSLOT;
                 if (!(peek_full || mbar_wait(full0 + 8 * s, ph, abort_flag, 3))) { ok = false; break; }
                 if (prof) c1 = clock64();
-                if (!(peek_sf || mbar_wait(smem_u32(&sffull_bar[slot]), (it >> 1) & 1u, abort_flag, 5))) { ok = false; break; }
+                if (!(peek_sf || mbar_wait(smem_u32(&sffull_bar[slot]), (it / C::NSLOT) & 1u, abort_flag, 5))) { ok = false; break; }
                 tc_fence_after();
                 const int n_mma = (kb == k_blocks - 1) ? p.last_atoms : 4;
                 const uint32_t sfw_c = tmem_base + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
@@ -421,7 +519,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                             // so that nothing but the commit sits between this block's last MMA and the
                             // next block's first
                             peek_full = mbar_test_wait(full0 + 8 * s_n, ph_n);
-                            peek_sf = mbar_test_wait(smem_u32(&sffull_bar[slot ^ 1u]), ((it + 1) >> 1) & 1u);
+                            peek_sf = mbar_test_wait(smem_u32(&sffull_bar[(it + 1) % C::NSLOT]), ((it + 1) / C::NSLOT) & 1u);
                         }
                     }
                 }
@@ -452,39 +550,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
             const uint32_t acc = tcount % C::ACC_STAGES;
             const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
-            if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
+            if (!mbar_wait_parked(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
-            const int64_t n = nt * BM + ew * 32 + lane;
-            const int64_t m0 = mt * BN;
-            const bool n_ok = n < p.N;
-            const float bias_n = (p.bias != nullptr && n_ok) ? p.bias[n] : 0.f;
-            const float alpha = p.alpha;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (p.debug & 16) continue;
-                uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)(acc * BN + c0);
-                tc_ld32(taddr, v);
-                tc_wait_ld();
-                if (m0 + c0 < p.M && n_ok && !(p.debug & 1)) {
-                    if (p.out_dtype == OUT_BF16) {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (m0 + c0) * p.N + n;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (m0 + c0 + i < p.M) o[(int64_t)i * p.N] = __float2bfloat16_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
-                    } else if (p.out_dtype == OUT_F16) {
-                        __half* o = reinterpret_cast<__half*>(p.out) + (m0 + c0) * p.N + n;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (m0 + c0 + i < p.M) o[(int64_t)i * p.N] = __float2half_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
-                    } else {
-                        float* o = reinterpret_cast<float*>(p.out) + (m0 + c0) * p.N + n;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (m0 + c0 + i < p.M) o[(int64_t)i * p.N] = fmaf(alpha, __uint_as_float(v[i]), bias_n);
-                    }
-                }
-            }
+            drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
@@ -506,12 +574,12 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < k_blocks; ++kb) {
                 if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 6)) { ok = false; break; }
-                if (it >= 2) {
+                if (it >= C::NSLOT) {
                     if (!mbar_wait(empty0 + 8 * s2, ph2, abort_flag, 7)) { ok = false; break; }
                     if (++s2 == STAGES) { s2 = 0; ph2 ^= 1u; }
                 }
                 tc_fence_after();
-                const uint32_t slot = it & 1u;
+                const uint32_t slot = it % C::NSLOT;
                 const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
                 if (!(p.debug & 2)) {
                     uint32_t v[C::ATOMS * 4];
@@ -551,6 +619,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
 }
 
+#include "gemm_pair.cuh"
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -563,6 +633,7 @@ struct DeviceState {
     int* status_dev = nullptr;
     unsigned long long* stats_host = nullptr;
     unsigned long long* stats_dev = nullptr;
+    bool pair_attr_set[2][2] = {{false, false}, {false, false}};
     bool attr_set[2][5] = {{false, false, false, false, false}, {false, false, false, false, false}};
 };
 
@@ -636,7 +707,7 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     using C = Cfg<KIND, BN>;
     // every CTA allocates all 512 tensor-memory columns: the shared-memory request also keeps
     // the kernel at one CTA per SM
-    size_t smem = (size_t)C::STAGES * C::STAGE_BYTES + 256 + 1024;
+    size_t smem = (size_t)C::STAGES * C::STAGE_BYTES + 256 + EPI_STAGE_BYTES + 1024;
     if (smem < 120 * 1024) smem = 120 * 1024;
     if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
     p.stages = C::STAGES;
@@ -656,7 +727,42 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     return TFP4_OK;
 }
 
+template <int KIND, int BN>
+int launch_pair(DeviceState* st, const Plan& plan, GemmParams& p, int slot, cudaStream_t stream) {
+    using C = PairCfg<KIND, BN>;
+    size_t smem = (size_t)C::STAGES * C::STAGE_BYTES + 512 + EPI_STAGE_BYTES + 1024;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+    if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
+    p.stages = C::STAGES;
+    if (!st->pair_attr_set[KIND][slot]) {
+        TFP4_CK(cudaFuncSetAttribute(gemm_pair_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     st->max_smem));
+        st->pair_attr_set[KIND][slot] = true;
+    }
+    const int64_t tiles = p.m_tiles * ((p.n_tiles + 1) / 2);
+    const int64_t pairs = st->sm_count / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, BN>, plan.tmW, plan.tmA, p);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "thor_fp4_b200: pair GEMM launch failed: %s\n", cudaGetErrorString(e));
+        return TFP4_ERR_LAUNCH;
+    }
+    return TFP4_OK;
+}
+
 int g_force_bn = 0;
+int g_pair_mode = -1;   // 1: use the two-CTA kernel whenever the shape allows; otherwise never
 int g_debug = 0;
 
 }  // namespace
@@ -676,8 +782,9 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     }
     if (!packedA || !sblkA || !packedB || !sblkB || !out || out_dtype < 0 || out_dtype > 2 ||
         (reinterpret_cast<uintptr_t>(packedA) & 31) || (reinterpret_cast<uintptr_t>(packedB) & 31) ||
-        (reinterpret_cast<uintptr_t>(sblkA) & 15) || (reinterpret_cast<uintptr_t>(sblkB) & 15)) {
-        fprintf(stderr, "thor_fp4: gemm bad argument (code buffers 32-byte, scale buffers 16-byte aligned)\n");
+        (reinterpret_cast<uintptr_t>(sblkA) & 15) || (reinterpret_cast<uintptr_t>(sblkB) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & 15)) {
+        fprintf(stderr, "thor_fp4: gemm bad argument (code buffers 32-byte, scale buffers and output 16-byte aligned)\n");
         return TFP4_ERR_BAD_ARG;
     }
     std::lock_guard<std::mutex> lk(g_mu);
@@ -697,18 +804,15 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     if (bn == 0) {
         if (M <= 128) bn = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
         else if (M <= 192) bn = 192;
-        else if (M <= 256) bn = 256;
-        else {
-            // 192-token tiles leave room for two accumulators (the epilogue of one tile overlaps the
-            // main loop of the next); 256-token tiles do more work per MMA but drain serially.  The
-            // wider tile only pays when every CTA gets at most one tile.
-            const int64_t tiles256 = ((M + 255) / 256) * ((N + BM - 1) / BM);
-            bn = (tiles256 <= st->sm_count && (M % 256) == 0) ? 256 : 192;
-        }
+        else bn = 256;   // measured: the wider tile wins even though its accumulator is drained serially
     }
     int dev = 0;
     cudaGetDevice(&dev);
-    PlanKey key{packedA, packedB, M, N, K, kind, bn, dev};
+    // two-CTA kernel: needs at least one 256-row weight tile pair and a wide token tile
+    // (opt-in: cross-CTA barrier round trips currently keep it behind the single-CTA kernel)
+    const bool pair = g_pair_mode == 1 && (bn == 256 || bn == 192) && N >= 256 && st->sm_count >= 2;
+    const uint32_t box_a = pair ? (uint32_t)(bn / 2) : (uint32_t)bn;
+    PlanKey key{packedA, packedB, M, N, K, kind, pair ? -bn : bn, dev};
     auto it = g_plans.find(key);
     if (it == g_plans.end()) {
         ++g_plan_misses;
@@ -717,13 +821,13 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
         if (kind == 0) {
             rc = encode_map(&pl.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedB, (uint64_t)K / 2, rowsW, (uint64_t)K / 2, 128, BM);
             if (rc) return rc;
-            rc = encode_map(&pl.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedA, (uint64_t)K / 2, rowsA, (uint64_t)K / 2, 128, (uint32_t)bn);
+            rc = encode_map(&pl.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedA, (uint64_t)K / 2, rowsA, (uint64_t)K / 2, 128, box_a);
             if (rc) return rc;
         } else {
             // 4-bit weights, expanded by TMA to 16 codes per 16 bytes of shared memory
             rc = encode_map(&pl.tmW, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, packedB, (uint64_t)K, rowsW, (uint64_t)K / 2, 128, BM);
             if (rc) return rc;
-            rc = encode_map(&pl.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedA, (uint64_t)K, rowsA, (uint64_t)K, 128, (uint32_t)bn);
+            rc = encode_map(&pl.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, packedA, (uint64_t)K, rowsA, (uint64_t)K, 128, box_a);
             if (rc) return rc;
         }
         if (g_plans.size() > 4096) g_plans.clear();
@@ -754,6 +858,10 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     p.status = st->status_dev;
     p.stats = st->stats_dev;
     const Plan& pl = it->second;
+    if (pair) {
+        if (kind == 0) return bn == 256 ? launch_pair<0, 256>(st, pl, p, 0, stream) : launch_pair<0, 192>(st, pl, p, 1, stream);
+        return bn == 256 ? launch_pair<1, 256>(st, pl, p, 0, stream) : launch_pair<1, 192>(st, pl, p, 1, stream);
+    }
 #define TFP4_GO(KINDV)                                                          \
     switch (bn) {                                                               \
         case 32: return launch<KINDV, 32>(st, pl, p, 0, stream);                \
@@ -775,6 +883,7 @@ int gemm_warm() {
 }
 
 void gemm_set_debug(int d) { g_debug = d; }
+void gemm_set_pair_mode(int m) { g_pair_mode = m; }
 
 // per-CTA cycle counters of the MMA-issuing thread, written when debug bit 1024 is set:
 // {total, waiting for operands, waiting for the accumulator, issuing}

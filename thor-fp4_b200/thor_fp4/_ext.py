@@ -49,6 +49,9 @@ SIGNATURES = {
     "tfp4_clear_status": (None, []),
     "tfp4_plan_stats": (None, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "tfp4_set_token_tile": (None, [c_int]),
+    "tfp4_set_pair_mode": (None, [c_int]),
+    "tfp4_set_debug": (None, [c_int]),
+    "tfp4_debug_stats": (c_int, [ctypes.POINTER(ctypes.c_uint64), c_int]),
 }
 OPTIONAL_SIGNATURES = {
     "tfp4_swiglu_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
