@@ -117,6 +117,8 @@ void tfp4_set_token_tile(int bn);
  * for ablation timing (bit0 stores, bit1 scale copies, bit2 MMAs, bit3 loads, bit4 tensor-memory
  * reads; bit 1024 records per-CTA cycle counters read back with tfp4_debug_stats: 4 values per CTA). */
 void tfp4_set_pair_mode(int mode);
+/* K split of small-batch GEMMs: 0 automatic, 1 never, n = about n K ranges (test hook). */
+void tfp4_set_splits(int n);
 void tfp4_set_debug(int bits);
 int tfp4_debug_stats(unsigned long long* out, int n_ctas);
 

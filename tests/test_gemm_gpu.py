@@ -172,3 +172,32 @@ def test_mx8_gemm_matches_fake_quant(shape):
     y = lin(x)
     ref = thor_fp4.mx_fake_quant(x, "mxfp8") @ thor_fp4.mx_fake_quant(lin.weight.detach(), "mxfp4").t()
     assert rrms(y, ref) < 4e-3
+
+
+@gpu
+@pytest.mark.parametrize("shape", [(1, 256, 4096), (17, 512, 8192), (128, 384, 2048), (100, 136, 2304)])
+@pytest.mark.parametrize("splits", [0, 2, 4, 7])
+@pytest.mark.parametrize("od", ["f32", "bf16"])
+def test_gemm_split_k_matches_oracle(shape, splits, od):
+    """Small batches split K over otherwise idle SMs (f32 partial tiles + a reduction kernel)."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = shape
+    x, w = _operands(M, N, K, seed=K + M)
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    bias = torch.randn(N, device="cuda") * 0.01
+    out = torch.empty(M, N, dtype=_ext.OUT_TORCH[od], device="cuda")
+    _ext.core().tfp4_set_splits(splits)
+    try:
+        ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, od, bias=bias)
+        torch.cuda.synchronize()
+        again = out.clone()
+        ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, od, bias=bias)
+        torch.cuda.synchronize()
+    finally:
+        _ext.core().tfp4_set_splits(0)
+    assert _ext.status() == 0
+    assert torch.equal(out, again)          # fixed summation order
+    ref = _oracle_out(a, b, bias.cpu().numpy())
+    assert _fro(out.float().cpu().numpy(), ref) < (TOL if od == "f32" else 3e-3)

@@ -17,6 +17,7 @@ int gemm_block_scaled(int, const void*, const void*, const void*, const void*, f
 void gemm_set_token_tile(int);
 void gemm_set_debug(int);
 void gemm_set_pair_mode(int);
+void gemm_set_splits(int);
 int gemm_debug_stats(unsigned long long*, int);
 int gemm_status_word();
 void gemm_clear_status();
@@ -113,6 +114,7 @@ void tfp4_plan_stats(uint64_t* hits, uint64_t* misses) { tfp4::gemm_plan_stats(h
 void tfp4_set_token_tile(int bn) { tfp4::gemm_set_token_tile(bn); }
 void tfp4_set_debug(int bits) { tfp4::gemm_set_debug(bits); }
 void tfp4_set_pair_mode(int mode) { tfp4::gemm_set_pair_mode(mode); }
+void tfp4_set_splits(int n) { tfp4::gemm_set_splits(n); }
 int tfp4_debug_stats(unsigned long long* out, int n_ctas) { return tfp4::gemm_debug_stats(out, n_ctas); }
 
 }  // extern "C"

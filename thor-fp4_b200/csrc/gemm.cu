@@ -63,6 +63,9 @@ struct GemmParams {
     int32_t k_blocks;
     int32_t last_atoms;      // NVFP4: 64-element MMAs in the last K block (1..4); MX: 32-element ones
     int32_t stages;
+    int32_t splits;          // K is cut into this many ranges; > 1: partial sums go to `ws` (f32, [split][M][N])
+    int32_t kb_per_split;
+    float* ws;
     int32_t debug;           // test hook: bit0 no stores, bit1 no scale copies, bit2 no MMA, bit3 no loads, bit4 no tmem loads
     int* status;             // host-visible status word (0 = ok)
     unsigned long long* stats;   // host-visible per-CTA cycle counters (debug bit 1024), 4 per CTA
@@ -211,27 +214,28 @@ __device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
 constexpr int EPI_STAGE_BYTES = 2 * 16384;
 template <int BN>
 __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t tmem_acc, int ew, int lane,
-                                           int64_t n_base, int64_t m0, uint8_t* stage) {
+                                           int64_t n_base, int64_t m0, uint8_t* stage,
+                                           void* out_ptr, int out_dtype, const float* bias) {
     const int64_t n = n_base + ew * 32 + lane;
-    const float bias_n = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.f;
+    const float bias_n = (bias != nullptr && n < p.N) ? bias[n] : 0.f;
     const float alpha = p.alpha;
-    const int esize = (p.out_dtype == OUT_F32) ? 4 : 2;
+    const int esize = (out_dtype == OUT_F32) ? 4 : 2;
     const int row_bytes = BM * esize;                 // one token row of the tile
     const int tid = ew * 32 + lane;
     if (p.debug & 16) return;
     const uint32_t t_lane = tmem_acc + ((uint32_t)(ew * 32) << 16);
     const int per_row = row_bytes >> 4;               // 16-byte pieces per token row
     const int pieces = 32 * per_row;
-    uint8_t* out = reinterpret_cast<uint8_t*>(p.out);
+    uint8_t* out = reinterpret_cast<uint8_t*>(out_ptr);
     auto emit = [&](const uint32_t (&v)[32], int c0) {
         if ((p.debug & 1) || m0 + c0 >= p.M) return;  // uniform across the four warps
         uint8_t* buf = stage + ((c0 >> 5) & 1) * 16384;
         uint8_t* mine = buf + tid * esize;
-        if (p.out_dtype == OUT_BF16) {
+        if (out_dtype == OUT_BF16) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
                 *reinterpret_cast<__nv_bfloat16*>(mine + i * row_bytes) = __float2bfloat16_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
-        } else if (p.out_dtype == OUT_F16) {
+        } else if (out_dtype == OUT_F16) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
                 *reinterpret_cast<__half*>(mine + i * row_bytes) = __float2half_rn(fmaf(alpha, __uint_as_float(v[i]), bias_n));
@@ -397,7 +401,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t total_tiles = p.m_tiles * p.n_tiles;
+    // work item = (weight tile, token tile, K range); the K range is the fastest index
+    const int64_t total_tiles = p.m_tiles * p.n_tiles * p.splits;
     const int k_blocks = p.k_blocks;
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
 
@@ -410,7 +415,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+                const int64_t sp = tile % p.splits, tl = tile / p.splits;
+                const int64_t nt = tl / p.m_tiles, mt = tl - nt * p.m_tiles;
+                const int kb0 = (int)sp * p.kb_per_split;
+                const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
                 const int64_t a_tile0 = (mt * BN) >> 7;     // first 128-row scale tile of this token tile
                 int a_tiles = 0;
 #pragma unroll
@@ -426,7 +434,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const uint32_t my_sf_dst = (lane == 2) ? smem_u32(sSFW) : smem_u32(sSFA) + (uint32_t)(lane - 3) * C::ATOMS * 512;
                 const uint32_t my_sf_stage = (lane == 2) ? (uint32_t)C::SFW_BYTES : (uint32_t)C::SFA_BYTES;
                 const bool sf_lane = lane >= 2 && lane < 3 + a_tiles;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * s;
                     if (p.debug & 8) {
@@ -470,8 +478,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t d_tmem = tmem_base + acc * BN;
             // token tiles of 192 start at row 0 or 64 of a 128-row scale atom: rows 32c..32c+31 of
             // an atom sit in scale column c, so the token-side scale address moves by 0 or 2 columns
-            const uint32_t sf_off = (BN == 192) ? (uint32_t)((((tile % p.m_tiles) * BN) & 127) >> 5) : 0u;
-            for (int kb = 0; kb < k_blocks; ++kb) {
+            const uint32_t sf_off = (BN == 192) ? (uint32_t)(((((tile / p.splits) % p.m_tiles) * BN) & 127) >> 5) : 0u;
+            const int kb0 = (int)(tile % p.splits) * p.kb_per_split;
+            const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+            for (int kb = kb0; kb < kb1; ++kb) {
                 long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
                 if (prof) c0 = clock64();
                 // the barriers of this K block were polled once while the previous block's MMAs were
@@ -507,10 +517,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                             }
                             // advancing K by 64 (or 32) elements = 32 bytes inside the swizzle span
                             if (p.debug & 64) {
-                                if (elect_one()) tc_mma<KIND>(d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t, (kb > 0 || j > 0) ? 1u : 0u);
+                                if (elect_one()) tc_mma<KIND>(d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t, (kb > kb0 || j > 0) ? 1u : 0u);
                             } else {
                                 tc_mma_if<KIND>(on, d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t,
-                                                (kb > 0 || j > 0) ? 1u : 0u);
+                                                (kb > kb0 || j > 0) ? 1u : 0u);
                             }
                         }
                         if (j == 2 && !(p.debug & 32)) {
@@ -547,12 +557,16 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         uint32_t tcount = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-            const int64_t nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+            const int64_t sp = tile % p.splits, tl = tile / p.splits;
+            const int64_t nt = tl / p.m_tiles, mt = tl - nt * p.m_tiles;
             const uint32_t acc = tcount % C::ACC_STAGES;
             const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
             if (!mbar_wait_parked(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
-            drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage);
+            if (p.splits > 1)   // partial sum of this K range, f32, bias and cast happen in the reduction
+                drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.ws + sp * p.M * p.N, OUT_F32, nullptr);
+            else
+                drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.out, p.out_dtype, p.bias);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
@@ -572,7 +586,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         bool ok = true;
         const uint32_t sfw_base = smem_u32(sSFW), sfa_base = smem_u32(sSFA);
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
+            const int kb0 = (int)(tile % p.splits) * p.kb_per_split;
+            const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+            for (int kb = kb0; kb < kb1; ++kb) {
                 if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 6)) { ok = false; break; }
                 if (it >= C::NSLOT) {
                     if (!mbar_wait(empty0 + 8 * s2, ph2, abort_flag, 7)) { ok = false; break; }
@@ -619,6 +635,35 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
 }
 
+// Sum of the split-K partial tiles: out[m, n] = cast( sum_s ws[s][m][n] + bias[n] ), four elements
+// per thread, splits added in a fixed order (deterministic).
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t MN, int64_t N,
+                     const float* __restrict__ bias, void* __restrict__ out, int out_dtype) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= MN) return;
+    float4 acc = *reinterpret_cast<const float4*>(ws + i);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(ws + (int64_t)s * MN + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias != nullptr) {
+        const float4 b = *reinterpret_cast<const float4*>(bias + (i % N));
+        acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+    }
+    if (out_dtype == OUT_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + i) = acc;
+    } else if (out_dtype == OUT_BF16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + i) = v;
+    } else {
+        __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+        uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(out) + i) = v;
+    }
+}
+
 #include "gemm_pair.cuh"
 
 // ------------------------------------------------------------------ host side
@@ -633,6 +678,8 @@ struct DeviceState {
     int* status_dev = nullptr;
     unsigned long long* stats_host = nullptr;
     unsigned long long* stats_dev = nullptr;
+    float* ws = nullptr;          // split-K partial sums, grown on demand
+    size_t ws_bytes = 0;
     bool pair_attr_set[2][2] = {{false, false}, {false, false}};
     bool attr_set[2][5] = {{false, false, false, false, false}, {false, false, false, false, false}};
 };
@@ -666,7 +713,9 @@ int ensure_driver() {
     return TFP4_OK;
 }
 
-int ensure_device(DeviceState** out) {
+// per-device state; the pinned status / counter words are created only when `with_pinned`
+// (a caller that brings its own scratch never reaches an allocating call)
+int ensure_device(DeviceState** out, bool with_pinned = true) {
     int dev = 0;
     TFP4_CK(cudaGetDevice(&dev));
     auto it = g_dev.find(dev);
@@ -674,14 +723,17 @@ int ensure_device(DeviceState** out) {
         DeviceState st;
         TFP4_CK(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
         TFP4_CK(cudaDeviceGetAttribute(&st.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        it = g_dev.emplace(dev, st).first;
+    }
+    DeviceState& st = it->second;
+    if (with_pinned && st.status_host == nullptr) {
         TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), sizeof(int), cudaHostAllocMapped));
         *st.status_host = 0;
         TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0));
         TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.stats_host), 256 * 4 * sizeof(unsigned long long), cudaHostAllocMapped));
         TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.stats_dev), st.stats_host, 0));
-        it = g_dev.emplace(dev, st).first;
     }
-    *out = &it->second;
+    *out = &st;
     return TFP4_OK;
 }
 
@@ -717,8 +769,14 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
         st->attr_set[KIND][bn_slot] = true;
     }
     const int64_t tiles = p.m_tiles * p.n_tiles;
-    const unsigned grid = (unsigned)(tiles < st->sm_count ? tiles : st->sm_count);
-    gemm_bs_kernel<KIND, BN><<<grid, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
+    const int64_t tiles_all = tiles * p.splits;
+    const unsigned grid_all = (unsigned)(tiles_all < st->sm_count ? tiles_all : st->sm_count);
+    gemm_bs_kernel<KIND, BN><<<grid_all, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
+    if (p.splits > 1) {
+        const int64_t MN = p.M * p.N;
+        splitk_reduce_kernel<<<(unsigned)((MN / 4 + 255) / 256), 256, 0, stream>>>(p.ws, p.splits, MN, p.N, p.bias, p.out,
+                                                                                   p.out_dtype);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: GEMM launch failed: %s\n", cudaGetErrorString(e));
@@ -761,16 +819,25 @@ int launch_pair(DeviceState* st, const Plan& plan, GemmParams& p, int slot, cuda
     return TFP4_OK;
 }
 
+// scratch supplied by the caller of gemm_block_scaled_ws instead of the library's own
+struct ExtScratch {
+    int* status;                 // device-visible status word
+    unsigned long long* stats;   // 256 x 4 counters (may be null)
+    float* ws;                   // split-K partial sums
+    size_t ws_bytes;
+};
+
 int g_force_bn = 0;
+int g_force_splits = 0;    // 0 automatic, 1 never split K, n split into (about) n ranges
 int g_pair_mode = -1;   // 1: use the two-CTA kernel whenever the shape allows; otherwise never
 int g_debug = 0;
 
 }  // namespace
 
 // kind 0: NVFP4 x NVFP4 ; kind 1: MXFP8 activations x MXFP4 weights
-int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const void* packedB,
-                      const void* sblkB, float alpha, const float* bias, void* out, int64_t M, int64_t N,
-                      int64_t K, int out_dtype, cudaStream_t stream) {
+int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const void* packedB,
+                         const void* sblkB, float alpha, const float* bias, void* out, int64_t M, int64_t N,
+                         int64_t K, int out_dtype, cudaStream_t stream, const ExtScratch* ext) {
     if (M < 1 || N < 8 || (N % 8) != 0) {
         fprintf(stderr, "thor_fp4: gemm needs M >= 1, N >= 8, N %% 8 == 0 (got M=%ld N=%ld)\n", (long)M, (long)N);
         return TFP4_ERR_BAD_M;
@@ -791,9 +858,9 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     int rc = ensure_driver();
     if (rc) return rc;
     DeviceState* st = nullptr;
-    rc = ensure_device(&st);
+    rc = ensure_device(&st, ext == nullptr);
     if (rc) return rc;
-    if (*st->status_host != 0) {
+    if (ext == nullptr && *st->status_host != 0) {
         fprintf(stderr, "thor_fp4_b200: an earlier GEMM gave up waiting on the device (code %d)\n", *st->status_host);
         return TFP4_ERR_DEVICE_TIMEOUT;
     }
@@ -854,9 +921,44 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     const int64_t rem = K - (int64_t)(p.k_blocks - 1) * kb_elems;
     p.last_atoms = (int32_t)(kind == 0 ? rem / 64 : rem / 32);
     p.stages = 0;
+    // split K when the output tiles alone would leave most SMs idle (small batches): each K range
+    // becomes a work item writing an f32 partial tile, summed by a second kernel
+    p.splits = 1;
+    p.kb_per_split = p.k_blocks;
+    p.ws = nullptr;
+    {
+        const int64_t tiles = p.m_tiles * p.n_tiles;
+        int want = g_force_splits;
+        if (want == 0) want = (!pair && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
+        if (want > p.k_blocks / 4) want = p.k_blocks / 4;
+        if (want > 16) want = 16;
+        if (want > 1 && !pair) {
+            p.kb_per_split = (p.k_blocks + want - 1) / want;
+            p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+        }
+        if (p.splits > 1) {
+            const size_t need = (size_t)p.splits * (size_t)M * (size_t)N * sizeof(float);
+            if (ext != nullptr) {
+                if (need > ext->ws_bytes) {
+                    fprintf(stderr, "thor_fp4: split-K needs %zu bytes of scratch, %zu available\n", need, ext->ws_bytes);
+                    return TFP4_ERR_BAD_ARG;
+                }
+                p.ws = ext->ws;
+            } else {
+                if (st->ws_bytes < need) {      // like the reference's scratch: grows on first / larger shapes
+                    if (st->ws) cudaFree(st->ws);
+                    st->ws = nullptr;
+                    st->ws_bytes = 0;
+                    TFP4_CK(cudaMalloc(reinterpret_cast<void**>(&st->ws), need));
+                    st->ws_bytes = need;
+                }
+                p.ws = st->ws;
+            }
+        }
+    }
     p.debug = g_debug;
-    p.status = st->status_dev;
-    p.stats = st->stats_dev;
+    p.status = ext ? ext->status : st->status_dev;
+    p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
     if (pair) {
         if (kind == 0) return bn == 256 ? launch_pair<0, 256>(st, pl, p, 0, stream) : launch_pair<0, 192>(st, pl, p, 1, stream);
@@ -873,6 +975,15 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
     if (kind == 0) { TFP4_GO(0) } else { TFP4_GO(1) }
 #undef TFP4_GO
 }
+
+int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const void* packedB,
+                      const void* sblkB, float alpha, const float* bias, void* out, int64_t M, int64_t N,
+                      int64_t K, int out_dtype, cudaStream_t stream) {
+    return gemm_block_scaled_ws(kind, packedA, sblkA, packedB, sblkB, alpha, bias, out, M, N, K, out_dtype, stream,
+                                nullptr);
+}
+
+void gemm_set_splits(int n) { g_force_splits = n < 0 ? 0 : n; }
 
 int gemm_warm() {
     std::lock_guard<std::mutex> lk(g_mu);

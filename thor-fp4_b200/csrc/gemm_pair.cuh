@@ -317,7 +317,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
             if (!mbar_wait_parked(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
-            drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, (2 * np + rank) * BM, mt * BN, epi_stage);
+            drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, (2 * np + rank) * BM, mt * BN, epi_stage, p.out, p.out_dtype, p.bias);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * acc);

@@ -50,6 +50,7 @@ SIGNATURES = {
     "tfp4_plan_stats": (None, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "tfp4_set_token_tile": (None, [c_int]),
     "tfp4_set_pair_mode": (None, [c_int]),
+    "tfp4_set_splits": (None, [c_int]),
     "tfp4_set_debug": (None, [c_int]),
     "tfp4_debug_stats": (c_int, [ctypes.POINTER(ctypes.c_uint64), c_int]),
 }
