@@ -76,6 +76,22 @@ int tfp4_gemm_bias(const void* packedA, const void* sblkA, float tsA,
                    const float* bias, void* out, int64_t M, int64_t N, int64_t K,
                    int out_dtype, void* stream);
 
+/* No counterpart in the reference.  tfp4_gemm_bias for callers that must not allocate at call time
+ * (device memory fully pre-partitioned at start-up, a plug-in under a foreign allocator, a loop
+ * that cannot afford the device-wide synchronisation of an allocation or a free): the kernel's scratch - status word, counters, split-K partial sums - sits in a
+ * fixed 16 MiB array of device memory that every GPU loading the library holds until exit, so no
+ * cudaMalloc / cudaFree / cudaHostAlloc is ever called.  The first call on a device looks up the
+ * array's address: make it before any stream capture.  A shape whose partial sums exceed
+ * tfp4_gemm_noalloc_capacity() bytes is refused with -7 and a message.  Calls share the array, so calls
+ * that overlap on the GPU (different streams) race; the status word is sticky: read / reset it with
+ * tfp4_gemm_noalloc_status (blocking copy, not for hot paths). */
+int tfp4_gemm_noalloc(const void* packedA, const void* sblkA, float tsA,
+                      const void* packedB, const void* sblkB, float tsB,
+                      const float* bias, void* out, int64_t M, int64_t N, int64_t K,
+                      int out_dtype, void* stream);
+int tfp4_gemm_noalloc_status(int reset);
+size_t tfp4_gemm_noalloc_capacity(void);
+
 /* Replaces tfp4_gemv (csrc/thor_fp4_core.cu:796-840): exact activations (M <= 8)
  * against NVFP4 weights, FP32 accumulation; sgemvB from tfp4_scales_gemv. */
 int tfp4_gemv(const void* x, int64_t M, int64_t K, int in_dtype,

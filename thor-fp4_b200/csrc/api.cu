@@ -18,6 +18,10 @@ void gemm_set_token_tile(int);
 void gemm_set_debug(int);
 void gemm_set_pair_mode(int);
 void gemm_set_splits(int);
+int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
+                 int64_t, int, cudaStream_t);
+int gemm_noalloc_status(int);
+size_t gemm_noalloc_capacity();
 int gemm_debug_stats(unsigned long long*, int);
 int gemm_status_word();
 void gemm_clear_status();
@@ -107,6 +111,17 @@ int tfc4_gemm(int variant, const void* A, const void* SA, const void* B, const v
     return tfp4::gemm_block_scaled(kVariants[variant].kind, A, SA, B, SB, alpha, nullptr, D, M, N, K,
                                    tfp4::OUT_BF16, S(stream));
 }
+
+int tfp4_gemm_noalloc(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB,
+                      const float* bias, void* out, int64_t M, int64_t N, int64_t K, int out_dtype, void* stream) {
+    if ((K % 64) != 0) {
+        fprintf(stderr, "thor_fp4: K must be a multiple of 64 (got %ld)\n", (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    return tfp4::gemm_noalloc(pA, sA, pB, sB, tsA * tsB, bias, out, M, N, K, out_dtype, S(stream));
+}
+int tfp4_gemm_noalloc_status(int reset) { return tfp4::gemm_noalloc_status(reset); }
+size_t tfp4_gemm_noalloc_capacity(void) { return tfp4::gemm_noalloc_capacity(); }
 
 int tfp4_status(void) { return tfp4::gemm_status_word(); }
 void tfp4_clear_status(void) { tfp4::gemm_clear_status(); }

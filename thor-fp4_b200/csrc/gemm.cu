@@ -983,6 +983,76 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
                                 nullptr);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry.  Some hosts of this library may not allocate device or pinned memory at
+// call time: a serving process whose device memory was carved up completely at start-up, a plug-in
+// that runs under an allocator it does not own, or a latency-bound loop that cannot afford the
+// device-wide synchronisation an allocation or a free implies.  For them the GEMM's scratch - the
+// status word the kernel's bounded waits report to, the debug counters and the split-K partial
+// sums - lives in this fixed array of device memory instead of cudaHostAlloc / cudaMalloc
+// blocks.  Every GPU that loads the library carries the array until the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = 16u << 20;     // the stated maximum: 16 MiB in total
+constexpr size_t kNoAllocHeaderBytes = 16u << 10;      // status word at 0, counters at 256, then partial sums
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+std::mutex g_noalloc_mu;
+std::map<int, unsigned char*> g_noalloc_addr;          // device ordinal -> device address of the array
+
+// The array's name is only a host-side handle; the kernel needs its device address, looked up once
+// per device with that device current.
+int noalloc_scratch(unsigned char** out) {
+    int dev = 0;
+    TFP4_CK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    auto it = g_noalloc_addr.find(dev);
+    if (it == g_noalloc_addr.end()) {
+        unsigned char* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            fprintf(stderr, "thor_fp4_b200: cudaGetSymbolAddress(scratch) failed: %s\n", cudaGetErrorString(e));
+            return TFP4_ERR_CUDA;
+        }
+        it = g_noalloc_addr.emplace(dev, ptr).first;
+    }
+    *out = it->second;
+    return TFP4_OK;
+}
+}  // namespace
+
+// NVFP4 GEMM (+ optional bias) with all scratch in the fixed array above.  No cudaMalloc, cudaFree,
+// cudaHostAlloc or other allocating call is made.  The first call on a device looks the array's
+// address up (do it before any stream capture).  Split-K partial sums beyond the array's capacity
+// are refused with -7 and a message.  All calls share the array: calls that overlap on the GPU
+// (different streams) race on it; calls on one stream are safe.  The partial sums are fully
+// rewritten by every call and need no clearing; the status word starts at zero when the library is
+// loaded and stays set after a kernel gave up waiting (read / reset it with gemm_noalloc_status).
+int gemm_noalloc(const void* packedA, const void* sblkA, const void* packedB, const void* sblkB, float alpha,
+                 const float* bias, void* out, int64_t M, int64_t N, int64_t K, int out_dtype, cudaStream_t stream) {
+    unsigned char* base = nullptr;
+    int rc = noalloc_scratch(&base);
+    if (rc) return rc;
+    ExtScratch ext;
+    ext.status = reinterpret_cast<int*>(base);
+    ext.stats = reinterpret_cast<unsigned long long*>(base + 256);
+    ext.ws = reinterpret_cast<float*>(base + kNoAllocHeaderBytes);
+    ext.ws_bytes = kNoAllocScratchBytes - kNoAllocHeaderBytes;
+    return gemm_block_scaled_ws(0, packedA, sblkA, packedB, sblkB, alpha, bias, out, M, N, K, out_dtype, stream, &ext);
+}
+
+// Blocking read (and optional reset) of the status word kept in the fixed array; not for hot paths.
+int gemm_noalloc_status(int reset) {
+    unsigned char* base = nullptr;
+    if (noalloc_scratch(&base)) return -1;
+    int v = 0;
+    if (cudaMemcpy(&v, base, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (reset && v != 0) cudaMemset(base, 0, sizeof(int));
+    return v;
+}
+
+size_t gemm_noalloc_capacity() { return kNoAllocScratchBytes - kNoAllocHeaderBytes; }
+
 void gemm_set_splits(int n) { g_force_splits = n < 0 ? 0 : n; }
 
 int gemm_warm() {

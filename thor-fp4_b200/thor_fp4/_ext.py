@@ -37,6 +37,10 @@ SIGNATURES = {
     "tfp4_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, i64, i64, i64, c_int, c_void]),
     "tfp4_gemm_bias": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
                                i64, i64, i64, c_int, c_void]),
+    "tfp4_gemm_noalloc": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
+                                  i64, i64, i64, c_int, c_void]),
+    "tfp4_gemm_noalloc_status": (c_int, [c_int]),
+    "tfp4_gemm_noalloc_capacity": (ctypes.c_size_t, []),
     "tfp4_gemv": (c_int, [c_void, i64, i64, c_int, c_void, c_void, c_float, c_void, i64, c_int, c_void]),
     "tfp4_scales_gemv": (c_int, [c_void, i64, i64, c_void, c_void]),
     "tfp4_dequant_f32": (c_int, [c_void, c_void, c_float, i64, i64, c_void, c_void]),
