@@ -665,6 +665,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t MN, int64
 }
 
 #include "gemm_pair.cuh"
+#include "gemm_duo.cuh"
 
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -681,6 +682,7 @@ struct DeviceState {
     float* ws = nullptr;          // split-K partial sums, grown on demand
     size_t ws_bytes = 0;
     bool pair_attr_set[2][2] = {{false, false}, {false, false}};
+    bool duo_attr_set = false;
     bool attr_set[2][5] = {{false, false, false, false, false}, {false, false, false, false, false}};
 };
 
@@ -819,6 +821,36 @@ int launch_pair(DeviceState* st, const Plan& plan, GemmParams& p, int slot, cuda
     return TFP4_OK;
 }
 
+int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, cudaStream_t stream) {
+    const size_t smem = DuoCfg::SMEM_BYTES;
+    if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
+    p.stages = DuoCfg::OP_STAGES;
+    if (!st->duo_attr_set) {
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        st->duo_attr_set = true;
+    }
+    const int64_t tiles = ((p.M + DuoCfg::TILE_M - 1) / DuoCfg::TILE_M) * ((p.N + DuoCfg::TILE_N - 1) / DuoCfg::TILE_N);
+    const int64_t pairs = st->sm_count / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_duo_kernel, plan.tmW, plan.tmA, p);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "thor_fp4_b200: two-CTA GEMM launch failed: %s\n", cudaGetErrorString(e));
+        return TFP4_ERR_LAUNCH;
+    }
+    return TFP4_OK;
+}
+
 // scratch supplied by the caller of gemm_block_scaled_ws instead of the library's own
 struct ExtScratch {
     int* status;                 // device-visible status word
@@ -829,7 +861,8 @@ struct ExtScratch {
 
 int g_force_bn = 0;
 int g_force_splits = 0;    // 0 automatic, 1 never split K, n split into (about) n ranges
-int g_pair_mode = -1;   // 1: use the two-CTA kernel whenever the shape allows; otherwise never
+int g_pair_mode = -1;   // -1: automatic (256x256 two-CTA kernel for NVFP4 batches above 128 tokens); 0: single-CTA kernel only;
+                        // 1: the older two-CTA kernel (weights on the MMA's M side); 2: same as automatic
 int g_debug = 0;
 
 }  // namespace
@@ -878,8 +911,11 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // two-CTA kernel: needs at least one 256-row weight tile pair and a wide token tile
     // (opt-in: cross-CTA barrier round trips currently keep it behind the single-CTA kernel)
     const bool pair = g_pair_mode == 1 && (bn == 256 || bn == 192) && N >= 256 && st->sm_count >= 2;
-    const uint32_t box_a = pair ? (uint32_t)(bn / 2) : (uint32_t)bn;
-    PlanKey key{packedA, packedB, M, N, K, kind, pair ? -bn : bn, dev};
+    // 256 x 256 tiles on CTA pairs: NVFP4, more than one 128-token tile, no forced tile width or K split
+    const bool duo = g_pair_mode == 2 && kind == 0 && M > 128 && g_force_bn == 0 &&
+                     g_force_splits <= 1 && st->sm_count >= 2;
+    const uint32_t box_a = duo ? 128u : (pair ? (uint32_t)(bn / 2) : (uint32_t)bn);
+    PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : (pair ? -bn : bn), dev};
     auto it = g_plans.find(key);
     if (it == g_plans.end()) {
         ++g_plan_misses;
@@ -929,10 +965,10 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     {
         const int64_t tiles = p.m_tiles * p.n_tiles;
         int want = g_force_splits;
-        if (want == 0) want = (!pair && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
+        if (want == 0) want = (!pair && !duo && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
         if (want > p.k_blocks / 4) want = p.k_blocks / 4;
         if (want > 16) want = 16;
-        if (want > 1 && !pair) {
+        if (want > 1 && !pair && !duo) {
             p.kb_per_split = (p.k_blocks + want - 1) / want;
             p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
         }
@@ -960,6 +996,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.status = ext ? ext->status : st->status_dev;
     p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
+    if (duo) return launch_duo(st, pl, p, stream);
     if (pair) {
         if (kind == 0) return bn == 256 ? launch_pair<0, 256>(st, pl, p, 0, stream) : launch_pair<0, 192>(st, pl, p, 1, stream);
         return bn == 256 ? launch_pair<1, 256>(st, pl, p, 0, stream) : launch_pair<1, 192>(st, pl, p, 1, stream);
