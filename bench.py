@@ -304,7 +304,7 @@ def run_ours(args):
         line["e2e"] = {"value": world * flop / (e2e_max * 1e-3) / 1e12, "unit": "TFLOPS",
                        "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                        "ms_per_step": e2e_max, "api": "thor_fp4.Linear.forward, pinned host buffers"}
-    if not args.no_cpu and world >= 1:
+    if not args.no_cpu and world == 1:      # the CPU baseline is a single-GPU-run item
         line["cpu_baseline"] = cpu_baseline(args)
     print(json.dumps(line))
     if world > 1:

@@ -40,7 +40,7 @@ def _fro(got, ref):
 @pytest.mark.parametrize("shape", [(1, 128, 64), (3, 136, 192), (17, 512, 1024), (128, 128, 256),
                                    (255, 384, 832), (300, 264, 2048), (512, 1024, 4096)])
 @pytest.mark.parametrize("bn", [0, 32, 64, 128, 192, 256])
-@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("pair", [0, 1, 2])
 def test_gemm_matches_oracle_f32(shape, bn, pair):
     import thor_fp4
     from thor_fp4 import _ext
@@ -58,6 +58,38 @@ def test_gemm_matches_oracle_f32(shape, bn, pair):
         _ext.core().tfp4_set_pair_mode(-1)
     assert _ext.status() == 0
     assert _fro(out.cpu().numpy(), _oracle_out(a, b)) < TOL
+
+
+@gpu
+@pytest.mark.parametrize("shape", [(129, 64, 64), (256, 256, 256), (257, 72, 320), (300, 264, 2048), (640, 776, 1088),
+                                   (1000, 520, 2112), (2048, 1024, 4096)])
+@pytest.mark.parametrize("od", ["bf16", "f16", "f32"])
+def test_two_cta_kernel_equals_single_cta_kernel(shape, od):
+    """The 256x256 two-CTA kernel (TMA-store epilogue, token rows on the MMA's M side) against the
+    single-CTA kernel on the same operands: same products, same K order, so equal bits; ragged M,
+    N and K tails, bias, all output types."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = shape
+    x, w = _operands(M, N, K, seed=M + K, outliers=True)
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    bias = torch.randn(N, device="cuda") * 0.01
+    outs = []
+    L = _ext.core()
+    try:
+        for mode in (0, 2):
+            L.tfp4_set_pair_mode(mode)
+            L.tfp4_set_splits(1)
+            out = torch.full((M, N), float("nan"), dtype=_ext.OUT_TORCH[od], device="cuda")
+            ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, od, bias=bias)
+            torch.cuda.synchronize()
+            outs.append(out)
+    finally:
+        L.tfp4_set_pair_mode(-1)
+        L.tfp4_set_splits(0)
+    assert _ext.status() == 0
+    assert torch.equal(outs[0], outs[1])
 
 
 @gpu

@@ -821,7 +821,31 @@ int launch_pair(DeviceState* st, const Plan& plan, GemmParams& p, int slot, cuda
     return TFP4_OK;
 }
 
-int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, cudaStream_t stream) {
+// tensor maps of GEMM outputs (byte view, 128 bytes x 32 rows per store), cached per buffer and shape
+struct OutKey {
+    const void* out; int64_t M, N; int esize; int dev;
+    bool operator<(const OutKey& o) const { return std::tie(out, M, N, esize, dev) < std::tie(o.out, o.M, o.N, o.esize, o.dev); }
+};
+std::map<OutKey, CUtensorMap> g_out_maps;
+
+int out_map(const CUtensorMap** map, void* out, int64_t M, int64_t N, int esize, int dev) {
+    OutKey key{out, M, N, esize, dev};
+    auto it = g_out_maps.find(key);
+    if (it == g_out_maps.end()) {
+        CUtensorMap m;
+        int rc = encode_map(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, out, (uint64_t)(N * esize), (uint64_t)M, (uint64_t)(N * esize), 128, 32);
+        if (rc) return rc;
+        if (g_out_maps.size() > 4096) g_out_maps.clear();
+        it = g_out_maps.emplace(key, m).first;
+    }
+    *map = &it->second;
+    return TFP4_OK;
+}
+
+int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int dev, cudaStream_t stream) {
+    const CUtensorMap* tm_out = nullptr;
+    int rc = out_map(&tm_out, p.out, p.M, p.N, p.out_dtype == OUT_F32 ? 4 : 2, dev);
+    if (rc) return rc;
     const size_t smem = DuoCfg::SMEM_BYTES;
     if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
     p.stages = DuoCfg::OP_STAGES;
@@ -833,7 +857,7 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, cudaStream_t st
     const int64_t pairs = st->sm_count / 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(DUO_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -843,7 +867,7 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, cudaStream_t st
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_duo_kernel, plan.tmW, plan.tmA, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_duo_kernel, plan.tmW, plan.tmA, *tm_out, p);
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: two-CTA GEMM launch failed: %s\n", cudaGetErrorString(e));
         return TFP4_ERR_LAUNCH;
@@ -911,9 +935,11 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // two-CTA kernel: needs at least one 256-row weight tile pair and a wide token tile
     // (opt-in: cross-CTA barrier round trips currently keep it behind the single-CTA kernel)
     const bool pair = g_pair_mode == 1 && (bn == 256 || bn == 192) && N >= 256 && st->sm_count >= 2;
-    // 256 x 256 tiles on CTA pairs: NVFP4, more than one 128-token tile, no forced tile width or K split
-    const bool duo = g_pair_mode == 2 && kind == 0 && M > 128 && g_force_bn == 0 &&
-                     g_force_splits <= 1 && st->sm_count >= 2;
+    // 256 x 256 tiles on CTA pairs: NVFP4, no forced tile width or K split; chosen automatically once
+    // there are enough tiles to occupy most CTA pairs (smaller batches do better on single-CTA tiles with split K)
+    const int64_t duo_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const bool duo_ok = kind == 0 && M > 128 && N >= 64 && g_force_bn == 0 && g_force_splits <= 1 && st->sm_count >= 2;
+    const bool duo = duo_ok && (g_pair_mode == 2 || (g_pair_mode == -1 && duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5));
     const uint32_t box_a = duo ? 128u : (pair ? (uint32_t)(bn / 2) : (uint32_t)bn);
     PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : (pair ? -bn : bn), dev};
     auto it = g_plans.find(key);
@@ -996,7 +1022,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.status = ext ? ext->status : st->status_dev;
     p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
-    if (duo) return launch_duo(st, pl, p, stream);
+    if (duo) return launch_duo(st, pl, p, dev, stream);
     if (pair) {
         if (kind == 0) return bn == 256 ? launch_pair<0, 256>(st, pl, p, 0, stream) : launch_pair<0, 192>(st, pl, p, 1, stream);
         return bn == 256 ? launch_pair<1, 256>(st, pl, p, 0, stream) : launch_pair<1, 192>(st, pl, p, 1, stream);

@@ -2,47 +2,58 @@
 // 256-feature tile with tcgen05.mma.cta_group::2.  Included by gemm.cu inside its anonymous
 // namespace, after the single-CTA kernel, its PTX wrappers and gemm_pair.cuh.
 //
-// Why this shape.  Measured on B200: one 128x256x64 NVFP4 MMA takes 128 cycles whatever feeds it,
-// a barrier hop inside a CTA costs ~180 cycles, a hop between the CTAs of a cluster ~550, an
-// L2-resident 16 KB TMA load ~650, and all SMs together pull ~85 bytes per cycle and SM out of L2.
-// A single CTA with a 128x256 tile needs 105 bytes per cycle and has room for three 54 KB stages,
-// i.e. 1000 cycles of cover for a 1700-cycle refill chain: it is bound by both.  Here each CTA
-// loads only its own 128 token rows and its own 128 of the 256 feature rows per K block (32 KB,
-// 64 bytes per cycle at full MMA rate), so six stages fit: 2500 cycles of cover.
+// Why this shape.  Measured on B200: one 128x256x64 NVFP4 MMA takes 128 cycles whatever feeds it
+// (and one 256x256x64 MMA of a CTA pair the same 128), a barrier hop inside a CTA costs ~180
+// cycles, a hop between the CTAs of a cluster ~550, an L2-resident 16 KB TMA load ~650, and all
+// SMs together pull ~85 bytes per cycle and SM out of L2.  A single CTA with a 128x256 tile needs
+// 105 bytes per cycle and has room for three 54 KB stages, i.e. 1000 cycles of cover for a
+// 1700-cycle refill chain: it is bound by both.  Here each CTA loads only its own 128 token rows
+// and its own 128 of the 256 feature rows per K block (32 KB, 64 bytes per cycle at full MMA
+// rate), and five stages fit: 2000 cycles of cover.
 //
 // Orientation.  Tokens are the MMA's M side (lane of the accumulator), features its N side
-// (column): a thread of the epilogue then holds 32 consecutive features of one token, which are
-// contiguous in the row-major output, and stores them directly - no transposition through
-// shared memory, which is what keeps the six stages affordable.
+// (column): a thread of the epilogue holds consecutive features of one token, i.e. a contiguous
+// piece of an output row.
 //
 //   warp 0      producer, both CTAs: per K block two TMA loads (own tokens, own feature half)
 //   warp 1      leader: MMA issuer.  peer: relays "my operands landed" to the leader's barrier
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns -> alpha, bias, cast -> 16-byte stores
-//   warps 6-9   scale loaders: scale atoms (own pipeline, four K blocks ahead of the operands)
-//               shared memory -> registers -> tcgen05.st into one of four scale slots
+//   warps 2-5   epilogue: tcgen05.ld -> alpha, bias, cast -> swizzled shared memory -> one TMA
+//               store per warp and 128 bytes of output row (32 rows), double buffered; the
+//               accumulator is handed back as soon as its last columns are in registers
+//   warps 6-9   scale loaders: scale atoms of two K blocks at a time, shared memory ->
+//               registers -> tcgen05.st into the scale slots of tensor memory
+//   warp 10     scale producer: bulk copies of the scale atoms, two K blocks per copy, running
+//               ahead of the operand pipeline
 // Barriers.  full[s] (leader: own bytes + the peer's relay; peer: own bytes), empty[s] / tfull:
 // local in each CTA, signalled by the leader's tcgen05.commit with a two-CTA mask.  sfl[i]: scale
 // atoms landed (local).  sfree[i]: the four loader warps have read scale stage i (local).
-// sffull[slot] / tempty: in the leader, 8 arrivals (4 warps of each CTA).  Every wait is bounded.
-// All waits poll with CTA-scope mbarrier.test_wait: a cluster-scope acquire on the MMA-issuing
-// thread was measured to cost ~250 cycles per poll even when it succeeds at once (it waits for
-// the thread's outstanding tcgen05 work), which alone halves the MMA rate.
+// sffull[i] / tempty: in the leader, 8 arrivals (4 warps of each CTA).  Every wait is bounded.
+// The MMA issuer polls with mbarrier.test_wait; every other warp waits with try_wait, which parks
+// the warp: ten warps spinning on shared-memory barriers slow the issuer's own polls down.  Arrivals on the other CTA's barriers are
+// relaxed: a releasing arrive at cluster scope first waits for everything its thread has in
+// flight (bulk copies, global stores), measured at 500-1200 cycles per arrival.
+
+constexpr int DUO_THREADS = 352;
 
 struct DuoCfg {
     static constexpr int TILE_M = 256, TILE_N = 256;
-    static constexpr int OP_STAGES = 6;
+    static constexpr int OP_STAGES = 5;
     static constexpr int X_BYTES = 128 * KB_BYTES;            // own token rows, one K block
     static constexpr int W_BYTES = 128 * KB_BYTES;            // own half of the feature rows
-    static constexpr int SF_STAGES = 4;
-    static constexpr int SF_PART = 4 * 512;                   // the scale atoms of 128 rows for one K block
+    static constexpr int SF_STAGES = 2;                       // each holds the scales of two K blocks
+    static constexpr int SF_PART = 8 * 512;                   // the scale atoms of 128 rows for two K blocks
     static constexpr int SF_STAGE_BYTES = 3 * SF_PART;        // own tokens, feature rows 0-127, feature rows 128-255
-    static constexpr int NSLOT = 4;                           // scale slots in tensor memory
+    static constexpr int NSLOT = 5;                           // scale slots in tensor memory: one per operand stage
     static constexpr int SF_COL = 256;                        // behind the 256 accumulator columns
+    static constexpr int EPI_BUF = 32 * 128;                  // 32 rows x 128 bytes, one TMA store
+    static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF;         // two buffers for each epilogue warp
     static constexpr int BAR_BYTES = 512;
-    static constexpr int SMEM_BYTES = OP_STAGES * (X_BYTES + W_BYTES) + SF_STAGES * SF_STAGE_BYTES + BAR_BYTES + 1024;
+    static constexpr int SMEM_BYTES =
+        OP_STAGES * (X_BYTES + W_BYTES) + EPI_BYTES + SF_STAGES * SF_STAGE_BYTES + BAR_BYTES + 1024;
     static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
     static_assert(SF_COL + NSLOT * TMEM_SF_SLOT_COLS <= TMEM_COLS, "scale slots do not fit");
-    static_assert(NSLOT < OP_STAGES, "a loader waits on the stage barrier NSLOT K blocks back");
+    static_assert(NSLOT == OP_STAGES, "K block i uses operand stage and scale slot i % OP_STAGES alike");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 
 __device__ __forceinline__ void tc_mma_pair_nvf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -60,22 +71,51 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}"
         ::"r"(bar) : "memory");
 }
-// Remote arrival without a release fence.  A releasing arrive at cluster scope first waits for
-// everything the thread has in flight (its bulk copies, its global stores): measured 500-1200
-// cycles per arrival here.  What the arrival publishes is already complete when it is made - a
-// TMA transfer whose barrier the thread has seen flip, tensor-memory stores after
+// Remote arrival without a release fence.  What the arrival publishes is already complete when
+// it is made - a TMA transfer whose barrier the thread has seen flip, tensor-memory stores after
 // tcgen05.wait::st, tensor-memory loads after tcgen05.wait::ld - so no fence is needed.
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ void st_global_v4(void* ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+// Waiting with a long suspend hint: the warp sleeps in hardware until the phase completes (or the
+// hint, in nanoseconds, runs out) instead of re-issuing polls that compete with the MMA issuer
+// for the shared-memory instruction queue of their SM partition.  Bounded like every other wait.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    const long long t0 = clock64();
+    for (uint32_t it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(20000u)
+            : "memory");
+        if (ok) return true;
+        if ((it & 7u) == 7u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_CYCLES) {
+                *abort_flag = code;
+                return false;
+            }
+        }
+    }
 }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most one of this thread's bulk-store groups may still be reading shared memory
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// one 32-column chunk of one token row: alpha, bias, cast, 16-byte stores (columns beyond N dropped)
-__device__ __forceinline__ void duo_emit(const uint32_t (&v)[32], uint8_t* out_row, int64_t n, int64_t N, float alpha,
-                                         const float* bias, int out_dtype) {
-    float f[32];
+// 32 accumulator columns of one token row -> alpha, bias -> floats
+__device__ __forceinline__ void duo_scale(const uint32_t (&v)[32], float (&f)[32], int64_t n, int64_t N, float alpha,
+                                          const float* bias) {
     if (bias != nullptr) {
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
@@ -90,50 +130,97 @@ __device__ __forceinline__ void duo_emit(const uint32_t (&v)[32], uint8_t* out_r
 #pragma unroll
         for (int i = 0; i < 32; ++i) f[i] = fmaf(alpha, __uint_as_float(v[i]), 0.f);
     }
-    if (out_dtype == OUT_F32) {
-        float* o = reinterpret_cast<float*>(out_row) + n;
+}
+// 32 columns as 16-bit values: four 16-byte chunks of a 128-byte row, chunk index XOR (row & 7)
+// (the 128-byte swizzle the TMA store expects)
+__device__ __forceinline__ void duo_put16(const float (&f)[32], uint32_t row_addr, int chunk0, int row, bool bf16) {
+    uint32_t h[16];
+    if (bf16) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-            if (n + i + 4 <= N)
-                st_global_v4(o + i, __float_as_uint(f[i]), __float_as_uint(f[i + 1]), __float_as_uint(f[i + 2]), __float_as_uint(f[i + 3]));
-    } else {
-        uint32_t h[16];
-        if (out_dtype == OUT_BF16) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                h[i] = *reinterpret_cast<uint32_t*>(&t);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-                h[i] = *reinterpret_cast<uint32_t*>(&t);
-            }
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            h[i] = *reinterpret_cast<uint32_t*>(&t);
         }
-        uint16_t* o = reinterpret_cast<uint16_t*>(out_row) + n;
+    } else {
 #pragma unroll
-        for (int i = 0; i < 32; i += 8)
-            if (n + i + 8 <= N) st_global_v4(o + i, h[i / 2], h[i / 2 + 1], h[i / 2 + 2], h[i / 2 + 3]);
+        for (int i = 0; i < 16; ++i) {
+            __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            h[i] = *reinterpret_cast<uint32_t*>(&t);
+        }
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        st_shared_v4(row_addr + (uint32_t)(((chunk0 + c) ^ (row & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+}
+__device__ __forceinline__ void duo_put32(const float (&f)[32], uint32_t row_addr, int row) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+        st_shared_v4(row_addr + (uint32_t)((c ^ (row & 7)) << 4), __float_as_uint(f[4 * c]), __float_as_uint(f[4 * c + 1]),
+                     __float_as_uint(f[4 * c + 2]), __float_as_uint(f[4 * c + 3]));
 }
 
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
+// One full K block of the two-CTA MMA stream in a single statement: four MMAs (K = 64 each,
+// operands 32 bytes further into the 128-byte swizzle span each time, so only the low descriptor
+// word changes), the look-ahead polls of the next K block's two barriers between them, and the
+// commit that frees the stage in both CTAs.  The issuing warp is one thread of control with no
+// instruction-level parallelism to speak of, about five cycles per instruction: every instruction
+// between two MMAs counts, so nothing is recomputed here that the caller can keep in a register.
+// Returns 1 if both polled barriers had completed the polled phase.
+__device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate, uint32_t d, uint32_t a_lo, uint32_t b_lo,
+                                               uint32_t desc_hi, uint32_t sf, uint32_t full_next, uint32_t sf_next,
+                                               uint32_t par_next, uint32_t empty_bar) {
+    uint32_t ready;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q, pa, pt, pf, ps;\n\t"
+        ".reg .b16 m;\n\t"
+        ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g0, g1, g2, g3;\n\t"
+        ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "setp.ne.b32 pa, %2, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b16 m, 3;\n\t"
+        "add.u32 a1, %4, 2;\n\tadd.u32 a2, %4, 4;\n\tadd.u32 a3, %4, 6;\n\t"
+        "add.u32 b1, %5, 2;\n\tadd.u32 b2, %5, 4;\n\tadd.u32 b3, %5, 6;\n\t"
+        "mov.b64 da0, {%4, %6};\n\tmov.b64 da1, {a1, %6};\n\tmov.b64 da2, {a2, %6};\n\tmov.b64 da3, {a3, %6};\n\t"
+        "mov.b64 db0, {%5, %6};\n\tmov.b64 db1, {b1, %6};\n\tmov.b64 db2, {b2, %6};\n\tmov.b64 db3, {b3, %6};\n\t"
+        "add.u32 f1, %7, 4;\n\tadd.u32 f2, %7, 8;\n\tadd.u32 f3, %7, 12;\n\t"
+        "add.u32 g0, %7, 16;\n\tadd.u32 g1, %7, 24;\n\tadd.u32 g2, %7, 32;\n\tadd.u32 g3, %7, 40;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da0, db0, %12, [%7], [g0], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%8], %10;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da1, db1, %12, [f1], [g1], pt;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%9], %10;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da2, db2, %12, [f2], [g2], pt;\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da3, db3, %12, [f3], [g3], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%11], m;\n\t"
+        "and.pred pf, pf, ps;\n\t"
+        "selp.u32 %0, 1, 0, pf;\n\t"
+        "}"
+        : "=r"(ready)
+        : "r"(on), "r"(accumulate), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf), "r"(full_next), "r"(sf_next),
+          "r"(par_next), "r"(empty_bar), "n"(DuoCfg::IDESC)
+        : "memory");
+    return ready;
+}
+
+__global__ void __launch_bounds__(DUO_THREADS, 1)
+gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
     using C = DuoCfg;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sX = smem;
     uint8_t* sWh = sX + (size_t)C::OP_STAGES * C::X_BYTES;
-    uint8_t* sSF = sWh + (size_t)C::OP_STAGES * C::W_BYTES;
+    uint8_t* sEpi = sWh + (size_t)C::OP_STAGES * C::W_BYTES;
+    uint8_t* sSF = sEpi + C::EPI_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSF + (size_t)C::SF_STAGES * C::SF_STAGE_BYTES);
     uint64_t* full_bar = bars;                               // [OP_STAGES]
     uint64_t* empty_bar = full_bar + C::OP_STAGES;           // [OP_STAGES]
     uint64_t* sfl_bar = empty_bar + C::OP_STAGES;            // [SF_STAGES]
     uint64_t* sfree_bar = sfl_bar + C::SF_STAGES;            // [SF_STAGES]
-    uint64_t* sffull_bar = sfree_bar + C::SF_STAGES;         // [NSLOT]     used in the leader
+    uint64_t* sffull_bar = sfree_bar + C::SF_STAGES;         // [NSLOT]      used in the leader
     uint64_t* tfull_bar = sffull_bar + C::NSLOT;             // [1]
-    uint64_t* tempty_bar = tfull_bar + 1;                    // [1]         used in the leader
+    uint64_t* tempty_bar = tfull_bar + 1;                    // [1]          used in the leader
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -150,7 +237,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             mbar_init(smem_u32(&sfl_bar[s]), 1);
             mbar_init(smem_u32(&sfree_bar[s]), 4);
         }
-        for (int i = 0; i < C::NSLOT; ++i) mbar_init(smem_u32(&sffull_bar[i]), 8);
+        for (int s = 0; s < C::NSLOT; ++s) mbar_init(smem_u32(&sffull_bar[s]), 8);
         mbar_init(smem_u32(tfull_bar), 1);
         mbar_init(smem_u32(tempty_bar), 8);
         *abort_flag = 0;
@@ -172,14 +259,15 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const int64_t total_tiles = tiles_m * tiles_n;
     const int64_t first = blockIdx.x >> 1, stride = gridDim.x >> 1;
     const int k_blocks = p.k_blocks;
+    const int grans = (k_blocks + 1) >> 1;                   // scale granules (two K blocks) per tile
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     const uint32_t sfl0 = smem_u32(sfl_bar), sfree0 = smem_u32(sfree_bar), sffull0 = smem_u32(sffull_bar);
+    const bool prof = (p.debug & 1024) != 0;
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (both CTAs)
         uint32_t s = 0, ph = 0;
         bool ok = true;
-        const bool prof = (p.debug & 1024) != 0;
         long long c_wait = 0;
         const CUtensorMap* my_map = (lane == 0) ? &tmX : &tmW;
         const uint32_t my_dst = (lane == 0) ? smem_u32(sX) : smem_u32(sWh);
@@ -188,7 +276,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const int my_y = (lane == 0) ? (int)(mt * C::TILE_M + rank * 128) : (int)(nt * C::TILE_N + rank * 128);
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const long long t0 = prof ? clock64() : 0;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+                if (!mbar_wait_sleep(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
                 if (prof) c_wait += clock64() - t0;
                 const uint32_t bar = full0 + 8 * s;
                 if (p.debug & 8) {
@@ -211,14 +299,19 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     } else if (warp == 1) {
         if (leader) {
             // -------------------------------------------------------- MMA issuer
-            // The warp walks the loop together; one elected lane issues.  Nothing but two barrier
-            // polls and a few adds sits between the last MMA of a K block and the first of the next:
-            // the tensor pipe runs at most about one instruction ahead of its issuer.
-            uint32_t s = 0, ph = 0, slot = 0, sph = 0, tcount = 0;
-            bool ok = true;
+            // The warp walks the loop together (uniform control flow keeps the operands in uniform
+            // registers); lane 0's instructions are the ones that take effect.  Per K block: one
+            // statement with the four MMAs, the polls of the next K block's barriers and the commit
+            // (duo_kblock); the blocking, bounded wait is only the fallback when a poll failed.
+            uint32_t s = 0, ph = 0, tcount = 0;
+            const uint32_t on = (lane == 0) ? 1u : 0u;
+            bool ok = true, peek = false;
             const uint64_t adesc_base = desc_sw128(smem_u32(sX)), bdesc_base = desc_sw128(smem_u32(sWh));
-            const bool prof = (p.debug & 1024) != 0;
-            long long c_full = 0, c_sf = 0, c_issue = 0, c_acc = 0;
+            const uint32_t desc_hi = (uint32_t)(adesc_base >> 32);
+            const uint32_t a_lo0 = (uint32_t)adesc_base, b_lo0 = (uint32_t)bdesc_base;
+            const uint32_t sf0 = tmem_base + C::SF_COL;
+            long long c_acc = 0, c_wait = 0, c_blk = 0;
+            uint32_t n_miss = 0;
             const long long c_begin = clock64();
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 const long long ta = prof ? clock64() : 0;
@@ -226,39 +319,46 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 if (prof) c_acc += clock64() - ta;
                 tc_fence_after();
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    long long t0 = 0, t1 = 0, t2 = 0;
-                    if (prof) t0 = clock64();
-                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 3)) { ok = false; break; }
-                    if (prof) t1 = clock64();
-                    if (!mbar_wait(sffull0 + 8 * slot, sph, abort_flag, 5)) { ok = false; break; }
-                    if (prof) t2 = clock64();
-                    tc_fence_after();
-                    const int n_mma = (kb == k_blocks - 1) ? p.last_atoms : 4;
-                    if (elect_one()) {
-                        const uint64_t adesc = adesc_base + (uint64_t)(s * (C::X_BYTES >> 4));
-                        const uint64_t bdesc = bdesc_base + (uint64_t)(s * (C::W_BYTES >> 4));
-                        const uint32_t sf = tmem_base + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
-                        if (!(p.debug & 4)) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                if (j < n_mma)
-                                    tc_mma_pair_nvf4(tmem_base, adesc + 2 * j, bdesc + 2 * j, C::IDESC, sf + 4 * j,
-                                                     sf + TMEM_SFA_OFF + 8 * j, (kb > 0 || j > 0) ? 1u : 0u);
-                        }
-                        tc_commit_pair(empty0 + 8 * s);          // frees stage s (and scale slot) in both CTAs
-                        if (kb == k_blocks - 1) tc_commit_pair(smem_u32(tfull_bar));   // accumulator ready in both CTAs
+                    if (!peek) {
+                        // scales of this K block are in tensor memory of both CTAs; operands of both CTAs landed
+                        const long long t0 = prof ? clock64() : 0;
+                        if (!mbar_wait(sffull0 + 8 * s, ph, abort_flag, 5)) { ok = false; break; }
+                        if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 3)) { ok = false; break; }
+                        if (prof) { c_wait += clock64() - t0; ++n_miss; }
                     }
-                    __syncwarp();
-                    if (prof) { c_full += t1 - t0; c_sf += t2 - t1; c_issue += clock64() - t2; }
-                    if (++s == C::OP_STAGES) { s = 0; ph ^= 1u; }
-                    if (++slot == C::NSLOT) { slot = 0; sph ^= 1u; }
+                    if (!(p.debug & 64)) tc_fence_after();
+                    const bool last = kb == k_blocks - 1;
+                    const uint32_t s_n = (s + 1 == C::OP_STAGES) ? 0u : s + 1;
+                    const uint32_t ph_n = (s + 1 == C::OP_STAGES) ? ph ^ 1u : ph;
+                    const uint32_t a_lo = a_lo0 + s * (C::X_BYTES >> 4), b_lo = b_lo0 + s * (C::W_BYTES >> 4);
+                    const uint32_t sf = sf0 + s * TMEM_SF_SLOT_COLS;
+                    uint32_t ready;
+                    if ((!last || p.last_atoms == 4) && !(p.debug & 4)) {
+                        const long long tb = prof ? clock64() : 0;
+                        ready = duo_kblock(on, kb > 0 ? 1u : 0u, tmem_base, a_lo, b_lo, desc_hi, sf, full0 + 8 * s_n,
+                                           sffull0 + 8 * s_n, ph_n, empty0 + 8 * s);
+                        if (prof) c_blk += clock64() - tb;
+                    } else {
+                        // ragged last K block (or MMAs switched off by the test hook)
+                        const uint64_t adesc = ((uint64_t)desc_hi << 32) | a_lo, bdesc = ((uint64_t)desc_hi << 32) | b_lo;
+                        const uint32_t m_on = (p.debug & 4) ? 0u : on;
+                        for (int j = 0; j < p.last_atoms || (!last && j < 4); ++j)
+                            tc_mma_pair_if<0>(m_on, tmem_base, adesc + 2 * j, bdesc + 2 * j, C::IDESC, sf + 4 * j,
+                                              sf + TMEM_SFA_OFF + 8 * j, (kb > 0 || j > 0) ? 1u : 0u);
+                        tc_commit_pair_if(on, empty0 + 8 * s);
+                        ready = (mbar_test_wait(full0 + 8 * s_n, ph_n) && mbar_test_wait(sffull0 + 8 * s_n, ph_n)) ? 1u : 0u;
+                    }
+                    if (last) tc_commit_pair_if(on, smem_u32(tfull_bar));   // accumulator ready in both CTAs
+                    peek = __all_sync(0xffffffffu, ready != 0u) && !(p.debug & 32);
+                    s = s_n; ph = ph_n;
                 }
             }
             if (prof && lane == 0 && p.stats != nullptr && blockIdx.x < 256) {
                 p.stats[blockIdx.x * 4 + 0] = (unsigned long long)(clock64() - c_begin);
-                p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_full;
-                p.stats[blockIdx.x * 4 + 2] = (unsigned long long)c_sf;
-                p.stats[blockIdx.x * 4 + 3] = (unsigned long long)(c_issue + (c_acc << 32));
+                p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_wait;
+                p.stats[blockIdx.x * 4 + 2] = (unsigned long long)n_miss;
+                p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_acc;
+                p.stats[600 + blockIdx.x] = (unsigned long long)c_blk;
             }
         } else {
             // -------------------------------------------------------- relay (peer CTA)
@@ -267,7 +367,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const uint32_t full0_leader = map_to_cta(full0, 0);
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 9)) { ok = false; break; }
+                    if (!mbar_wait_sleep(full0 + 8 * s, ph, abort_flag, 9)) { ok = false; break; }
                     if (lane == 0) mbar_arrive_cluster_relaxed(full0_leader + 8 * s);
                     if (++s == C::OP_STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -276,144 +376,177 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
         const int q = warp & 3;                              // tensor-memory lane quarter this warp may read
-        uint32_t tcount = 0;
+        uint32_t tcount = 0, nstore = 0;
         bool ok = true;
         const uint32_t tempty_leader = map_to_cta(smem_u32(tempty_bar), 0);
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
         const int esize = (p.out_dtype == OUT_F32) ? 4 : 2;
+        const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)q * 2u * C::EPI_BUF;
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
             const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
-            if (!mbar_wait(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4)) { ok = false; break; }
+            if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
-            const int64_t m = mt * C::TILE_M + rank * 128 + q * 32 + lane;
+            const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
             const int64_t n0 = nt * C::TILE_N;
-            uint8_t* out_row = reinterpret_cast<uint8_t*>(p.out) + (size_t)m * (size_t)p.N * esize;
-            const bool row_ok = m < p.M && !(p.debug & 1);
-            // the read of the next 32 columns is in flight while the current ones are converted and stored
+            // 32 columns are converted while the read of the next 32 is in flight
             uint32_t va[32], vb[32];
             tc_ld32(t_lane, va);
 #pragma unroll 1
-            for (int c = 0; c < C::TILE_N; c += 64) {
+            for (int c0 = 0; c0 < C::TILE_N; c0 += 64) {
+                // ---- columns c0 .. c0+31 (in va); read c0+32.. into vb
                 tc_wait_ld();
-                tc_ld32(t_lane + (uint32_t)(c + 32), vb);
-                if (row_ok && n0 + c < p.N) duo_emit(va, out_row, n0 + c, p.N, p.alpha, p.bias, p.out_dtype);
-                tc_wait_ld();
-                if (c + 64 < C::TILE_N) {
-                    tc_ld32(t_lane + (uint32_t)(c + 64), va);
+                tc_ld32(t_lane + (uint32_t)(c0 + 32), vb);
+                uint32_t buf = my_buf + (nstore & 1u) * C::EPI_BUF;
+                uint32_t row_addr = buf + (uint32_t)lane * 128u;
+                float f[32];
+                if (lane == 0) bulk_wait_read_1();           // the store issued from this buffer two slabs ago has read it
+                __syncwarp();
+                duo_scale(va, f, n0 + c0, p.N, p.alpha, p.bias);
+                if (esize == 2) {
+                    duo_put16(f, row_addr, 0, lane, p.out_dtype == OUT_BF16);
                 } else {
-                    // the accumulator is in registers: hand it back before the last stores
+                    duo_put32(f, row_addr, lane);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < p.M && n0 + c0 < p.N && !(p.debug & 1)) tma_store_2d(&tmO, (int)((n0 + c0) * 4), (int)row0, buf);
+                        bulk_commit_group();
+                    }
+                    ++nstore;
+                    buf = my_buf + (nstore & 1u) * C::EPI_BUF;
+                    row_addr = buf + (uint32_t)lane * 128u;
+                    if (lane == 0) bulk_wait_read_1();
+                    __syncwarp();
+                }
+                // ---- columns c0+32 .. c0+63 (in vb); read c0+64.. into va, or hand the accumulator back
+                tc_wait_ld();
+                if (c0 + 64 < C::TILE_N) {
+                    tc_ld32(t_lane + (uint32_t)(c0 + 64), va);
+                } else {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);
                 }
-                if (row_ok && n0 + c + 32 < p.N) duo_emit(vb, out_row, n0 + c + 32, p.N, p.alpha, p.bias, p.out_dtype);
+                duo_scale(vb, f, n0 + c0 + 32, p.N, p.alpha, p.bias);
+                if (esize == 2) duo_put16(f, row_addr, 4, lane, p.out_dtype == OUT_BF16);
+                else duo_put32(f, row_addr, lane);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    // rows beyond M and bytes beyond the row end are clipped by the copy engine; a slab that
+                    // lies outside altogether still closes an (empty) group, so that "all but the latest
+                    // group" always names the store that last used the other buffer
+                    const int64_t nn = n0 + c0 + (esize == 2 ? 0 : 32);
+                    if (row0 < p.M && nn < p.N && !(p.debug & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
+                    bulk_commit_group();
+                }
+                ++nstore;
             }
         }
-    } else {
+        if (lane == 0) bulk_wait_all();
+    } else if (warp < 10) {
         // ------------------------------------------------------------ scale loaders (warps 6..9, both CTAs)
         const int q = warp & 3;
-        const bool issuer = warp == 6;                       // this warp also issues the scale-atom copies
-        uint32_t sfs = 0, sfph = 0, slot = 0, es = 0, eph = 0, it = 0;
+        uint32_t g = 0, it = 0, slot = 0, sph = 0;           // granule counter; K block counter, its slot and slot phase
         bool ok = true;
-        const bool prof = (p.debug & 1024) != 0 && issuer && !leader;
-        long long c_sfl = 0, c_free = 0, c_empty = 0, c_st = 0, c_arr = 0, c_ld = 0;
+        const bool profl = prof && warp == 6 && !leader;
+        long long c_sfl = 0, c_empty = 0, c_st = 0;
         const uint32_t sf_base = smem_u32(sSF);
         const uint32_t sffull_leader = map_to_cta(sffull0, 0);
-        // the copies run SF_STAGES K blocks ahead of the loaders: a second (tile, kb) cursor
-        int64_t tile2 = first;
-        int kb2 = 0;
-        uint32_t sfs2 = 0;
-        auto issue_sf = [&]() {
-            // lanes 0..2: scales of own tokens, of feature rows 0-127, of feature rows 128-255
-            if (tile2 >= total_tiles) return;
-            const int64_t nt2 = tile2 / tiles_m, mt2 = tile2 - nt2 * tiles_m;
-            const int atoms = (kb2 == k_blocks - 1) ? p.last_atoms : 4;
-            const uint32_t bytes = (uint32_t)atoms * 512u;
-            const int64_t ta = 2 * mt2 + rank, tw = 2 * nt2;
-            const bool a_ok = ta < p.rows_a_tiles, w1_ok = tw + 1 < p.rows_w_tiles;
-            const uint32_t bar = sfl0 + 8 * sfs2;
-            if (p.debug & 8) {
-                if (lane == 0) mbar_arrive(bar);
-            } else {
-                if (lane == 0) mbar_expect_tx(bar, bytes * (uint32_t)(1 + (a_ok ? 1 : 0) + (w1_ok ? 1 : 0)));
-                __syncwarp();
-                const uint32_t dst = sf_base + sfs2 * C::SF_STAGE_BYTES + (uint32_t)lane * C::SF_PART;
-                const int64_t koff = (int64_t)kb2 * C::SF_PART;
-                if (lane == 0 && a_ok) bulk_load(dst, p.sfA + ta * p.sf_tile_stride + koff, bytes, bar);
-                if (lane == 1) bulk_load(dst, p.sfW + tw * p.sf_tile_stride + koff, bytes, bar);
-                if (lane == 2 && w1_ok) bulk_load(dst, p.sfW + (tw + 1) * p.sf_tile_stride + koff, bytes, bar);
-            }
-            if (++kb2 == k_blocks) { kb2 = 0; tile2 += stride; }
-            if (++sfs2 == C::SF_STAGES) sfs2 = 0;
-        };
-        if (issuer)
-            for (int i = 0; i < C::SF_STAGES; ++i) issue_sf();
+        const uint32_t t_q = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_COL;
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                long long t0 = prof ? clock64() : 0;
-                if (!mbar_wait(sfl0 + 8 * sfs, sfph, abort_flag, 6)) { ok = false; break; }
-                if (prof) c_sfl += clock64() - t0;
-                t0 = prof ? clock64() : 0;
-                uint32_t va[16], vw[2][16];
-                const uint32_t src = sf_base + sfs * C::SF_STAGE_BYTES + lane * 16;
+            for (int gi = 0; gi < grans && ok; ++gi, ++g) {
+                const uint32_t st = g & 1u, gph = (g >> 1) & 1u;
+                long long t0 = profl ? clock64() : 0;
+                if (!mbar_wait_sleep(sfl0 + 8 * st, gph, abort_flag, 6)) { ok = false; break; }
+                if (profl) c_sfl += clock64() - t0;
+                uint32_t va[32], vw0[32], vw1[32];
+                const uint32_t src = sf_base + st * C::SF_STAGE_BYTES + lane * 16;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < 8; ++j) {
                     ld_shared_v4(src + 512 * j, &va[4 * j]);
-                    ld_shared_v4(src + C::SF_PART + 512 * j, &vw[0][4 * j]);
-                    ld_shared_v4(src + 2 * C::SF_PART + 512 * j, &vw[1][4 * j]);
+                    ld_shared_v4(src + C::SF_PART + 512 * j, &vw0[4 * j]);
+                    ld_shared_v4(src + 2 * C::SF_PART + 512 * j, &vw1[4 * j]);
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sfree0 + 8 * sfs);
-                if (prof) c_ld += clock64() - t0;
-                if (issuer) {
-                    // refill this scale stage once all four warps have it in registers
-                    t0 = prof ? clock64() : 0;
-                    if (!mbar_wait(sfree0 + 8 * sfs, sfph, abort_flag, 10)) { ok = false; break; }
-                    if (prof) c_free += clock64() - t0;
-                    issue_sf();
-                }
-                if (it >= C::NSLOT) {
-                    // the slot is free once the MMAs of the K block NSLOT back are done
-                    t0 = prof ? clock64() : 0;
-                    if (!mbar_wait(empty0 + 8 * es, eph, abort_flag, 7)) { ok = false; break; }
-                    if (prof) c_empty += clock64() - t0;
-                    if (++es == C::OP_STAGES) { es = 0; eph ^= 1u; }
-                }
-                tc_fence_after();
-                t0 = prof ? clock64() : 0;
-                if (!(p.debug & 2)) {
-                    const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
-                    tc_st<16>(t_base, va);
-                    // feature-side scales: MMA j reads 8 columns, rows 0-127 then rows 128-255
-                    uint32_t u[32];
+                if (lane == 0) mbar_arrive(sfree0 + 8 * st);
+                const int nkb = (2 * gi + 2 <= k_blocks) ? 2 : 1;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                for (int b = 0; b < 2; ++b) {
+                    if (b < nkb) {
+                        if (it >= (uint32_t)C::NSLOT) {
+                            // the slot is free once the MMAs of the K block NSLOT back (same ring index) are done
+                            t0 = profl ? clock64() : 0;
+                            if (!mbar_wait_sleep(empty0 + 8 * slot, sph ^ 1u, abort_flag, 7)) { ok = false; break; }
+                            if (profl) c_empty += clock64() - t0;
+                        }
+                        tc_fence_after();
+                        t0 = profl ? clock64() : 0;
+                        if (!(p.debug & 2)) {
+                            const uint32_t t_base = t_q + slot * TMEM_SF_SLOT_COLS;
+                            tc_st<16>(t_base, va + 16 * b);
+                            // feature-side scales: MMA j reads 8 columns, rows 0-127 then rows 128-255
+                            uint32_t u[32];
 #pragma unroll
-                        for (int t = 0; t < 2; ++t)
+                            for (int j = 0; j < 4; ++j)
 #pragma unroll
-                            for (int w = 0; w < 4; ++w) u[8 * j + 4 * t + w] = vw[t][4 * j + w];
-                    tc_st<16>(t_base + TMEM_SFA_OFF, u);
-                    tc_st<16>(t_base + TMEM_SFA_OFF + 16, u + 16);
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                                for (int w = 0; w < 4; ++w) {
+                                    u[8 * j + w] = vw0[16 * b + 4 * j + w];
+                                    u[8 * j + 4 + w] = vw1[16 * b + 4 * j + w];
+                                }
+                            tc_st<16>(t_base + TMEM_SFA_OFF, u);
+                            tc_st<16>(t_base + TMEM_SFA_OFF + 16, u + 16);
+                            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        }
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster_relaxed(sffull_leader + 8 * slot);
+                        if (profl) c_st += clock64() - t0;
+                        ++it;
+                        if (++slot == (uint32_t)C::NSLOT) { slot = 0; sph ^= 1u; }
+                    }
                 }
-                tc_fence_before();
-                __syncwarp();
-                long long t1 = prof ? clock64() : 0;
-                if (lane == 0) mbar_arrive_cluster_relaxed(sffull_leader + 8 * slot);
-                if (prof) { c_st += t1 - t0; c_arr += clock64() - t1; }
-                ++it;
-                if (++sfs == C::SF_STAGES) { sfs = 0; sfph ^= 1u; }
-                if (++slot == C::NSLOT) slot = 0;
             }
         }
-        if (prof && lane == 0 && p.stats != nullptr && blockIdx.x < 256) {
+        if (profl && lane == 0 && p.stats != nullptr && blockIdx.x < 256) {
             p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_sfl;
-            p.stats[blockIdx.x * 4 + 2] = (unsigned long long)c_free;
+            p.stats[blockIdx.x * 4 + 2] = (unsigned long long)c_st;
             p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_empty;
-            p.stats[600 + blockIdx.x * 2] = (unsigned long long)c_st;
-            p.stats[600 + blockIdx.x * 2 + 1] = (unsigned long long)(c_arr + (c_ld << 32));
         }
-        if (!ok && issuer && lane == 0) {
+    } else {
+        // ------------------------------------------------------------ scale producer (warp 10, both CTAs)
+        // lanes 0..2: scales of own tokens, of feature rows 0-127, of feature rows 128-255
+        uint32_t g = 0;
+        bool ok = true;
+        const uint32_t sf_base = smem_u32(sSF);
+        for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
+            const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+            const int64_t ta = 2 * mt + rank, tw = 2 * nt;
+            const bool a_ok = ta < p.rows_a_tiles, w1_ok = tw + 1 < p.rows_w_tiles;
+            const uint8_t* my_src = (lane == 0) ? p.sfA + ta * p.sf_tile_stride
+                                                : p.sfW + (tw + (lane == 2 ? 1 : 0)) * p.sf_tile_stride;
+            const bool my_ok = (lane == 0) ? a_ok : (lane == 1 ? true : (lane == 2 ? w1_ok : false));
+            const uint32_t parts = 1u + (a_ok ? 1u : 0u) + (w1_ok ? 1u : 0u);
+            for (int gi = 0; gi < grans; ++gi, ++g) {
+                const uint32_t st = g & 1u;
+                if (!mbar_wait_sleep(sfree0 + 8 * st, ((g >> 1) & 1u) ^ 1u, abort_flag, 10)) { ok = false; break; }
+                const int kb0 = 2 * gi;
+                int atoms = 0;
+                for (int kb = kb0; kb < kb0 + 2 && kb < k_blocks; ++kb) atoms += (kb == k_blocks - 1) ? p.last_atoms : 4;
+                const uint32_t bytes = (uint32_t)atoms * 512u;
+                const uint32_t bar = sfl0 + 8 * st;
+                if (p.debug & 8) {
+                    if (lane == 0) mbar_arrive(bar);
+                } else {
+                    if (lane == 0) mbar_expect_tx(bar, bytes * parts);
+                    __syncwarp();
+                    if (my_ok)
+                        bulk_load(sf_base + st * C::SF_STAGE_BYTES + (uint32_t)lane * C::SF_PART,
+                                  my_src + (int64_t)kb0 * 2048, bytes, bar);
+                }
+            }
+        }
+        if (!ok && lane == 0) {
             const long long t0 = clock64();
             while (clock64() - t0 < 4000000ll) {}
         }
