@@ -850,7 +850,8 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int dev, cudaSt
     if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
     p.stages = DuoCfg::OP_STAGES;
     if (!st->duo_attr_set) {
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
         st->duo_attr_set = true;
     }
     const int64_t tiles = ((p.M + DuoCfg::TILE_M - 1) / DuoCfg::TILE_M) * ((p.N + DuoCfg::TILE_N - 1) / DuoCfg::TILE_N);
@@ -867,7 +868,9 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int dev, cudaSt
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_duo_kernel, plan.tmW, plan.tmA, *tm_out, p);
+    // the instantiation with the test hooks runs only while a debug mask is set
+    cudaError_t e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<true>, plan.tmW, plan.tmA, *tm_out, p)
+                            : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<false>, plan.tmW, plan.tmA, *tm_out, p);
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: two-CTA GEMM launch failed: %s\n", cudaGetErrorString(e));
         return TFP4_ERR_LAUNCH;

@@ -159,50 +159,61 @@ __device__ __forceinline__ void duo_put32(const float (&f)[32], uint32_t row_add
                      __float_as_uint(f[4 * c + 2]), __float_as_uint(f[4 * c + 3]));
 }
 
-// One full K block of the two-CTA MMA stream in a single statement: four MMAs (K = 64 each,
+// One K block of the two-CTA MMA stream in a single statement: up to four MMAs (K = 64 each,
 // operands 32 bytes further into the 128-byte swizzle span each time, so only the low descriptor
-// word changes), the look-ahead polls of the next K block's two barriers between them, and the
-// commit that frees the stage in both CTAs.  The issuing warp is one thread of control with no
-// instruction-level parallelism to speak of, about five cycles per instruction: every instruction
-// between two MMAs counts, so nothing is recomputed here that the caller can keep in a register.
-// Returns 1 if both polled barriers had completed the polled phase.
-__device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate, uint32_t d, uint32_t a_lo, uint32_t b_lo,
-                                               uint32_t desc_hi, uint32_t sf, uint32_t full_next, uint32_t sf_next,
-                                               uint32_t par_next, uint32_t empty_bar) {
+// word changes), the look-ahead polls of the next K block's two barriers between them, the commit
+// that frees the stage in both CTAs and, after a tile's last K block, the commit that hands the
+// accumulator to the epilogue.  The issuing warp is a single thread of control, four to five cycles
+// per dependent instruction and about fifteen per branch, and the tensor pipe runs only about one
+// MMA ahead of it: whatever the warp executes per K block beyond ~500 cycles is lost MMA time, so
+// nothing is recomputed or branched on here that the caller can hand over in a register.
+// n_mma: MMAs to issue (4, or fewer in a ragged last K block).  Returns 1 if both polled barriers
+// had completed the polled phase.
+__device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last,
+                                               uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t sf,
+                                               uint32_t full_next, uint32_t sf_next, uint32_t par_next,
+                                               uint32_t empty_bar, uint32_t tfull_bar) {
     uint32_t ready;
     asm volatile(
         "{\n\t"
-        ".reg .pred q, pa, pt, pf, ps;\n\t"
+        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
         ".reg .b16 m;\n\t"
         ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g0, g1, g2, g3;\n\t"
         ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
         "setp.ne.b32 q, %1, 0;\n\t"
         "setp.ne.b32 pa, %2, 0;\n\t"
+        "setp.gt.and.u32 q0, %3, 0, q;\n\t"
+        "setp.gt.and.u32 q1, %3, 1, q;\n\t"
+        "setp.gt.and.u32 q2, %3, 2, q;\n\t"
+        "setp.gt.and.u32 q3, %3, 3, q;\n\t"
+        "setp.ne.and.b32 ql, %4, 0, q;\n\t"
         "setp.eq.b32 pt, 0, 0;\n\t"
         "mov.b16 m, 3;\n\t"
-        "add.u32 a1, %4, 2;\n\tadd.u32 a2, %4, 4;\n\tadd.u32 a3, %4, 6;\n\t"
-        "add.u32 b1, %5, 2;\n\tadd.u32 b2, %5, 4;\n\tadd.u32 b3, %5, 6;\n\t"
-        "mov.b64 da0, {%4, %6};\n\tmov.b64 da1, {a1, %6};\n\tmov.b64 da2, {a2, %6};\n\tmov.b64 da3, {a3, %6};\n\t"
-        "mov.b64 db0, {%5, %6};\n\tmov.b64 db1, {b1, %6};\n\tmov.b64 db2, {b2, %6};\n\tmov.b64 db3, {b3, %6};\n\t"
-        "add.u32 f1, %7, 4;\n\tadd.u32 f2, %7, 8;\n\tadd.u32 f3, %7, 12;\n\t"
-        "add.u32 g0, %7, 16;\n\tadd.u32 g1, %7, 24;\n\tadd.u32 g2, %7, 32;\n\tadd.u32 g3, %7, 40;\n\t"
-        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da0, db0, %12, [%7], [g0], pa;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%8], %10;\n\t"
-        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da1, db1, %12, [f1], [g1], pt;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%9], %10;\n\t"
-        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da2, db2, %12, [f2], [g2], pt;\n\t"
-        "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%3], da3, db3, %12, [f3], [g3], pt;\n\t"
-        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%11], m;\n\t"
+        "add.u32 a1, %6, 2;\n\tadd.u32 a2, %6, 4;\n\tadd.u32 a3, %6, 6;\n\t"
+        "add.u32 b1, %7, 2;\n\tadd.u32 b2, %7, 4;\n\tadd.u32 b3, %7, 6;\n\t"
+        "mov.b64 da0, {%6, %8};\n\tmov.b64 da1, {a1, %8};\n\tmov.b64 da2, {a2, %8};\n\tmov.b64 da3, {a3, %8};\n\t"
+        "mov.b64 db0, {%7, %8};\n\tmov.b64 db1, {b1, %8};\n\tmov.b64 db2, {b2, %8};\n\tmov.b64 db3, {b3, %8};\n\t"
+        "add.u32 f1, %9, 4;\n\tadd.u32 f2, %9, 8;\n\tadd.u32 f3, %9, 12;\n\t"
+        "add.u32 g0, %9, 16;\n\tadd.u32 g1, %9, 24;\n\tadd.u32 g2, %9, 32;\n\tadd.u32 g3, %9, 40;\n\t"
+        "@q0 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %15, [%9], [g0], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %12;\n\t"
+        "@q1 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %15, [f1], [g1], pt;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%11], %12;\n\t"
+        "@q2 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %15, [f2], [g2], pt;\n\t"
+        "@q3 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %15, [f3], [g3], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], m;\n\t"
+        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%14], m;\n\t"
         "and.pred pf, pf, ps;\n\t"
         "selp.u32 %0, 1, 0, pf;\n\t"
         "}"
         : "=r"(ready)
-        : "r"(on), "r"(accumulate), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf), "r"(full_next), "r"(sf_next),
-          "r"(par_next), "r"(empty_bar), "n"(DuoCfg::IDESC)
+        : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf),
+          "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
         : "memory");
     return ready;
 }
 
+template <bool DBG>
 __global__ void __launch_bounds__(DUO_THREADS, 1)
 gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                 const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
@@ -262,11 +273,15 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const int grans = (k_blocks + 1) >> 1;                   // scale granules (two K blocks) per tile
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
     const uint32_t sfl0 = smem_u32(sfl_bar), sfree0 = smem_u32(sfree_bar), sffull0 = smem_u32(sffull_bar);
-    const bool prof = (p.debug & 1024) != 0;
+    // test hooks (tfp4_set_debug) exist only in the DBG instantiation; the production one carries none of their branches
+    const int dbg = DBG ? p.debug : 0;
+    const bool prof = DBG && (dbg & 1024) != 0;
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (both CTAs)
-        uint32_t s = 0, ph = 0;
+        // Every role walks the stage ring continuously across tiles and keeps one phase bit per stage,
+        // toggled on each use of the stage.
+        uint32_t pmask = 0, s = 0;
         bool ok = true;
         long long c_wait = 0;
         const CUtensorMap* my_map = (lane == 0) ? &tmX : &tmW;
@@ -275,11 +290,13 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
             const int my_y = (lane == 0) ? (int)(mt * C::TILE_M + rank * 128) : (int)(nt * C::TILE_N + rank * 128);
             for (int kb = 0; kb < k_blocks; ++kb) {
+                const uint32_t ph = (pmask >> s) & 1u;
+                pmask ^= 1u << s;
                 const long long t0 = prof ? clock64() : 0;
                 if (!mbar_wait_sleep(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
                 if (prof) c_wait += clock64() - t0;
                 const uint32_t bar = full0 + 8 * s;
-                if (p.debug & 8) {
+                if (dbg & 8) {
                     if (lane == 0) mbar_arrive(bar);
                 } else {
                     // rows or K bytes outside the tensors are zero-filled and still counted in full
@@ -287,7 +304,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     __syncwarp();
                     if (lane < 2) tma_load_2d(my_dst + s * C::X_BYTES, my_map, kb * KB_BYTES, my_y, bar);
                 }
-                if (++s == C::OP_STAGES) { s = 0; ph ^= 1u; }
+                if (++s == C::OP_STAGES) s = 0;
             }
         }
         if (prof && lane == 0 && !leader && p.stats != nullptr && blockIdx.x < 256) p.stats[blockIdx.x * 4 + 0] = (unsigned long long)c_wait;
@@ -300,76 +317,75 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if (leader) {
             // -------------------------------------------------------- MMA issuer
             // The warp walks the loop together (uniform control flow keeps the operands in uniform
-            // registers); lane 0's instructions are the ones that take effect.  Per K block: one
-            // statement with the four MMAs, the polls of the next K block's barriers and the commit
-            // (duo_kblock); the blocking, bounded wait is only the fallback when a poll failed.
-            uint32_t s = 0, ph = 0, tcount = 0;
+            // registers); lane 0's instructions are the ones that take effect.  The K loop is unrolled
+            // over the five stages, so every address below is a base register plus a constant.  Per K
+            // block: one statement with the MMAs, the polls of the next K block's barriers and the
+            // commits (duo_kblock); the blocking, bounded wait is only the fallback when a poll failed.
+            uint32_t mmask = 0, tcount = 0;                  // phase bit per stage; tiles done
+            int s_start = 0;                                 // stage of the tile's first K block
             const uint32_t on = (lane == 0) ? 1u : 0u;
+            const uint32_t full_mma = (dbg & 4) ? 0u : 4u;   // test hook: no MMAs, commits only
             bool ok = true, peek = false;
             const uint64_t adesc_base = desc_sw128(smem_u32(sX)), bdesc_base = desc_sw128(smem_u32(sWh));
             const uint32_t desc_hi = (uint32_t)(adesc_base >> 32);
             const uint32_t a_lo0 = (uint32_t)adesc_base, b_lo0 = (uint32_t)bdesc_base;
             const uint32_t sf0 = tmem_base + C::SF_COL;
-            long long c_acc = 0, c_wait = 0, c_blk = 0;
+            const uint32_t tfull_a = smem_u32(tfull_bar);
+            const uint32_t last_atoms = (dbg & 4) ? 0u : (uint32_t)p.last_atoms;
+            long long c_acc = 0, c_wait = 0;
             uint32_t n_miss = 0;
             const long long c_begin = clock64();
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 const long long ta = prof ? clock64() : 0;
                 if (!mbar_wait(smem_u32(tempty_bar), (tcount & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
                 if (prof) c_acc += clock64() - ta;
-                tc_fence_after();
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!peek) {
-                        // scales of this K block are in tensor memory of both CTAs; operands of both CTAs landed
-                        const long long t0 = prof ? clock64() : 0;
-                        if (!mbar_wait(sffull0 + 8 * s, ph, abort_flag, 5)) { ok = false; break; }
-                        if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 3)) { ok = false; break; }
-                        if (prof) { c_wait += clock64() - t0; ++n_miss; }
+                // K block kb sits in stage (s_start + kb) % OP_STAGES: walk the unrolled ring, entering at s_start
+                for (int base = -s_start; base < k_blocks && ok; base += C::OP_STAGES) {
+#pragma unroll
+                    for (int u = 0; u < C::OP_STAGES; ++u) {
+                        const int kb = base + u;
+                        if ((unsigned)kb < (unsigned)k_blocks) {
+                            const uint32_t ph = (mmask >> u) & 1u;
+                            mmask ^= 1u << u;
+                            if (!peek) {
+                                // scales of this K block are in tensor memory of both CTAs; operands of both CTAs landed
+                                const long long t0 = prof ? clock64() : 0;
+                                if (!mbar_wait(sffull0 + 8 * u, ph, abort_flag, 5)) { ok = false; break; }
+                                if (!mbar_wait(full0 + 8 * u, ph, abort_flag, 3)) { ok = false; break; }
+                                if (prof) { c_wait += clock64() - t0; ++n_miss; }
+                            }
+                            tc_fence_after();
+                            const bool last = kb + 1 == k_blocks;
+                            const int un = (u + 1) % C::OP_STAGES;         // the next K block's stage (also across tiles)
+                            const uint32_t ready =
+                                duo_kblock(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
+                                           a_lo0 + u * (C::X_BYTES >> 4), b_lo0 + u * (C::W_BYTES >> 4), desc_hi,
+                                           sf0 + u * TMEM_SF_SLOT_COLS, full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u,
+                                           empty0 + 8 * u, tfull_a);
+                            peek = __all_sync(0xffffffffu, ready != 0u) && !(dbg & 32);
+                        }
                     }
-                    if (!(p.debug & 64)) tc_fence_after();
-                    const bool last = kb == k_blocks - 1;
-                    const uint32_t s_n = (s + 1 == C::OP_STAGES) ? 0u : s + 1;
-                    const uint32_t ph_n = (s + 1 == C::OP_STAGES) ? ph ^ 1u : ph;
-                    const uint32_t a_lo = a_lo0 + s * (C::X_BYTES >> 4), b_lo = b_lo0 + s * (C::W_BYTES >> 4);
-                    const uint32_t sf = sf0 + s * TMEM_SF_SLOT_COLS;
-                    uint32_t ready;
-                    if ((!last || p.last_atoms == 4) && !(p.debug & 4)) {
-                        const long long tb = prof ? clock64() : 0;
-                        ready = duo_kblock(on, kb > 0 ? 1u : 0u, tmem_base, a_lo, b_lo, desc_hi, sf, full0 + 8 * s_n,
-                                           sffull0 + 8 * s_n, ph_n, empty0 + 8 * s);
-                        if (prof) c_blk += clock64() - tb;
-                    } else {
-                        // ragged last K block (or MMAs switched off by the test hook)
-                        const uint64_t adesc = ((uint64_t)desc_hi << 32) | a_lo, bdesc = ((uint64_t)desc_hi << 32) | b_lo;
-                        const uint32_t m_on = (p.debug & 4) ? 0u : on;
-                        for (int j = 0; j < p.last_atoms || (!last && j < 4); ++j)
-                            tc_mma_pair_if<0>(m_on, tmem_base, adesc + 2 * j, bdesc + 2 * j, C::IDESC, sf + 4 * j,
-                                              sf + TMEM_SFA_OFF + 8 * j, (kb > 0 || j > 0) ? 1u : 0u);
-                        tc_commit_pair_if(on, empty0 + 8 * s);
-                        ready = (mbar_test_wait(full0 + 8 * s_n, ph_n) && mbar_test_wait(sffull0 + 8 * s_n, ph_n)) ? 1u : 0u;
-                    }
-                    if (last) tc_commit_pair_if(on, smem_u32(tfull_bar));   // accumulator ready in both CTAs
-                    peek = __all_sync(0xffffffffu, ready != 0u) && !(p.debug & 32);
-                    s = s_n; ph = ph_n;
                 }
+                s_start = (s_start + k_blocks) % C::OP_STAGES;
             }
             if (prof && lane == 0 && p.stats != nullptr && blockIdx.x < 256) {
                 p.stats[blockIdx.x * 4 + 0] = (unsigned long long)(clock64() - c_begin);
                 p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_wait;
                 p.stats[blockIdx.x * 4 + 2] = (unsigned long long)n_miss;
                 p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_acc;
-                p.stats[600 + blockIdx.x] = (unsigned long long)c_blk;
             }
         } else {
             // -------------------------------------------------------- relay (peer CTA)
-            uint32_t s = 0, ph = 0;
+            uint32_t rmask = 0, s = 0;
             bool ok = true;
             const uint32_t full0_leader = map_to_cta(full0, 0);
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
                 for (int kb = 0; kb < k_blocks; ++kb) {
+                    const uint32_t ph = (rmask >> s) & 1u;
+                    rmask ^= 1u << s;
                     if (!mbar_wait_sleep(full0 + 8 * s, ph, abort_flag, 9)) { ok = false; break; }
                     if (lane == 0) mbar_arrive_cluster_relaxed(full0_leader + 8 * s);
-                    if (++s == C::OP_STAGES) { s = 0; ph ^= 1u; }
+                    if (++s == C::OP_STAGES) s = 0;
                 }
             }
         }
@@ -409,7 +425,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        if (row0 < p.M && n0 + c0 < p.N && !(p.debug & 1)) tma_store_2d(&tmO, (int)((n0 + c0) * 4), (int)row0, buf);
+                        if (row0 < p.M && n0 + c0 < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)((n0 + c0) * 4), (int)row0, buf);
                         bulk_commit_group();
                     }
                     ++nstore;
@@ -437,7 +453,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     // lies outside altogether still closes an (empty) group, so that "all but the latest
                     // group" always names the store that last used the other buffer
                     const int64_t nn = n0 + c0 + (esize == 2 ? 0 : 32);
-                    if (row0 < p.M && nn < p.N && !(p.debug & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
+                    if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
                     bulk_commit_group();
                 }
                 ++nstore;
@@ -447,7 +463,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     } else if (warp < 10) {
         // ------------------------------------------------------------ scale loaders (warps 6..9, both CTAs)
         const int q = warp & 3;
-        uint32_t g = 0, it = 0, slot = 0, sph = 0;           // granule counter; K block counter, its slot and slot phase
+        uint32_t g = 0, lmask = 0, slot = 0;                 // granule counter; phase bits of the scale slots; slot = stage of the next K block
         bool ok = true;
         const bool profl = prof && warp == 6 && !leader;
         long long c_sfl = 0, c_empty = 0, c_st = 0;
@@ -474,15 +490,18 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
                     if (b < nkb) {
-                        if (it >= (uint32_t)C::NSLOT) {
-                            // the slot is free once the MMAs of the K block NSLOT back (same ring index) are done
+                        {
+                            // the slot is free once the MMAs of the K block that used this stage last are done
+                            // (a stage never used yet passes at once: the barrier's fresh phase counts as odd)
+                            const uint32_t sph = (lmask >> slot) & 1u;
+                            lmask ^= 1u << slot;
                             t0 = profl ? clock64() : 0;
                             if (!mbar_wait_sleep(empty0 + 8 * slot, sph ^ 1u, abort_flag, 7)) { ok = false; break; }
                             if (profl) c_empty += clock64() - t0;
                         }
                         tc_fence_after();
                         t0 = profl ? clock64() : 0;
-                        if (!(p.debug & 2)) {
+                        if (!(dbg & 2)) {
                             const uint32_t t_base = t_q + slot * TMEM_SF_SLOT_COLS;
                             tc_st<16>(t_base, va + 16 * b);
                             // feature-side scales: MMA j reads 8 columns, rows 0-127 then rows 128-255
@@ -502,8 +521,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster_relaxed(sffull_leader + 8 * slot);
                         if (profl) c_st += clock64() - t0;
-                        ++it;
-                        if (++slot == (uint32_t)C::NSLOT) { slot = 0; sph ^= 1u; }
+                        if (++slot == (uint32_t)C::NSLOT) slot = 0;
                     }
                 }
             }
@@ -535,7 +553,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 for (int kb = kb0; kb < kb0 + 2 && kb < k_blocks; ++kb) atoms += (kb == k_blocks - 1) ? p.last_atoms : 4;
                 const uint32_t bytes = (uint32_t)atoms * 512u;
                 const uint32_t bar = sfl0 + 8 * st;
-                if (p.debug & 8) {
+                if (dbg & 8) {
                     if (lane == 0) mbar_arrive(bar);
                 } else {
                     if (lane == 0) mbar_expect_tx(bar, bytes * parts);
