@@ -41,7 +41,14 @@ def parse():
     ap.add_argument("--inter", type=int, default=28672, help="mlp workload: intermediate size")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--ablate", action="store_true",
+                    help="time the GEMM with parts of the kernel switched off through the library's test hooks and print a table")
+    ap.add_argument("--profile", action="store_true",
+                    help="short run for a profiler: no CPU leg, no end-to-end leg, no sustained-load clock sampling")
+    args = ap.parse_args()
+    if args.profile:
+        args.no_cpu = args.no_e2e = True
+    return args
 
 
 def peaks():
@@ -175,6 +182,41 @@ def run_reference(args):
     }))
 
 
+def run_ablation(args):
+    """GEMM alone on fixed NVFP4 operands with parts of gemm_duo_kernel switched off (tfp4_set_debug masks:
+    1 no global stores, 2 no scale stores to tensor memory, 4 no MMAs, 8 no loads, 32 no look-ahead polls)."""
+    import thor_fp4
+    from thor_fp4 import _ext, ops
+    torch.cuda.set_device(0)
+    M, N, K = args.M, args.N, args.K
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda") * 0.02
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    L = _ext.device_lib()
+    cases = [(0, "full"), (32, "no look-ahead polls"), (1, "no global stores"), (2, "no scale stores to tensor memory"),
+             (8, "no loads"), (8 | 2 | 1, "MMAs + barrier protocol only"), (4 | 8 | 2 | 1, "barrier protocol only"), (0, "full again")]
+    try:
+        for mask, name in cases:
+            L.tfp4_set_debug(mask)
+            for _ in range(3):
+                ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, "bf16")
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, "bf16")
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / args.steps * 1e3
+            print(f"| {name} | {mask} | {us:.1f} | {2.0 * M * N * K / us / 1e6:.0f} |", flush=True)
+    finally:
+        L.tfp4_set_debug(0)
+    if _ext.status() != 0:
+        raise RuntimeError(f"device status word {_ext.status()}")
+
+
 def workload_name(args):
     return (f"thor_fp4.Linear({args.K},{args.N},bias=False,out_dtype=bf16), activation bf16 [{args.M},{args.K}] ~N(0,1), "
             "weight Kaiming-uniform fp32 quantized once (two-level NVFP4); step = activation quantize + block-scaled GEMM")
@@ -242,7 +284,7 @@ def run_ours(args):
     # step running (untimed) until the sampler has seen about half a second of this load
     t_load = time.perf_counter()
     i = args.steps
-    while time.perf_counter() - t_load < 0.5:
+    while not args.profile and time.perf_counter() - t_load < 0.5:
         for _ in range(20):
             step(i)
             i += 1
@@ -304,7 +346,9 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "kernel": "gemm_duo_kernel (tcgen05 cta_group::2 NVFP4 block-scaled GEMM, 256x256 tiles)",
                      "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
                      "peak_note": f"4 x {pk['src']} bf16 burst ({pk['bf16']}); no FP4 peak is measured on this pool",
-                     "frac_of_nominal_9000": gemm_tflops / 9000.0, "traffic": None,
+                     "frac_of_nominal_9000": gemm_tflops / 9000.0,
+                     # dram__bytes_read + dram__bytes_write of one launch at 8192^3 (ncu capture summarised under profiles/)
+                     "traffic": 208.0e6 if (M, N, K) == (8192, 8192, 8192) else None,
                      "avg_launch_ms": g_ms},
         "roofline_quantizer": {"bound": "hbm", "kernel": "quant_nvfp4_kernel", "achieved": q_gbs,
                                "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": q_gbs / pk["hbm_gbs"],
@@ -331,6 +375,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the engine has no CPU fallback (use --impl reference for the CPU arm)")
+    if args.ablate:
+        run_ablation(args)
+        return
     run_ours(args)
 
 

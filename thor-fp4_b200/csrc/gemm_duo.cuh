@@ -307,7 +307,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 if (++s == C::OP_STAGES) s = 0;
             }
         }
-        if (prof && lane == 0 && !leader && p.stats != nullptr && blockIdx.x < 256) p.stats[blockIdx.x * 4 + 0] = (unsigned long long)c_wait;
+        
         if (!ok && lane == 0) {
             // let copies already issued land before the CTA's shared memory goes away
             const long long t0 = clock64();
@@ -332,13 +332,14 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const uint32_t sf0 = tmem_base + C::SF_COL;
             const uint32_t tfull_a = smem_u32(tfull_bar);
             const uint32_t last_atoms = (dbg & 4) ? 0u : (uint32_t)p.last_atoms;
-            long long c_acc = 0, c_wait = 0;
+            long long c_acc = 0, c_wait = 0, s_obs = 0, s_commit = 0;
             uint32_t n_miss = 0;
             const long long c_begin = clock64();
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 const long long ta = prof ? clock64() : 0;
                 if (!mbar_wait(smem_u32(tempty_bar), (tcount & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
                 if (prof) c_acc += clock64() - ta;
+                if (prof && tcount > 0) s_obs += clock64();
                 // K block kb sits in stage (s_start + kb) % OP_STAGES: walk the unrolled ring, entering at s_start
                 for (int base = -s_start; base < k_blocks && ok; base += C::OP_STAGES) {
 #pragma unroll
@@ -367,12 +368,15 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     }
                 }
                 s_start = (s_start + k_blocks) % C::OP_STAGES;
+                if (prof && tile + stride < total_tiles) s_commit += clock64();
             }
             if (prof && lane == 0 && p.stats != nullptr && blockIdx.x < 256) {
                 p.stats[blockIdx.x * 4 + 0] = (unsigned long long)(clock64() - c_begin);
                 p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_wait;
                 p.stats[blockIdx.x * 4 + 2] = (unsigned long long)n_miss;
                 p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_acc;
+                p.stats[600 + blockIdx.x * 2] = (unsigned long long)s_commit;
+                p.stats[600 + blockIdx.x * 2 + 1] = (unsigned long long)s_obs;
             }
         } else {
             // -------------------------------------------------------- relay (peer CTA)
@@ -393,6 +397,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
         const int q = warp & 3;                              // tensor-memory lane quarter this warp may read
         uint32_t tcount = 0, nstore = 0;
+        long long s_wake = 0, s_rel = 0, e_ld = 0, e_rd = 0, e_cv = 0, e_fn = 0;
         bool ok = true;
         const uint32_t tempty_leader = map_to_cta(smem_u32(tempty_bar), 0);
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -401,6 +406,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
             const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
             if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4)) { ok = false; break; }
+            const bool profe = prof && leader && warp == 2 && tile + stride < total_tiles;
+            if (profe) s_wake += clock64();
             tc_fence_after();
             const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
             const int64_t n0 = nt * C::TILE_N;
@@ -410,15 +417,25 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll 1
             for (int c0 = 0; c0 < C::TILE_N; c0 += 64) {
                 // ---- columns c0 .. c0+31 (in va); read c0+32.. into vb
+                long long e0 = profe ? clock64() : 0;
                 tc_wait_ld();
                 tc_ld32(t_lane + (uint32_t)(c0 + 32), vb);
+                long long e1 = profe ? clock64() : 0;
                 uint32_t buf = my_buf + (nstore & 1u) * C::EPI_BUF;
                 uint32_t row_addr = buf + (uint32_t)lane * 128u;
                 float f[32];
                 if (lane == 0) bulk_wait_read_1();           // the store issued from this buffer two slabs ago has read it
                 __syncwarp();
-                duo_scale(va, f, n0 + c0, p.N, p.alpha, p.bias);
-                if (esize == 2) {
+                long long e2 = profe ? clock64() : 0;
+                if (profe) { e_ld += e1 - e0; e_rd += e2 - e1; }
+                if (dbg & 2048) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) st_shared_v4(row_addr + (uint32_t)((c ^ (lane & 7)) << 4), va[4 * c], va[4 * c + 1], va[4 * c + 2], va[4 * c + 3]);
+                } else {
+                    duo_scale(va, f, n0 + c0, p.N, p.alpha, p.bias);
+                }
+                if (dbg & 2048) {
+                } else if (esize == 2) {
                     duo_put16(f, row_addr, 0, lane, p.out_dtype == OUT_BF16);
                 } else {
                     duo_put32(f, row_addr, lane);
@@ -435,6 +452,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     __syncwarp();
                 }
                 // ---- columns c0+32 .. c0+63 (in vb); read c0+64.. into va, or hand the accumulator back
+                long long e3 = profe ? clock64() : 0;
+                if (profe) e_cv += e3 - e2;
                 tc_wait_ld();
                 if (c0 + 64 < C::TILE_N) {
                     tc_ld32(t_lane + (uint32_t)(c0 + 64), va);
@@ -442,12 +461,22 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);
+                    if (profe) s_rel += clock64();
                 }
-                duo_scale(vb, f, n0 + c0 + 32, p.N, p.alpha, p.bias);
-                if (esize == 2) duo_put16(f, row_addr, 4, lane, p.out_dtype == OUT_BF16);
-                else duo_put32(f, row_addr, lane);
+                long long e4 = profe ? clock64() : 0;
+                if (profe) e_ld += e4 - e3;
+                if (dbg & 2048) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) st_shared_v4(row_addr + (uint32_t)(((4 + c) ^ (lane & 7)) << 4), vb[4 * c], vb[4 * c + 1], vb[4 * c + 2], vb[4 * c + 3]);
+                } else {
+                    duo_scale(vb, f, n0 + c0 + 32, p.N, p.alpha, p.bias);
+                    if (esize == 2) duo_put16(f, row_addr, 4, lane, p.out_dtype == OUT_BF16);
+                    else duo_put32(f, row_addr, lane);
+                }
+                long long e5 = profe ? clock64() : 0;
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
+                if (profe) { e_cv += e5 - e4; e_fn += clock64() - e5; }
                 if (lane == 0) {
                     // rows beyond M and bytes beyond the row end are clipped by the copy engine; a slab that
                     // lies outside altogether still closes an (empty) group, so that "all but the latest
@@ -460,12 +489,20 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             }
         }
         if (lane == 0) bulk_wait_all();
+        if (prof && leader && warp == 2 && lane == 0 && p.stats != nullptr && blockIdx.x < 148) {
+            p.stats[876 + (blockIdx.x >> 1) * 2] = (unsigned long long)s_wake;      // 74 leaders x 2 words: 876..1023
+            p.stats[877 + (blockIdx.x >> 1) * 2] = (unsigned long long)s_rel;
+            p.stats[blockIdx.x * 4 + 4] = (unsigned long long)e_ld;     // the peer CTA's words 0..3: unused by its own roles in this slot order
+            p.stats[blockIdx.x * 4 + 5] = (unsigned long long)e_rd;
+            p.stats[blockIdx.x * 4 + 6] = (unsigned long long)e_cv;
+            p.stats[blockIdx.x * 4 + 7] = (unsigned long long)e_fn;
+        }
     } else if (warp < 10) {
         // ------------------------------------------------------------ scale loaders (warps 6..9, both CTAs)
         const int q = warp & 3;
         uint32_t g = 0, lmask = 0, slot = 0;                 // granule counter; phase bits of the scale slots; slot = stage of the next K block
         bool ok = true;
-        const bool profl = prof && warp == 6 && !leader;
+        const bool profl = false;
         long long c_sfl = 0, c_empty = 0, c_st = 0;
         const uint32_t sf_base = smem_u32(sSF);
         const uint32_t sffull_leader = map_to_cta(sffull0, 0);
