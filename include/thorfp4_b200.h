@@ -76,6 +76,14 @@ int tfp4_gemm_bias(const void* packedA, const void* sblkA, float tsA,
                    const float* bias, void* out, int64_t M, int64_t N, int64_t K,
                    int out_dtype, void* stream);
 
+/* Replaces the work between the two GEMMs of the reference's gated MLP (src/thor_fp4/fused.py:163-173:
+ * activation, elementwise product, re-quantization of the hidden tensor; csrc K14 mx8_mul for the MX form)
+ * for the NVFP4 block: gu is the [R, 2*I] f16/bf16 output of the stacked gate/up GEMM (I gate values,
+ * then I up values per row); writes the NVFP4 codes and scale tiles of h = silu(gate) * up (FP32 math,
+ * h rounded to the input type, per-tensor scale 1) exactly as tfp4_quant would from h.  in_dtype 1 f16, 2 bf16. */
+int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype,
+                      uint8_t* packed, uint8_t* sblk, void* stream);
+
 /* No counterpart in the reference.  tfp4_gemm_bias for callers that must not allocate at call time
  * (device memory fully pre-partitioned at start-up, a plug-in under a foreign allocator, a loop
  * that cannot afford the device-wide synchronisation of an allocation or a free): the kernel's scratch - status word, counters, split-K partial sums - sits in a

@@ -1,0 +1,91 @@
+"""GPU checks of the NVFP4 gated MLP (SwiGLU) block through the C ABI: the one-pass
+silu(gate)*up + quantize kernel against the oracle's quantizer applied to the same h, the
+block against a CPU emulation (fake-quantize, double-accumulate matmuls, bf16 intermediates),
+and the fused activation path against the unfused one.
+
+The reference pins the fused-epilogue outputs of its gated block only by loose tolerances
+(tests/test_fused.py:73-76 of the reference project); here h is defined as the unfused block
+holds it - FP32 silu(gate)*up rounded to bf16, per-tensor scale 1 - so the only freedom left is
+the last ulp of expf, which moves a few values across a bf16 rounding boundary."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+gpu = pytest.mark.gpu
+
+
+def _bf16_round(a: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).bfloat16().float().numpy()
+
+
+def _silu_mul(g: np.ndarray, u: np.ndarray) -> np.ndarray:
+    g = g.astype(np.float32)
+    return (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u.astype(np.float32)
+
+
+@gpu
+@pytest.mark.parametrize("R,I", [(300, 192), (1000, 1024), (128, 4096), (257, 64)])
+def test_swiglu_quant_matches_oracle_on_same_h(R, I):
+    from thor_fp4 import ops
+    g = torch.Generator(device="cuda").manual_seed(R + I)
+    gu = (torch.randn(R, 2 * I, device="cuda", generator=g) * 2.0).bfloat16()
+    packed, sblk = ops.swiglu_quantize_nvfp4(gu)
+    torch.cuda.synchronize()
+    guf = gu.float().cpu().numpy()
+    h = _bf16_round(_silu_mul(guf[:, :I], guf[:, I:]))
+    p_ref, s_ref = orc.quantize_nvfp4(h, 1.0, threads=orc.host_threads())
+    got_p, got_s = packed.cpu().numpy(), sblk.cpu().numpy()
+    # an expf that differs in its last bit moves a value across a bf16 boundary now and then: a handful of bytes
+    assert (got_s != s_ref).mean() < 2e-4
+    assert (got_p != p_ref).mean() < 5e-4
+    d_got = orc.dequantize_nvfp4(got_p, got_s, 1.0, R, I)
+    d_ref = orc.dequantize_nvfp4(p_ref, s_ref, 1.0, R, I)
+    assert np.linalg.norm(d_got - d_ref) / np.linalg.norm(d_ref) < 1e-3
+    # rows past R of the last 128-row tile are written as zeros
+    pad = ops.pad_rows(R)
+    assert not got_p[R * I // 2: pad * I // 2].any()
+
+
+@gpu
+def test_swiglu_quant_equals_unfused_path_bytes_mostly():
+    from thor_fp4 import ops
+    R, I = 512, 1536
+    gu = (torch.randn(R, 2 * I, device="cuda") * 1.5).bfloat16()
+    p1, s1 = ops.swiglu_quantize_nvfp4(gu)
+    h = (torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float()).to(torch.bfloat16)
+    p2, s2 = ops.quantize_nvfp4(h, 1.0)
+    torch.cuda.synchronize()
+    assert (p1 != p2).float().mean().item() < 5e-4
+    assert (s1 != s2).float().mean().item() < 2e-4
+
+
+@gpu
+@pytest.mark.parametrize("M", [200, 640])
+def test_nvfp4_gated_mlp_matches_cpu_emulation(M):
+    import thor_fp4
+    from thor_fp4.fused import NVFP4GatedMLP
+    H, I = 256, 512
+    torch.manual_seed(3)
+    mlp = NVFP4GatedMLP(H, I, device="cuda", out_dtype="f32", weight_std=0.05)
+    x = torch.randn(M, H, device="cuda").bfloat16()
+    y = mlp(x).float().cpu().numpy()
+    y_unfused = None
+    mlp.fuse_activation = False
+    y_unfused = mlp(x).float().cpu().numpy()
+    mlp.fuse_activation = True
+    torch.cuda.synchronize()
+    # CPU emulation with the oracle: fake-quantize, double-accumulate, bf16 g/u and h
+    thr = orc.host_threads()
+    wgu = torch.cat([mlp.w_gate.detach(), mlp.w_up.detach()], 0).float().cpu().numpy()
+    wd = mlp.w_down.detach().float().cpu().numpy()
+    xq = orc.nvfp4_fake_quant(x.float().cpu().numpy(), 1.0)
+    wguq = orc.nvfp4_fake_quant(wgu, orc.two_level_scale(wgu))
+    wdq = orc.nvfp4_fake_quant(wd, orc.two_level_scale(wd))
+    gu = _bf16_round(orc.gemm_f64acc(xq, wguq, None, 1.0, threads=thr))
+    h = _bf16_round(_silu_mul(gu[:, :I], gu[:, I:]))
+    ref = orc.gemm_f64acc(orc.nvfp4_fake_quant(h, 1.0), wdq, None, 1.0, threads=thr)
+    err = np.linalg.norm(y - ref) / np.linalg.norm(ref)
+    assert err < 1e-3, err
+    assert np.linalg.norm(y - y_unfused) / np.linalg.norm(y_unfused) < 1e-3

@@ -18,6 +18,7 @@ void gemm_set_token_tile(int);
 void gemm_set_debug(int);
 void gemm_set_pair_mode(int);
 void gemm_set_splits(int);
+int swiglu_quant_nvfp4(const void*, int64_t, int64_t, int, uint8_t*, uint8_t*, cudaStream_t);
 int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
                  int64_t, int, cudaStream_t);
 int gemm_noalloc_status(int);
@@ -110,6 +111,10 @@ int tfc4_gemm(int variant, const void* A, const void* SA, const void* B, const v
     }
     return tfp4::gemm_block_scaled(kVariants[variant].kind, A, SA, B, SB, alpha, nullptr, D, M, N, K,
                                    tfp4::OUT_BF16, S(stream));
+}
+
+int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype, uint8_t* packed, uint8_t* sblk, void* stream) {
+    return tfp4::swiglu_quant_nvfp4(gu, R, I, in_dtype, packed, sblk, S(stream));
 }
 
 int tfp4_gemm_noalloc(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB,

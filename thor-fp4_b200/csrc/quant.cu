@@ -68,7 +68,11 @@ __device__ __forceinline__ float fma_pz(float a, float b) {  // a*b + (+0): maps
 // 3: BRACKET without the tiny-input check (16-bit input and ts <= 128: the smallest non-zero
 // input, 2^-133, divided by the largest ds, 448 * 128, stays far above the 2^-150 underflow bound).
 // ROWS: rows per CTA, 128 (whole scale atoms) or 64 (half atoms; finer tiles for small grids).
-template <typename T, int MODE, int ROWS>
+// GATED: x is the output [R, 2K] of the stacked gate/up GEMM (row = K gate values, then K up values);
+// the quantized tensor is h = round_to_T(silu(gate) * up), computed in FP32, held in T like the
+// unfused block holds it, and quantized with the same code path (one pass instead of an elementwise
+// kernel with FP32 temporaries followed by the quantizer).
+template <typename T, int MODE, int ROWS, bool GATED = false>
 __global__ void __launch_bounds__(QT_THREADS)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
@@ -76,7 +80,8 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.y * ROWS;
     const int ra = (int)(r0 & 127);                    // first row of this CTA inside its scale atom
-    constexpr int UNROLL = (MODE == 0) ? 4 : 2;        // rows in flight per warp
+    constexpr int UNROLL = (MODE == 0 && !GATED) ? 4 : 2;   // rows in flight per warp
+    const int64_t ld = GATED ? 2 * K : K;              // input row stride in elements
     const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
     const int64_t col = c0 + lane * 8;
     const bool col_ok = col < K;
@@ -87,21 +92,36 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
 
     // warp w handles tile rows w, w+8, ..., w+120, UNROLL rows per step; the raw loads of
     // the next step are issued before the current step is processed (loads always in flight)
-    auto fetch_rows = [&](int it, Raw8<T> (&dst)[UNROLL]) {
+    constexpr int NSRC = GATED ? 2 : 1;
+    auto fetch_rows = [&](int it, Raw8<T> (&dst)[NSRC][UNROLL]) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int64_t r = r0 + warp + 8 * (it + u);
-            dst[u] = (col_ok && r < R) ? fetch8<T>(x + r * K + col) : zero8<T>();
+#pragma unroll
+            for (int g = 0; g < NSRC; ++g)
+                dst[g][u] = (col_ok && r < R) ? fetch8<T>(x + r * ld + g * K + col) : zero8<T>();
         }
     };
-    Raw8<T> cur[UNROLL], nxt[UNROLL];
+    Raw8<T> cur[NSRC][UNROLL], nxt[NSRC][UNROLL];
     fetch_rows(0, cur);
 #pragma unroll 1
     for (int it = 0; it < ROWS / 8; it += UNROLL) {
         if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, nxt);
         float f[UNROLL][8];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) widen8(cur[u], f[u]);
+        for (int u = 0; u < UNROLL; ++u) {
+            widen8(cur[0][u], f[u]);
+            if constexpr (GATED) {
+                float up[8];
+                widen8(cur[NSRC - 1][u], up);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float gte = f[u][i];
+                    const float hv = (gte / (1.0f + expf(-gte))) * up[i];
+                    f[u][i] = static_cast<float>(static_cast<T>(hv));     // h is held in T
+                }
+            }
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int rl = warp + 8 * (it + u);
@@ -151,7 +171,10 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                 *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
         }
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) cur[u] = nxt[u];
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int g = 0; g < NSRC; ++g) cur[g][u] = nxt[g][u];
+        }
     }
     __syncthreads();
     // scale bytes out: whole 512-byte atoms (ROWS == 128) or this CTA's half of each atom
@@ -397,6 +420,31 @@ int launch_quant_mx(const void* x, int64_t R, int64_t K, int kind, uint8_t* pack
 bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
 }  // namespace
+
+// h = silu(gate) * up from the stacked GEMM output gu [R, 2K] (16-bit), quantized to NVFP4 with
+// per-tensor scale 1: codes [R, K/2] and scale tiles exactly as quant_nvfp4 would produce from h.
+int swiglu_quant_nvfp4(const void* gu, int64_t R, int64_t K, int in_dtype, uint8_t* packed, uint8_t* sblk,
+                       cudaStream_t stream) {
+    if (K <= 0 || (K % 64) != 0) {
+        fprintf(stderr, "thor_fp4: intermediate size must be a multiple of 64 (got %ld)\n", (long)K);
+        return TFP4_ERR_BAD_K;
+    }
+    if (R <= 0) return TFP4_OK;
+    if (!gu || !packed || !sblk || (in_dtype != IN_F16 && in_dtype != IN_BF16) || misaligned(gu, 16) ||
+        misaligned(packed, 4) || misaligned(sblk, 8)) {
+        fprintf(stderr, "thor_fp4: tfp4_swiglu_quant needs a 16-byte aligned f16/bf16 input, packed 4-byte, sblk 8-byte aligned\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)(pad128(R) / 128));
+    if (in_dtype == IN_BF16)
+        quant_nvfp4_kernel<__nv_bfloat16, 0, 128, true><<<grid, QT_THREADS, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(gu), R, K, 1.0f, packed, sblk);
+    else
+        quant_nvfp4_kernel<__half, 0, 128, true><<<grid, QT_THREADS, 0, stream>>>(static_cast<const __half*>(gu), R, K, 1.0f,
+                                                                                  packed, sblk);
+    TFP4_CK(cudaGetLastError());
+    return TFP4_OK;
+}
 
 int quant_nvfp4(const void* x, int64_t R, int64_t K, int in_dtype, float ts, uint8_t* packed,
                 uint8_t* sblk, cudaStream_t stream) {

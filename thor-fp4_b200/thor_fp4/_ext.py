@@ -37,6 +37,7 @@ SIGNATURES = {
     "tfp4_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, i64, i64, i64, c_int, c_void]),
     "tfp4_gemm_bias": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
                                i64, i64, i64, c_int, c_void]),
+    "tfp4_swiglu_quant": (c_int, [c_void, i64, i64, c_int, c_void, c_void, c_void]),
     "tfp4_gemm_noalloc": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
                                   i64, i64, i64, c_int, c_void]),
     "tfp4_gemm_noalloc_status": (c_int, [c_int]),

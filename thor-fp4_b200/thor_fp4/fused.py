@@ -198,6 +198,7 @@ class NVFP4GatedMLP(nn.Module):
             else:
                 nn.init.normal_(w, std=weight_std)
         self.tensor_scales: tuple | None = None   # optional (ts_gate_up, ts_down) override
+        self.fuse_activation = True               # False: torch elementwise + separate quantizer (the checker's path)
         self._q = None
         self._bufs: dict = {}
 
@@ -232,7 +233,6 @@ class NVFP4GatedMLP(nn.Module):
                     "xp": torch.zeros(ops.packed_bytes(M, H), dtype=torch.uint8, device=dev),
                     "xs": torch.zeros(ops.scale_bytes(M, H), dtype=torch.uint8, device=dev),
                     "gu": torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev),
-                    "h": torch.empty(M, I, dtype=torch.bfloat16, device=dev),
                     "hp": torch.zeros(ops.packed_bytes(M, I), dtype=torch.uint8, device=dev),
                     "hs": torch.zeros(ops.scale_bytes(M, I), dtype=torch.uint8, device=dev),
                     "y": torch.empty(M, H, dtype=_ext.OUT_TORCH[self.out_dtype], device=dev),
@@ -240,9 +240,12 @@ class NVFP4GatedMLP(nn.Module):
                 self._bufs[key] = b
             ops.quantize_nvfp4(x, 1.0, b["xp"], b["xs"])
             ops.gemm(b["xp"], b["xs"], 1.0, wgu.packed, wgu.sblk, wgu.tensor_scale, b["gu"], M, 2 * I, H, "bf16")
-            h = b["h"]
-            h.copy_(F.silu(b["gu"][:, :I].float()) * b["gu"][:, I:].float())
-            ops.quantize_nvfp4(h, 1.0, b["hp"], b["hs"])
+            if self.fuse_activation:
+                # silu(gate) * up and the re-quantization of h in one pass over the GEMM output
+                ops.swiglu_quantize_nvfp4(b["gu"], b["hp"], b["hs"])
+            else:
+                h = (F.silu(b["gu"][:, :I].float()) * b["gu"][:, I:].float()).to(torch.bfloat16)
+                ops.quantize_nvfp4(h, 1.0, b["hp"], b["hs"])
             y = out if out is not None else b["y"]
             ops.gemm(b["hp"], b["hs"], 1.0, wd.packed, wd.sblk, wd.tensor_scale, y, M, H, I, self.out_dtype)
             return y

@@ -62,6 +62,26 @@ def quantize_nvfp4(x: torch.Tensor, tensor_scale: float = 1.0,
     return packed, sblk
 
 
+def swiglu_quantize_nvfp4(gu: torch.Tensor, packed: torch.Tensor | None = None,
+                          sblk: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """gu = (R, 2*I) f16/bf16 output of the stacked gate/up GEMM -> NVFP4 codes and scale tiles of
+    h = silu(gu[:, :I]) * gu[:, I:] (FP32 math, h held in gu's dtype, per-tensor scale 1), in one pass."""
+    L = _ext.device_lib()
+    _check_2d_cuda(gu)
+    assert gu.dtype in (torch.float16, torch.bfloat16), "stacked gate/up tensor must be f16 or bf16"
+    R, two_i = gu.shape
+    I = two_i // 2
+    assert two_i == 2 * I and I % 64 == 0, f"intermediate size {I} must be a multiple of 64"
+    if packed is None:
+        packed = torch.zeros(packed_bytes(R, I), dtype=torch.uint8, device=gu.device)
+    if sblk is None:
+        sblk = torch.zeros(scale_bytes(R, I), dtype=torch.uint8, device=gu.device)
+    rc = L.tfp4_swiglu_quant(gu.data_ptr(), R, I, _ext.IN_DTYPE[gu.dtype], packed.data_ptr(), sblk.data_ptr(),
+                             _ext.stream())
+    assert rc == 0, f"tfp4_swiglu_quant rc={rc}"
+    return packed, sblk
+
+
 def quantize_mx(x: torch.Tensor, kind: str = "mxfp4",
                 packed: torch.Tensor | None = None,
                 sblk: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
