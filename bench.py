@@ -217,6 +217,67 @@ def run_ablation(args):
         raise RuntimeError(f"device status word {_ext.status()}")
 
 
+def run_mlp(args):
+    """--workload mlp: the NVFP4 SwiGLU block (hidden --K, intermediate --inter, --M tokens), tensor-parallel over the
+    ranks: gate/up split by rows, down by columns, one all-reduce of the f32 partial outputs per step (strong scaling:
+    the block is fixed, each rank holds 1/P of the intermediate dimension)."""
+    import torch.distributed as dist
+    from thor_fp4 import _ext
+    from thor_fp4.parallel import TensorParallelGatedMLP
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    M, H, I = args.M, args.K, args.inter
+    torch.manual_seed(1234 + rank)
+    tp = TensorParallelGatedMLP(H, I, device=dev, reduce_dtype="f32" if world > 1 else "bf16", weight_std=0.02)
+    tp.local.refresh_weight()
+    xs = [torch.randn(M, H, device=dev).bfloat16() for _ in range(2)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for i in range(max(3, args.warmup)):
+        tp(xs[i % 2])
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a.record()
+    for i in range(args.steps):
+        tp(xs[i % 2])
+    b.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if _ext.status() != 0:
+        raise RuntimeError(f"device status word {_ext.status()}")
+    if rank == 0:
+        ms = float(t[0]) / args.steps
+        flop = 6.0 * M * H * I
+        pk = peaks()
+        print(json.dumps({
+            "metric": "NVFP4 SwiGLU MLP block TFLOPS (hidden 8192, intermediate 28672, 16384 tokens)", "value": flop / (ms * 1e-3) / 1e12,
+            "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": {"workload": f"NVFP4 gated MLP: x bf16 [{M},{H}] -> quantize -> [Wg;Wu] GEMM ({2 * I // world} rows per rank) -> "
+                                   f"silu*up + quantize -> Wd GEMM (K = {I // world} per rank) -> "
+                                   + ("all-reduce of f32 partials (NCCL)" if world > 1 else "bf16 out"),
+                       "tensor_parallel": world, "l2": "activations 268 MB and the 1.9 GB gate/up output exceed the 126 MB L2"},
+            "per_gpu_frac_of_4x_bf16_burst": flop / world / (ms * 1e-3) / 1e12 / (4.0 * pk["bf16"]),
+            "gpu_launches": 5 * args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def workload_name(args):
     return (f"thor_fp4.Linear({args.K},{args.N},bias=False,out_dtype=bf16), activation bf16 [{args.M},{args.K}] ~N(0,1), "
             "weight Kaiming-uniform fp32 quantized once (two-level NVFP4); step = activation quantize + block-scaled GEMM")
@@ -377,6 +438,11 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the engine has no CPU fallback (use --impl reference for the CPU arm)")
     if args.ablate:
         run_ablation(args)
+        return
+    if args.workload == "mlp":
+        if args.M == 8192 and args.K == 8192 and args.N == 8192:
+            args.M = 16384          # the block's own default batch
+        run_mlp(args)
         return
     run_ours(args)
 

@@ -56,9 +56,12 @@ class TensorParallelGatedMLP(nn.Module):
     `group` defaults to the world group."""
 
     def __init__(self, hidden: int, intermediate: int, group=None, device=None,
-                 reduce_dtype: str = "f32", weight_std: float | None = 0.02, local: nn.Module | None = None):
+                 reduce_dtype: str = "f32", weight_std: float | None = 0.02, local: nn.Module | None = None,
+                 chunks: int = 4):
         super().__init__()
         self.group = group
+        self.chunks = max(1, int(chunks))     # token chunks: the all-reduce of one overlaps the GEMMs of the next
+        self._y: dict = {}
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         a, b = _bounds(intermediate, self.world, self.rank, 64)
@@ -78,7 +81,31 @@ class TensorParallelGatedMLP(nn.Module):
         return self
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = self.local(x)
-        if self.world > 1:
+        if self.world == 1:
+            return self.local(x)
+        M = x.shape[0]
+        n = self.chunks if (M >= 256 * self.chunks and x.is_cuda) else 1
+        if n == 1:
+            y = self.local(x)
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            return y
+        # The partial outputs are summed chunk by chunk: NCCL runs on its own stream, ordered after
+        # the chunk's GEMMs, while this stream goes on with the next chunk.
+        step = -(-M // n)
+        step = -(-step // 256) * 256
+        first = self.local(x[:step])
+        y = self._y.get((M, first.dtype))
+        if y is None:
+            y = torch.empty(M, first.shape[1], dtype=first.dtype, device=first.device)
+            self._y[(M, first.dtype)] = y
+        works = []
+        for r0 in range(0, M, step):
+            r1 = min(M, r0 + step)
+            if r0 == 0:
+                y[:r1].copy_(first)
+            else:
+                self.local(x[r0:r1], out=y[r0:r1])
+            works.append(dist.all_reduce(y[r0:r1], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        for w in works:
+            w.wait()
         return y
