@@ -34,7 +34,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quant", "gemm", "mlp"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "mlp", "sweep"])
     ap.add_argument("--M", type=int, default=8192)
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--K", type=int, default=8192)
@@ -215,6 +215,72 @@ def run_ablation(args):
         L.tfp4_set_debug(0)
     if _ext.status() != 0:
         raise RuntimeError(f"device status word {_ext.status()}")
+
+
+def run_sweep(args):
+    """--workload sweep: the shape grids of the reference's benchmark configurations as a markdown table
+    (layer = activation quantize + GEMM through thor_fp4.Linear; median of 3 rounds of --steps calls)."""
+    import thor_fp4
+    from thor_fp4 import ops
+    torch.cuda.set_device(0)
+    torch.manual_seed(0)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        res = []
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            res.append(a.elapsed_time(b) / n * 1e3)
+        return float(np.median(res))
+
+    def outliers(x, frac, mul):
+        k = x.shape[1]
+        ch = torch.randperm(k, device=x.device)[: max(1, int(k * frac))]
+        x[:, ch] *= mul
+        return x
+
+    print("| layer (K -> N) | M | kind | us per call | TFLOPS | weight-stream GB/s |")
+    print("|---|---|---|---|---|---|")
+    grids = [((8192, 8192), [1, 2048, 8192], "bf16", False)]
+    grids += [((k, n), [1, 16, 128, 2048, 8192], "f16", True)
+              for (k, n) in ((4096, 5120), (5120, 20480), (20480, 5120), (8192, 28672), (28672, 8192))]
+    for (K, N), Ms, od, bias in grids:
+        lin = thor_fp4.Linear(K, N, bias=bias, out_dtype=od, device="cuda")
+        if bias:
+            with torch.no_grad():
+                lin.bias.normal_(std=0.01)
+        lin.refresh_weight()
+        for M in Ms:
+            x = outliers(torch.randn(M, K, device="cuda"), 0.005, 30.0).bfloat16()
+            us = timed(lambda: lin(x), args.steps)
+            wbytes = N * K * (0.5 + 1.0 / 16)
+            print(f"| {K} -> {N} | {M} | nvfp4 x nvfp4 ({lin.engine_kind}) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | {wbytes / us / 1e3:.0f} |",
+                  flush=True)
+        del lin
+        torch.cuda.empty_cache()
+    # MXFP8 activations x MXFP4 weights against NVFP4 x NVFP4 on the same data
+    M, K, N = 4096, 8192, 28672
+    x = outliers(torch.randn(M, K, device="cuda"), 0.001, 50.0)
+    w = torch.randn(N, K, device="cuda") * 0.02
+    ref = x @ w.t()
+    a8, w4 = thor_fp4.MXTensor.from_float(x, "mxfp8"), thor_fp4.MXTensor.from_float(w, "mxfp4")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    from thor_fp4 import _ext
+    vmx = _ext.device_lib().tfc4_variant_index(thor_fp4.linear.resolve_mx8_variant(K).encode())
+    us = timed(lambda: ops.gemm_mx(vmx, a8.packed, a8.sblk, w4.packed, w4.sblk, out, M, N, K), args.steps)
+    err = ((out.float() - ref).norm() / ref.norm()).item()
+    print(f"| {K} -> {N} | {M} | mxfp8 x mxfp4 (GEMM only) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | rel. error vs fp32 matmul {err:.4f} |")
+    an, wn = thor_fp4.NVFP4Tensor.from_float(x, 1.0), thor_fp4.NVFP4Tensor.from_float(w, None)
+    us = timed(lambda: ops.gemm(an.packed, an.sblk, 1.0, wn.packed, wn.sblk, wn.tensor_scale, out, M, N, K, "bf16"), args.steps)
+    err = ((out.float() - ref).norm() / ref.norm()).item()
+    print(f"| {K} -> {N} | {M} | nvfp4 x nvfp4 (GEMM only) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | rel. error vs fp32 matmul {err:.4f} |")
 
 
 def run_mlp(args):
@@ -438,6 +504,9 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the engine has no CPU fallback (use --impl reference for the CPU arm)")
     if args.ablate:
         run_ablation(args)
+        return
+    if args.workload == "sweep":
+        run_sweep(args)
         return
     if args.workload == "mlp":
         if args.M == 8192 and args.K == 8192 and args.N == 8192:

@@ -741,13 +741,14 @@ int ensure_device(DeviceState** out, bool with_pinned = true) {
 
 // rows x row_bytes byte matrix, box = 128 bytes x box_rows, 128-byte swizzle
 int encode_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner_elems,
-               uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows) {
+               uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows,
+               CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     cuuint64_t dims[2] = {inner_elems, rows};
     cuuint64_t strides[1] = {row_stride_bytes};
     cuuint32_t box[2] = {box_inner, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         fprintf(stderr, "thor_fp4_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r);
@@ -821,7 +822,8 @@ int launch_pair(DeviceState* st, const Plan& plan, GemmParams& p, int slot, cuda
     return TFP4_OK;
 }
 
-// tensor maps of GEMM outputs (byte view, 128 bytes x 32 rows per store), cached per buffer and shape
+// tensor maps of GEMM outputs (byte view; one store = 32 rows x 32 columns: 64 bytes wide with the 64-byte swizzle
+// for 16-bit outputs, 128 bytes wide with the 128-byte swizzle for f32), cached per buffer and shape
 struct OutKey {
     const void* out; int64_t M, N; int esize; int dev;
     bool operator<(const OutKey& o) const { return std::tie(out, M, N, esize, dev) < std::tie(o.out, o.M, o.N, o.esize, o.dev); }
@@ -833,7 +835,8 @@ int out_map(const CUtensorMap** map, void* out, int64_t M, int64_t N, int esize,
     auto it = g_out_maps.find(key);
     if (it == g_out_maps.end()) {
         CUtensorMap m;
-        int rc = encode_map(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, out, (uint64_t)(N * esize), (uint64_t)M, (uint64_t)(N * esize), 128, 32);
+        int rc = encode_map(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, out, (uint64_t)(N * esize), (uint64_t)M, (uint64_t)(N * esize),
+                            esize == 2 ? 64 : 128, 32, esize == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
         if (g_out_maps.size() > 4096) g_out_maps.clear();
         it = g_out_maps.emplace(key, m).first;

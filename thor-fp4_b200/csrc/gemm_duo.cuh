@@ -17,9 +17,11 @@
 //
 //   warp 0      producer, both CTAs: per K block two TMA loads (own tokens, own feature half)
 //   warp 1      leader: MMA issuer.  peer: relays "my operands landed" to the leader's barrier
-//   warps 2-5   epilogue: tcgen05.ld -> alpha, bias, cast -> swizzled shared memory -> one TMA
-//               store per warp and 128 bytes of output row (32 rows), double buffered; the
-//               accumulator is handed back as soon as its last columns are in registers
+//   warps 2-5,  epilogue, two warps per tensor-memory lane quarter (columns 0-127 and 128-255):
+//   11-14       tcgen05.ld 32 columns -> alpha, bias, cast -> swizzled shared memory -> one TMA store
+//               per warp and 32 x 32 block of the output; the accumulator is handed back as soon as a
+//               warp's last columns are in registers (fma + convert + st.shared of a 128 x 256 tile
+//               take one warp per quarter ~2200 cycles, which no MMA can overlap)
 //   warps 6-9   scale loaders: scale atoms of two K blocks at a time, shared memory ->
 //               registers -> tcgen05.st into the scale slots of tensor memory
 //   warp 10     scale producer: bulk copies of the scale atoms, two K blocks per copy, running
@@ -27,13 +29,13 @@
 // Barriers.  full[s] (leader: own bytes + the peer's relay; peer: own bytes), empty[s] / tfull:
 // local in each CTA, signalled by the leader's tcgen05.commit with a two-CTA mask.  sfl[i]: scale
 // atoms landed (local).  sfree[i]: the four loader warps have read scale stage i (local).
-// sffull[i] / tempty: in the leader, 8 arrivals (4 warps of each CTA).  Every wait is bounded.
+// sffull[i]: in the leader, 8 arrivals (4 loader warps of each CTA); tempty: 16 (8 epilogue warps of each).  Every wait is bounded.
 // The MMA issuer polls with mbarrier.test_wait; every other warp waits with try_wait, which parks
 // the warp: ten warps spinning on shared-memory barriers slow the issuer's own polls down.  Arrivals on the other CTA's barriers are
 // relaxed: a releasing arrive at cluster scope first waits for everything its thread has in
 // flight (bulk copies, global stores), measured at 500-1200 cycles per arrival.
 
-constexpr int DUO_THREADS = 352;
+constexpr int DUO_THREADS = 480;
 
 struct DuoCfg {
     static constexpr int TILE_M = 256, TILE_N = 256;
@@ -45,8 +47,8 @@ struct DuoCfg {
     static constexpr int SF_STAGE_BYTES = 3 * SF_PART;        // own tokens, feature rows 0-127, feature rows 128-255
     static constexpr int NSLOT = 5;                           // scale slots in tensor memory: one per operand stage
     static constexpr int SF_COL = 256;                        // behind the 256 accumulator columns
-    static constexpr int EPI_BUF = 32 * 128;                  // 32 rows x 128 bytes, one TMA store
-    static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF;         // two buffers for each epilogue warp
+    static constexpr int EPI_BUF = 32 * 128;                  // per epilogue warp: 2 x (32 rows x 64 bytes) or 1 x (32 x 128)
+    static constexpr int EPI_BYTES = 8 * EPI_BUF;             // eight epilogue warps
     static constexpr int BAR_BYTES = 512;
     static constexpr int SMEM_BYTES =
         OP_STAGES * (X_BYTES + W_BYTES) + EPI_BYTES + SF_STAGES * SF_STAGE_BYTES + BAR_BYTES + 1024;
@@ -111,8 +113,19 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // at most one of this thread's bulk-store groups may still be reading shared memory
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// two FP32 fused multiply-adds in one instruction (the epilogue's arithmetic is bound by the
+// throughput of its SM partition, not by latency: fewer instructions is what helps)
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c0, float c1) {
+    uint64_t av, bv, cv, dv;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(av) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(bv) : "f"(b));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(cv) : "f"(c0), "f"(c1));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(dv) : "l"(av), "l"(bv), "l"(cv));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(dv));
+}
 // 32 accumulator columns of one token row -> alpha, bias -> floats
 __device__ __forceinline__ void duo_scale(const uint32_t (&v)[32], float (&f)[32], int64_t n, int64_t N, float alpha,
                                           const float* bias) {
@@ -121,14 +134,13 @@ __device__ __forceinline__ void duo_scale(const uint32_t (&v)[32], float (&f)[32
         for (int i = 0; i < 32; i += 4) {
             float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
             if (n + i + 4 <= N) b = __ldg(reinterpret_cast<const float4*>(bias + n + i));
-            f[i] = fmaf(alpha, __uint_as_float(v[i]), b.x);
-            f[i + 1] = fmaf(alpha, __uint_as_float(v[i + 1]), b.y);
-            f[i + 2] = fmaf(alpha, __uint_as_float(v[i + 2]), b.z);
-            f[i + 3] = fmaf(alpha, __uint_as_float(v[i + 3]), b.w);
+            fma2(f[i], f[i + 1], __uint_as_float(v[i]), __uint_as_float(v[i + 1]), alpha, b.x, b.y);
+            fma2(f[i + 2], f[i + 3], __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]), alpha, b.z, b.w);
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) f[i] = fmaf(alpha, __uint_as_float(v[i]), 0.f);
+        for (int i = 0; i < 32; i += 2)
+            fma2(f[i], f[i + 1], __uint_as_float(v[i]), __uint_as_float(v[i + 1]), alpha, 0.f, 0.f);
     }
 }
 // 32 columns as 16-bit values: four 16-byte chunks of a 128-byte row, chunk index XOR (row & 7)
@@ -151,6 +163,28 @@ __device__ __forceinline__ void duo_put16(const float (&f)[32], uint32_t row_add
 #pragma unroll
     for (int c = 0; c < 4; ++c)
         st_shared_v4(row_addr + (uint32_t)(((chunk0 + c) ^ (row & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+}
+// 32 columns as 16-bit values into a 32-row x 64-byte block: four 16-byte chunks per row, chunk index
+// XOR ((row >> 1) & 3) (the 64-byte swizzle the TMA store expects)
+__device__ __forceinline__ void duo_put16_64(const float (&f)[32], uint32_t buf, int row, bool bf16) {
+    uint32_t h[16];
+    if (bf16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            h[i] = *reinterpret_cast<uint32_t*>(&t);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            h[i] = *reinterpret_cast<uint32_t*>(&t);
+        }
+    }
+    const uint32_t row_addr = buf + (uint32_t)row * 64u;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        st_shared_v4(row_addr + (uint32_t)((c ^ ((row >> 1) & 3)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
 }
 __device__ __forceinline__ void duo_put32(const float (&f)[32], uint32_t row_addr, int row) {
 #pragma unroll
@@ -250,7 +284,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
         for (int s = 0; s < C::NSLOT; ++s) mbar_init(smem_u32(&sffull_bar[s]), 8);
         mbar_init(smem_u32(tfull_bar), 1);
-        mbar_init(smem_u32(tempty_bar), 8);
+        mbar_init(smem_u32(tempty_bar), 16);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -393,110 +427,67 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 }
             }
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    } else if (warp < 6 || warp >= 11) {
+        // ------------------------------------------------------------ epilogue (warps 2..5 and 11..14, both CTAs)
         const int q = warp & 3;                              // tensor-memory lane quarter this warp may read
+        const int half = warp >= 11 ? 1 : 0;                 // which 128 of the 256 accumulator columns
         uint32_t tcount = 0, nstore = 0;
-        long long s_wake = 0, s_rel = 0, e_ld = 0, e_rd = 0, e_cv = 0, e_fn = 0;
         bool ok = true;
         const uint32_t tempty_leader = map_to_cta(smem_u32(tempty_bar), 0);
-        const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-        const int esize = (p.out_dtype == OUT_F32) ? 4 : 2;
-        const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)q * 2u * C::EPI_BUF;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128);
+        const bool out16 = p.out_dtype != OUT_F32, bf16 = p.out_dtype == OUT_BF16;
+        const int esize = out16 ? 2 : 4;
+        const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)(half * 4 + q) * C::EPI_BUF;
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
             const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
             if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4)) { ok = false; break; }
-            const bool profe = prof && leader && warp == 2 && tile + stride < total_tiles;
-            if (profe) s_wake += clock64();
             tc_fence_after();
             const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
-            const int64_t n0 = nt * C::TILE_N;
+            const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
             // 32 columns are converted while the read of the next 32 is in flight
             uint32_t va[32], vb[32];
             tc_ld32(t_lane, va);
 #pragma unroll 1
-            for (int c0 = 0; c0 < C::TILE_N; c0 += 64) {
-                // ---- columns c0 .. c0+31 (in va); read c0+32.. into vb
-                long long e0 = profe ? clock64() : 0;
-                tc_wait_ld();
-                tc_ld32(t_lane + (uint32_t)(c0 + 32), vb);
-                long long e1 = profe ? clock64() : 0;
-                uint32_t buf = my_buf + (nstore & 1u) * C::EPI_BUF;
-                uint32_t row_addr = buf + (uint32_t)lane * 128u;
-                float f[32];
-                if (lane == 0) bulk_wait_read_1();           // the store issued from this buffer two slabs ago has read it
-                __syncwarp();
-                long long e2 = profe ? clock64() : 0;
-                if (profe) { e_ld += e1 - e0; e_rd += e2 - e1; }
-                if (dbg & 2048) {
+            for (int c0 = 0; c0 < 128; c0 += 64) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) st_shared_v4(row_addr + (uint32_t)((c ^ (lane & 7)) << 4), va[4 * c], va[4 * c + 1], va[4 * c + 2], va[4 * c + 3]);
-                } else {
-                    duo_scale(va, f, n0 + c0, p.N, p.alpha, p.bias);
-                }
-                if (dbg & 2048) {
-                } else if (esize == 2) {
-                    duo_put16(f, row_addr, 0, lane, p.out_dtype == OUT_BF16);
-                } else {
-                    duo_put32(f, row_addr, lane);
+                for (int hh = 0; hh < 2; ++hh) {
+                    // columns c0 + 32*hh .. +31 are in va (hh = 0) or vb (hh = 1)
+                    tc_wait_ld();
+                    if (hh == 0) {
+                        tc_ld32(t_lane + (uint32_t)(c0 + 32), vb);
+                    } else if (c0 + 64 < 128) {
+                        tc_ld32(t_lane + (uint32_t)(c0 + 64), va);
+                    } else {
+                        // this warp's columns are all in registers: hand them back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);
+                    }
+                    const int64_t nn = n0 + c0 + 32 * hh;
+                    // 16-bit outputs alternate between two 2 KB blocks; f32 outputs have one 4 KB block
+                    const uint32_t buf = my_buf + (out16 ? (nstore & 1u) * (C::EPI_BUF / 2) : 0u);
+                    if (lane == 0) {
+                        if (out16) bulk_wait_read_1();       // the store issued from this block two chunks ago has read it
+                        else bulk_wait_read_0();
+                    }
+                    __syncwarp();
+                    float f[32];
+                    duo_scale(hh == 0 ? va : vb, f, nn, p.N, p.alpha, p.bias);
+                    if (out16) duo_put16_64(f, buf, lane, bf16);
+                    else duo_put32(f, buf + (uint32_t)lane * 128u, lane);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        if (row0 < p.M && n0 + c0 < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)((n0 + c0) * 4), (int)row0, buf);
+                        // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
+                        // lies outside altogether still closes an (empty) group, so that the group counts above hold
+                        if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
                         bulk_commit_group();
                     }
                     ++nstore;
-                    buf = my_buf + (nstore & 1u) * C::EPI_BUF;
-                    row_addr = buf + (uint32_t)lane * 128u;
-                    if (lane == 0) bulk_wait_read_1();
-                    __syncwarp();
                 }
-                // ---- columns c0+32 .. c0+63 (in vb); read c0+64.. into va, or hand the accumulator back
-                long long e3 = profe ? clock64() : 0;
-                if (profe) e_cv += e3 - e2;
-                tc_wait_ld();
-                if (c0 + 64 < C::TILE_N) {
-                    tc_ld32(t_lane + (uint32_t)(c0 + 64), va);
-                } else {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);
-                    if (profe) s_rel += clock64();
-                }
-                long long e4 = profe ? clock64() : 0;
-                if (profe) e_ld += e4 - e3;
-                if (dbg & 2048) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) st_shared_v4(row_addr + (uint32_t)(((4 + c) ^ (lane & 7)) << 4), vb[4 * c], vb[4 * c + 1], vb[4 * c + 2], vb[4 * c + 3]);
-                } else {
-                    duo_scale(vb, f, n0 + c0 + 32, p.N, p.alpha, p.bias);
-                    if (esize == 2) duo_put16(f, row_addr, 4, lane, p.out_dtype == OUT_BF16);
-                    else duo_put32(f, row_addr, lane);
-                }
-                long long e5 = profe ? clock64() : 0;
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (profe) { e_cv += e5 - e4; e_fn += clock64() - e5; }
-                if (lane == 0) {
-                    // rows beyond M and bytes beyond the row end are clipped by the copy engine; a slab that
-                    // lies outside altogether still closes an (empty) group, so that "all but the latest
-                    // group" always names the store that last used the other buffer
-                    const int64_t nn = n0 + c0 + (esize == 2 ? 0 : 32);
-                    if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
-                    bulk_commit_group();
-                }
-                ++nstore;
             }
         }
         if (lane == 0) bulk_wait_all();
-        if (prof && leader && warp == 2 && lane == 0 && p.stats != nullptr && blockIdx.x < 148) {
-            p.stats[876 + (blockIdx.x >> 1) * 2] = (unsigned long long)s_wake;      // 74 leaders x 2 words: 876..1023
-            p.stats[877 + (blockIdx.x >> 1) * 2] = (unsigned long long)s_rel;
-            p.stats[blockIdx.x * 4 + 4] = (unsigned long long)e_ld;     // the peer CTA's words 0..3: unused by its own roles in this slot order
-            p.stats[blockIdx.x * 4 + 5] = (unsigned long long)e_rd;
-            p.stats[blockIdx.x * 4 + 6] = (unsigned long long)e_cv;
-            p.stats[blockIdx.x * 4 + 7] = (unsigned long long)e_fn;
-        }
     } else if (warp < 10) {
         // ------------------------------------------------------------ scale loaders (warps 6..9, both CTAs)
         const int q = warp & 3;
