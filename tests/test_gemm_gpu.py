@@ -207,6 +207,37 @@ def test_mx8_gemm_matches_fake_quant(shape):
 
 
 @gpu
+@pytest.mark.parametrize("shape", [(129, 64, 128), (256, 256, 256), (300, 264, 1152), (1000, 520, 2176), (2048, 1024, 4096)])
+def test_mx8_two_cta_kernel_equals_single_cta_kernel(shape):
+    """MXFP8 x MXFP4 on the 256x256 two-CTA kernel against the single-CTA kernel: equal bits, and both
+    within bf16 rounding of the fake-quantized product."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = shape
+    x = torch.randn(M, K, device="cuda")
+    w = torch.randn(N, K, device="cuda") * 0.05
+    a, b = thor_fp4.MXTensor.from_float(x, "mxfp8"), thor_fp4.MXTensor.from_float(w, "mxfp4")
+    L = _ext.core()
+    v = L.tfc4_variant_index(thor_fp4.linear.resolve_mx8_variant(K).encode())
+    outs = []
+    try:
+        for mode in (0, 2):
+            L.tfp4_set_pair_mode(mode)
+            L.tfp4_set_splits(1)
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.gemm_mx(v, a.packed, a.sblk, b.packed, b.sblk, out, M, N, K)
+            torch.cuda.synchronize()
+            outs.append(out)
+    finally:
+        L.tfp4_set_pair_mode(-1)
+        L.tfp4_set_splits(0)
+    assert _ext.status() == 0
+    assert torch.equal(outs[0], outs[1])
+    ref = thor_fp4.mx_fake_quant(x, "mxfp8") @ thor_fp4.mx_fake_quant(w, "mxfp4").t()
+    assert rrms(outs[1], ref) < 4e-3
+
+
+@gpu
 @pytest.mark.parametrize("shape", [(1, 256, 4096), (17, 512, 8192), (128, 384, 2048), (100, 136, 2304)])
 @pytest.mark.parametrize("splits", [0, 2, 4, 7])
 @pytest.mark.parametrize("od", ["f32", "bf16"])

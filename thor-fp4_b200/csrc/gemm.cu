@@ -845,7 +845,7 @@ int out_map(const CUtensorMap** map, void* out, int64_t M, int64_t N, int esize,
     return TFP4_OK;
 }
 
-int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int dev, cudaStream_t stream) {
+int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int dev, cudaStream_t stream) {
     const CUtensorMap* tm_out = nullptr;
     int rc = out_map(&tm_out, p.out, p.M, p.N, p.out_dtype == OUT_F32 ? 4 : 2, dev);
     if (rc) return rc;
@@ -853,8 +853,10 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int dev, cudaSt
     if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
     p.stages = DuoCfg::OP_STAGES;
     if (!st->duo_attr_set) {
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
         st->duo_attr_set = true;
     }
     const int64_t tiles = ((p.M + DuoCfg::TILE_M - 1) / DuoCfg::TILE_M) * ((p.N + DuoCfg::TILE_N - 1) / DuoCfg::TILE_N);
@@ -872,8 +874,13 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int dev, cudaSt
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // the instantiation with the test hooks runs only while a debug mask is set
-    cudaError_t e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<true>, plan.tmW, plan.tmA, *tm_out, p)
-                            : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<false>, plan.tmW, plan.tmA, *tm_out, p);
+    cudaError_t e;
+    if (kind == 0)
+        e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<0, true>, plan.tmW, plan.tmA, *tm_out, p)
+                    : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<0, false>, plan.tmW, plan.tmA, *tm_out, p);
+    else
+        e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<1, true>, plan.tmW, plan.tmA, *tm_out, p)
+                    : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<1, false>, plan.tmW, plan.tmA, *tm_out, p);
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: two-CTA GEMM launch failed: %s\n", cudaGetErrorString(e));
         return TFP4_ERR_LAUNCH;
@@ -944,7 +951,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // 256 x 256 tiles on CTA pairs: NVFP4, no forced tile width or K split; chosen automatically once
     // there are enough tiles to occupy most CTA pairs (smaller batches do better on single-CTA tiles with split K)
     const int64_t duo_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    const bool duo_ok = kind == 0 && M > 128 && N >= 64 && g_force_bn == 0 && g_force_splits <= 1 && st->sm_count >= 2;
+    const bool duo_ok = M > 128 && N >= 64 && g_force_bn == 0 && g_force_splits <= 1 && st->sm_count >= 2;
     const bool duo = duo_ok && (g_pair_mode == 2 || (g_pair_mode == -1 && duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5));
     const uint32_t box_a = duo ? 128u : (pair ? (uint32_t)(bn / 2) : (uint32_t)bn);
     PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : (pair ? -bn : bn), dev};
@@ -1028,7 +1035,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.status = ext ? ext->status : st->status_dev;
     p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
-    if (duo) return launch_duo(st, pl, p, dev, stream);
+    if (duo) return launch_duo(st, pl, p, kind, dev, stream);
     if (pair) {
         if (kind == 0) return bn == 256 ? launch_pair<0, 256>(st, pl, p, 0, stream) : launch_pair<0, 192>(st, pl, p, 1, stream);
         return bn == 256 ? launch_pair<1, 256>(st, pl, p, 0, stream) : launch_pair<1, 192>(st, pl, p, 1, stream);

@@ -53,6 +53,12 @@ struct DuoCfg {
     static constexpr int SMEM_BYTES =
         OP_STAGES * (X_BYTES + W_BYTES) + EPI_BYTES + SF_STAGES * SF_STAGE_BYTES + BAR_BYTES + 1024;
     static constexpr uint32_t IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+    // MXFP8 tokens (A operand, e4m3 = 0 at bit 7) x MXFP4 weights (B operand, e2m1 = 5 at bit 10), UE8M0 scales (bit 23);
+    // MMA j of a K block takes scale byte j of the 32-bit scale columns (ids at bits 29 and 4)
+    static constexpr uint32_t IDESC_MX = (0u << 7) | (5u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24);
+    static constexpr uint32_t IDESC_MX1 = IDESC_MX | (1u << 29) | (1u << 4);
+    static constexpr uint32_t IDESC_MX2 = IDESC_MX | (2u << 29) | (2u << 4);
+    static constexpr uint32_t IDESC_MX3 = IDESC_MX | (3u << 29) | (3u << 4);
     static_assert(SF_COL + NSLOT * TMEM_SF_SLOT_COLS <= TMEM_COLS, "scale slots do not fit");
     static_assert(NSLOT == OP_STAGES, "K block i uses operand stage and scale slot i % OP_STAGES alike");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
@@ -247,7 +253,58 @@ __device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate,
     return ready;
 }
 
-template <bool DBG>
+// The same for MXFP8 tokens x MXFP4 weights: four kind::mxf8f6f4 MMAs of K = 32, one scale byte per row and MMA
+// (byte j of the K block's 32-bit scale columns, selected in the instruction descriptor and in the top bits of
+// the scale address).
+__device__ __forceinline__ uint32_t duo_kblock_mx(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last,
+                                                  uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t sf,
+                                                  uint32_t full_next, uint32_t sf_next, uint32_t par_next,
+                                                  uint32_t empty_bar, uint32_t tfull_bar) {
+    uint32_t ready;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+        ".reg .b16 m;\n\t"
+        ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g0, g1, g2, g3;\n\t"
+        ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "setp.ne.b32 pa, %2, 0;\n\t"
+        "setp.gt.and.u32 q0, %3, 0, q;\n\t"
+        "setp.gt.and.u32 q1, %3, 1, q;\n\t"
+        "setp.gt.and.u32 q2, %3, 2, q;\n\t"
+        "setp.gt.and.u32 q3, %3, 3, q;\n\t"
+        "setp.ne.and.b32 ql, %4, 0, q;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b16 m, 3;\n\t"
+        "add.u32 a1, %6, 2;\n\tadd.u32 a2, %6, 4;\n\tadd.u32 a3, %6, 6;\n\t"
+        "add.u32 b1, %7, 2;\n\tadd.u32 b2, %7, 4;\n\tadd.u32 b3, %7, 6;\n\t"
+        "mov.b64 da0, {%6, %8};\n\tmov.b64 da1, {a1, %8};\n\tmov.b64 da2, {a2, %8};\n\tmov.b64 da3, {a3, %8};\n\t"
+        "mov.b64 db0, {%7, %8};\n\tmov.b64 db1, {b1, %8};\n\tmov.b64 db2, {b2, %8};\n\tmov.b64 db3, {b3, %8};\n\t"
+        "or.b32 f1, %9, 0x40000000;\n\tor.b32 f2, %9, 0x80000000;\n\tor.b32 f3, %9, 0xC0000000;\n\t"
+        "add.u32 g0, %9, 16;\n\tor.b32 g1, g0, 0x40000000;\n\tor.b32 g2, g0, 0x80000000;\n\tor.b32 g3, g0, 0xC0000000;\n\t"
+        "@q0 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da0, db0, %15, [%9], [g0], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %12;\n\t"
+        "@q1 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da1, db1, %16, [f1], [g1], pt;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%11], %12;\n\t"
+        "@q2 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da2, db2, %17, [f2], [g2], pt;\n\t"
+        "@q3 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da3, db3, %18, [f3], [g3], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], m;\n\t"
+        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%14], m;\n\t"
+        "and.pred pf, pf, ps;\n\t"
+        "selp.u32 %0, 1, 0, pf;\n\t"
+        "}"
+        : "=r"(ready)
+        : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf),
+          "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC_MX),
+          "n"(DuoCfg::IDESC_MX1), "n"(DuoCfg::IDESC_MX2), "n"(DuoCfg::IDESC_MX3)
+        : "memory");
+    return ready;
+}
+
+// KIND 0: NVFP4 x NVFP4 (256 elements of K per K block, four scale atoms per 128 rows and K block);
+// KIND 1: MXFP8 tokens x MXFP4 weights (128 elements per K block, one atom; the 4-bit weights are expanded by TMA
+// to one byte per code in shared memory, and that copy credits its packed size to the barrier).
+template <int KIND, bool DBG>
 __global__ void __launch_bounds__(DUO_THREADS, 1)
 gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                 const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
@@ -310,6 +367,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     // test hooks (tfp4_set_debug) exist only in the DBG instantiation; the production one carries none of their branches
     const int dbg = DBG ? p.debug : 0;
     const bool prof = DBG && (dbg & 1024) != 0;
+    constexpr int ATOMS = (KIND == 0) ? 4 : 1;               // scale atoms per 128 rows and K block
+    constexpr uint32_t TX_BYTES = (KIND == 0) ? (uint32_t)(C::X_BYTES + C::W_BYTES) : (uint32_t)(C::X_BYTES + C::W_BYTES / 2);
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (both CTAs)
@@ -334,7 +393,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     if (lane == 0) mbar_arrive(bar);
                 } else {
                     // rows or K bytes outside the tensors are zero-filled and still counted in full
-                    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(C::X_BYTES + C::W_BYTES));
+                    if (lane == 0) mbar_expect_tx(bar, TX_BYTES);
                     __syncwarp();
                     if (lane < 2) tma_load_2d(my_dst + s * C::X_BYTES, my_map, kb * KB_BYTES, my_y, bar);
                 }
@@ -392,8 +451,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                             tc_fence_after();
                             const bool last = kb + 1 == k_blocks;
                             const int un = (u + 1) % C::OP_STAGES;         // the next K block's stage (also across tiles)
-                            const uint32_t ready =
-                                duo_kblock(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
+                            const uint32_t ready = (KIND == 0 ? duo_kblock : duo_kblock_mx)(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
                                            a_lo0 + u * (C::X_BYTES >> 4), b_lo0 + u * (C::W_BYTES >> 4), desc_hi,
                                            sf0 + u * TMEM_SF_SLOT_COLS, full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u,
                                            empty0 + 8 * u, tfull_a);
@@ -504,10 +562,11 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 long long t0 = profl ? clock64() : 0;
                 if (!mbar_wait_sleep(sfl0 + 8 * st, gph, abort_flag, 6)) { ok = false; break; }
                 if (profl) c_sfl += clock64() - t0;
-                uint32_t va[32], vw0[32], vw1[32];
+                // the atoms of the granule's two K blocks: ATOMS each per part, consecutive in shared memory
+                uint32_t va[8 * ATOMS], vw0[8 * ATOMS], vw1[8 * ATOMS];
                 const uint32_t src = sf_base + st * C::SF_STAGE_BYTES + lane * 16;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < 2 * ATOMS; ++j) {
                     ld_shared_v4(src + 512 * j, &va[4 * j]);
                     ld_shared_v4(src + C::SF_PART + 512 * j, &vw0[4 * j]);
                     ld_shared_v4(src + 2 * C::SF_PART + 512 * j, &vw1[4 * j]);
@@ -531,18 +590,25 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                         t0 = profl ? clock64() : 0;
                         if (!(dbg & 2)) {
                             const uint32_t t_base = t_q + slot * TMEM_SF_SLOT_COLS;
-                            tc_st<16>(t_base, va + 16 * b);
-                            // feature-side scales: MMA j reads 8 columns, rows 0-127 then rows 128-255
-                            uint32_t u[32];
+                            if constexpr (KIND == 0) {
+                                tc_st<16>(t_base, va + 16 * b);
+                                // feature-side scales: MMA j reads 8 columns, rows 0-127 then rows 128-255
+                                uint32_t u[32];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
+                                for (int j = 0; j < 4; ++j)
 #pragma unroll
-                                for (int w = 0; w < 4; ++w) {
-                                    u[8 * j + w] = vw0[16 * b + 4 * j + w];
-                                    u[8 * j + 4 + w] = vw1[16 * b + 4 * j + w];
-                                }
-                            tc_st<16>(t_base + TMEM_SFA_OFF, u);
-                            tc_st<16>(t_base + TMEM_SFA_OFF + 16, u + 16);
+                                    for (int w = 0; w < 4; ++w) {
+                                        u[8 * j + w] = vw0[16 * b + 4 * j + w];
+                                        u[8 * j + 4 + w] = vw1[16 * b + 4 * j + w];
+                                    }
+                                tc_st<16>(t_base + TMEM_SFA_OFF, u);
+                                tc_st<16>(t_base + TMEM_SFA_OFF + 16, u + 16);
+                            } else {
+                                // one atom per part: 4 columns of token scales, 4 + 4 of feature scales
+                                tc_st<4>(t_base, va + 4 * b);
+                                tc_st<4>(t_base + TMEM_SFA_OFF, vw0 + 4 * b);
+                                tc_st<4>(t_base + TMEM_SFA_OFF + 4, vw1 + 4 * b);
+                            }
                             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                         }
                         tc_fence_before();
@@ -578,7 +644,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 if (!mbar_wait_sleep(sfree0 + 8 * st, ((g >> 1) & 1u) ^ 1u, abort_flag, 10)) { ok = false; break; }
                 const int kb0 = 2 * gi;
                 int atoms = 0;
-                for (int kb = kb0; kb < kb0 + 2 && kb < k_blocks; ++kb) atoms += (kb == k_blocks - 1) ? p.last_atoms : 4;
+                for (int kb = kb0; kb < kb0 + 2 && kb < k_blocks; ++kb) atoms += (KIND == 0) ? ((kb == k_blocks - 1) ? p.last_atoms : 4) : 1;
                 const uint32_t bytes = (uint32_t)atoms * 512u;
                 const uint32_t bar = sfl0 + 8 * st;
                 if (dbg & 8) {
@@ -588,7 +654,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     __syncwarp();
                     if (my_ok)
                         bulk_load(sf_base + st * C::SF_STAGE_BYTES + (uint32_t)lane * C::SF_PART,
-                                  my_src + (int64_t)kb0 * 2048, bytes, bar);
+                                  my_src + (int64_t)kb0 * (ATOMS * 512), bytes, bar);
                 }
             }
         }
