@@ -207,6 +207,49 @@ def test_mx8_gemm_matches_fake_quant(shape):
 
 
 @gpu
+def test_starved_wait_gives_up_and_library_recovers():
+    """Every device-side wait is bounded.  The test hook 512 makes the producer warps of the two-CTA kernel signal
+    nothing and shortens the limit to ~10 ms: the consumers' waits run out, the kernel tears down in order (tensor
+    memory freed, both CTAs of each pair leave together), the status word records which role gave up, the next call
+    is refused with -8, and after tfp4_clear_status the same operands give the right answer again."""
+    import ctypes
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = 512, 512, 1024
+    x, w = _operands(M, N, K, seed=9)
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    L = _ext.core()
+
+    def raw_gemm():
+        return L.tfp4_gemm(a.packed.data_ptr(), a.sblk.data_ptr(), ctypes.c_float(1.0), b.packed.data_ptr(),
+                           b.sblk.data_ptr(), ctypes.c_float(b.tensor_scale), out.data_ptr(), M, N, K,
+                           _ext.OUT_DTYPE["bf16"], _ext.stream())
+    try:
+        L.tfp4_set_pair_mode(2)
+        L.tfp4_set_debug(512)
+        assert raw_gemm() == 0                   # the launch itself succeeds
+        torch.cuda.synchronize()                 # returns: nothing hangs
+        assert 1 <= _ext.status() <= 10          # code of the role whose wait ran out first
+        assert raw_gemm() == -8                  # refused until the status word is cleared
+    finally:
+        L.tfp4_set_debug(0)
+        L.tfp4_clear_status()
+    assert _ext.status() == 0
+    assert raw_gemm() == 0
+    torch.cuda.synchronize()
+    L.tfp4_set_pair_mode(0)
+    try:
+        ref = torch.empty_like(out)
+        ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, ref, M, N, K, "bf16")
+        torch.cuda.synchronize()
+    finally:
+        L.tfp4_set_pair_mode(-1)
+    assert torch.equal(out, ref)
+
+
+@gpu
 @pytest.mark.parametrize("shape", [(129, 64, 128), (256, 256, 256), (300, 264, 1152), (1000, 520, 2176), (2048, 1024, 4096)])
 def test_mx8_two_cta_kernel_equals_single_cta_kernel(shape):
     """MXFP8 x MXFP4 on the 256x256 two-CTA kernel against the single-CTA kernel: equal bits, and both

@@ -110,14 +110,15 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // bounded wait: false if the abort flag is up or the time limit passed.  Polls with the
 // non-blocking test_wait: try_wait parks the thread and wakes it late, which costs more than the
 // issue slots of the handful of waiting warps.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          long long limit = WAIT_CYCLES) {
     if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_test_wait(bar, parity)) return true;
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = code;
                 return false;
             }

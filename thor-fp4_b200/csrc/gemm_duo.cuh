@@ -88,7 +88,8 @@ __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_add
 // Waiting with a long suspend hint: the warp sleeps in hardware until the phase completes (or the
 // hint, in nanoseconds, runs out) instead of re-issuing polls that compete with the MMA issuer
 // for the shared-memory instruction queue of their SM partition.  Bounded like every other wait.
-__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                                long long limit = WAIT_CYCLES) {
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
         uint32_t ok;
@@ -102,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, v
         if (ok) return true;
         if ((it & 7u) == 7u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_CYCLES) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = code;
                 return false;
             }
@@ -367,6 +368,10 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     // test hooks (tfp4_set_debug) exist only in the DBG instantiation; the production one carries none of their branches
     const int dbg = DBG ? p.debug : 0;
     const bool prof = DBG && (dbg & 1024) != 0;
+    // test hook 512: the producer never signals its barriers and every wait gives up after ~10 ms instead of ~1 s,
+    // which exercises the give-up path (abort flag, status word, orderly teardown) without hanging anything
+    const bool starve = DBG && (dbg & 512) != 0;
+    const long long wlim = starve ? 20000000ll : WAIT_CYCLES;
     constexpr int ATOMS = (KIND == 0) ? 4 : 1;               // scale atoms per 128 rows and K block
     constexpr uint32_t TX_BYTES = (KIND == 0) ? (uint32_t)(C::X_BYTES + C::W_BYTES) : (uint32_t)(C::X_BYTES + C::W_BYTES / 2);
 
@@ -386,10 +391,12 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 const uint32_t ph = (pmask >> s) & 1u;
                 pmask ^= 1u << s;
                 const long long t0 = prof ? clock64() : 0;
-                if (!mbar_wait_sleep(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
+                if (!mbar_wait_sleep(empty0 + 8 * s, ph ^ 1u, abort_flag, 1, wlim)) { ok = false; break; }
                 if (prof) c_wait += clock64() - t0;
                 const uint32_t bar = full0 + 8 * s;
-                if (dbg & 8) {
+                if (starve) {
+                    // nothing is signalled: the consumers' waits run out
+                } else if (dbg & 8) {
                     if (lane == 0) mbar_arrive(bar);
                 } else {
                     // rows or K bytes outside the tensors are zero-filled and still counted in full
@@ -430,7 +437,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const long long c_begin = clock64();
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 const long long ta = prof ? clock64() : 0;
-                if (!mbar_wait(smem_u32(tempty_bar), (tcount & 1u) ^ 1u, abort_flag, 2)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(tempty_bar), (tcount & 1u) ^ 1u, abort_flag, 2, wlim)) { ok = false; break; }
                 if (prof) c_acc += clock64() - ta;
                 if (prof && tcount > 0) s_obs += clock64();
                 // K block kb sits in stage (s_start + kb) % OP_STAGES: walk the unrolled ring, entering at s_start
@@ -444,8 +451,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                             if (!peek) {
                                 // scales of this K block are in tensor memory of both CTAs; operands of both CTAs landed
                                 const long long t0 = prof ? clock64() : 0;
-                                if (!mbar_wait(sffull0 + 8 * u, ph, abort_flag, 5)) { ok = false; break; }
-                                if (!mbar_wait(full0 + 8 * u, ph, abort_flag, 3)) { ok = false; break; }
+                                if (!mbar_wait(sffull0 + 8 * u, ph, abort_flag, 5, wlim)) { ok = false; break; }
+                                if (!mbar_wait(full0 + 8 * u, ph, abort_flag, 3, wlim)) { ok = false; break; }
                                 if (prof) { c_wait += clock64() - t0; ++n_miss; }
                             }
                             tc_fence_after();
@@ -479,7 +486,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     const uint32_t ph = (rmask >> s) & 1u;
                     rmask ^= 1u << s;
-                    if (!mbar_wait_sleep(full0 + 8 * s, ph, abort_flag, 9)) { ok = false; break; }
+                    if (!mbar_wait_sleep(full0 + 8 * s, ph, abort_flag, 9, wlim)) { ok = false; break; }
                     if (lane == 0) mbar_arrive_cluster_relaxed(full0_leader + 8 * s);
                     if (++s == C::OP_STAGES) s = 0;
                 }
@@ -498,7 +505,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)(half * 4 + q) * C::EPI_BUF;
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
             const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
-            if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4)) { ok = false; break; }
+            if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
             tc_fence_after();
             const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
             const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
@@ -560,7 +567,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             for (int gi = 0; gi < grans && ok; ++gi, ++g) {
                 const uint32_t st = g & 1u, gph = (g >> 1) & 1u;
                 long long t0 = profl ? clock64() : 0;
-                if (!mbar_wait_sleep(sfl0 + 8 * st, gph, abort_flag, 6)) { ok = false; break; }
+                if (!mbar_wait_sleep(sfl0 + 8 * st, gph, abort_flag, 6, wlim)) { ok = false; break; }
                 if (profl) c_sfl += clock64() - t0;
                 // the atoms of the granule's two K blocks: ATOMS each per part, consecutive in shared memory
                 uint32_t va[8 * ATOMS], vw0[8 * ATOMS], vw1[8 * ATOMS];
@@ -583,7 +590,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                             const uint32_t sph = (lmask >> slot) & 1u;
                             lmask ^= 1u << slot;
                             t0 = profl ? clock64() : 0;
-                            if (!mbar_wait_sleep(empty0 + 8 * slot, sph ^ 1u, abort_flag, 7)) { ok = false; break; }
+                            if (!mbar_wait_sleep(empty0 + 8 * slot, sph ^ 1u, abort_flag, 7, wlim)) { ok = false; break; }
                             if (profl) c_empty += clock64() - t0;
                         }
                         tc_fence_after();
@@ -641,7 +648,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const uint32_t parts = 1u + (a_ok ? 1u : 0u) + (w1_ok ? 1u : 0u);
             for (int gi = 0; gi < grans; ++gi, ++g) {
                 const uint32_t st = g & 1u;
-                if (!mbar_wait_sleep(sfree0 + 8 * st, ((g >> 1) & 1u) ^ 1u, abort_flag, 10)) { ok = false; break; }
+                if (!mbar_wait_sleep(sfree0 + 8 * st, ((g >> 1) & 1u) ^ 1u, abort_flag, 10, wlim)) { ok = false; break; }
                 const int kb0 = 2 * gi;
                 int atoms = 0;
                 for (int kb = kb0; kb < kb0 + 2 && kb < k_blocks; ++kb) atoms += (KIND == 0) ? ((kb == k_blocks - 1) ? p.last_atoms : 4) : 1;
