@@ -1,25 +1,30 @@
-// gemm.cu -- hand-written tcgen05 block-scaled GEMM for sm_100a.
+// gemm.cu -- hand-written tcgen05 block-scaled GEMMs for sm_100a and their host side.
 //
 //   out[m, n] = cast( alpha * sum_k deq(act)[m, k] * deq(W)[n, k] + bias[n] )
 //
-// computed as (W @ act^T): the 128-row MMA "M" side is a tile of WEIGHT rows
-// (output features) and the MMA "N" side is a tile of BN tokens, so any batch
-// M >= 1 only pads the narrow side and the accumulator lane index is the output
-// column n.  This replaces the reference's cuBLASLt call
-// (csrc/thor_fp4_core.cu:697-757) and its CUTLASS variants
-// (csrc/cutlass_kernels.cu:191-224).
+// This replaces the reference's cuBLASLt call (csrc/thor_fp4_core.cu:697-757) and its CUTLASS
+// variants (csrc/cutlass_kernels.cu:191-224).  Three kernels share the PTX wrappers below:
+//   * gemm_duo_kernel (gemm_duo.cuh): CTA pairs, 256-token x 256-feature tiles, the path of every
+//     batch above 128 tokens with enough tiles to fill the GPU;
+//   * gemm_bs_kernel (this file): one CTA per tile, computed as (W @ act^T) - the 128-row MMA "M" side
+//     is a tile of WEIGHT rows and the "N" side a tile of BN tokens, so a batch of any size only pads
+//     the narrow side; with split K (f32 partial tiles + splitk_reduce_kernel) it is the small-batch path;
+//   * gemm_pair_kernel (gemm_pair.cuh): an earlier two-CTA form, opt-in, kept for comparison.
 //
-// Pipeline per CTA (persistent over output tiles, 192 threads):
+// gemm_bs_kernel, per CTA (persistent over output tiles, 320 threads):
 //   warp 0      producer: per 128-byte K block one TMA tile of W codes, one of
 //               act codes (128B-swizzled) and the matching 512-byte scale atoms
 //               (plain bulk copies - atoms of one K block are contiguous),
 //               all completing on the stage's "full" mbarrier;
-//   warp 1      MMA issuer: tcgen05.cp moves the scale atoms shared -> tensor
-//               memory, then 4 tcgen05.mma.block_scale per stage accumulate in
+//   warp 1      MMA issuer: 4 tcgen05.mma.block_scale per stage accumulate in
 //               tensor memory; tcgen05.commit releases the stage / publishes the
 //               accumulator;
+//   warps 6..9  scale loaders: scale atoms shared memory -> registers -> tcgen05.st
+//               into a scale slot of tensor memory (tcgen05.cp costs more tensor-pipe
+//               time than the MMAs it feeds);
 //   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns, alpha / bias / cast,
-//               row-major stores; with BN <= 128 two accumulators alternate so the
+//               transposed through shared memory, 16-byte row-major stores; with
+//               BN <= 128 two accumulators alternate so the
 //               epilogue of tile i overlaps the main loop of tile i+1.
 //
 // KIND 0: NVFP4 x NVFP4   (kind::mxf4nvf4, UE4M3 scale per 16, 256 elements per K block)
