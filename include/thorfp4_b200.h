@@ -76,6 +76,15 @@ int tfp4_gemm_bias(const void* packedA, const void* sblkA, float tsA,
                    const float* bias, void* out, int64_t M, int64_t N, int64_t K,
                    int out_dtype, void* stream);
 
+/* The two calls one forward pass of the reference's Linear makes (src/thor_fp4/linear.py:240-262: tfp4_quant of the
+ * activation into the layer's cached buffers, then tfp4_gemm, then the bias add) as one entry point, for hosts
+ * where the per-call cost of the foreign-function boundary matters (small batches are launch-bound).  Same
+ * arguments and error codes as the two calls. */
+int tfp4_linear(const void* x, int64_t M, int64_t K, int in_dtype, float act_ts,
+                uint8_t* act_packed, uint8_t* act_sblk,
+                const void* w_packed, const void* w_sblk, float w_ts,
+                const float* bias, void* out, int64_t N, int out_dtype, void* stream);
+
 /* Replaces the work between the two GEMMs of the reference's gated MLP (src/thor_fp4/fused.py:163-173:
  * activation, elementwise product, re-quantization of the hidden tensor; csrc K14 mx8_mul for the MX form)
  * for the NVFP4 block: gu is the [R, 2*I] f16/bf16 output of the stacked gate/up GEMM (I gate values,

@@ -80,6 +80,13 @@ int tfp4_gemm_bias(const void* pA, const void* sA, float tsA, const void* pB, co
                    const float* bias, void* out, int64_t M, int64_t N, int64_t K, int out_dtype, void* stream) {
     return tfp4::gemm_block_scaled(0, pA, sA, pB, sB, tsA * tsB, bias, out, M, N, K, out_dtype, S(stream));
 }
+int tfp4_linear(const void* x, int64_t M, int64_t K, int in_dtype, float act_ts, uint8_t* act_packed, uint8_t* act_sblk,
+                const void* w_packed, const void* w_sblk, float w_ts, const float* bias, void* out, int64_t N,
+                int out_dtype, void* stream) {
+    int rc = tfp4_quant(x, M, K, in_dtype, act_ts, act_packed, act_sblk, stream);
+    if (rc) return rc;
+    return tfp4_gemm_bias(act_packed, act_sblk, act_ts, w_packed, w_sblk, w_ts, bias, out, M, N, K, out_dtype, stream);
+}
 int tfp4_gemv(const void* x, int64_t M, int64_t K, int in_dtype, const uint8_t* pB, const uint8_t* sg, float tsB,
               void* out, int64_t N, int out_dtype, void* stream) {
     return tfp4::gemv(x, M, K, in_dtype, pB, sg, tsB, out, N, out_dtype, S(stream));

@@ -37,6 +37,8 @@ SIGNATURES = {
     "tfp4_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, i64, i64, i64, c_int, c_void]),
     "tfp4_gemm_bias": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
                                i64, i64, i64, c_int, c_void]),
+    "tfp4_linear": (c_int, [c_void, i64, i64, c_int, c_float, c_void, c_void, c_void, c_void, c_float, c_void, c_void,
+                            i64, c_int, c_void]),
     "tfp4_swiglu_quant": (c_int, [c_void, i64, i64, c_int, c_void, c_void, c_void]),
     "tfp4_gemm_noalloc": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
                                   i64, i64, i64, c_int, c_void]),
@@ -129,7 +131,8 @@ def cublaslt_version() -> int:
 
 
 def stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of the current stream without building a torch.cuda.Stream object (called on every launch)
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def status() -> int:

@@ -26,6 +26,8 @@ from .ops import MXTensor, NVFP4Tensor
 
 __all__ = ["Linear", "resolve_mx8_variant"]
 
+_OPS_QUANT, _OPS_GEMM = ops.quantize_nvfp4, ops.gemm     # to notice when a caller has replaced them
+
 _DEFAULT_NV_VARIANTS = ["nvfp4_128x256x256_c2x1", "nvfp4_128x128x256_c1"]
 _MX8_SMALL_K = ["mxfp8xfp4_128x128x128_c2x1", "mxfp8xfp4_128x128x256_c1"]
 _MX8_BIG_K = ["mxfp8xfp4_128x256x128_c2x1", "mxfp8xfp4_128x128x256_c1"]
@@ -200,6 +202,16 @@ class Linear(nn.Module):
                 self._act_bufs[key] = bufs
             packed, sblk, out = bufs
             if self.engine_kind == "lt":
+                if ops.quantize_nvfp4 is _OPS_QUANT and ops.gemm is _OPS_GEMM:
+                    # both steps in one foreign call (small batches are bound by per-call host cost); the
+                    # two-call form below stays for callers that wrap or replace ops.quantize_nvfp4 / ops.gemm
+                    b = self._bias_f32()
+                    rc = _ext.device_lib().tfp4_linear(
+                        x.data_ptr(), M, K, _ext.IN_DTYPE[dt], self.act_tensor_scale, packed.data_ptr(), sblk.data_ptr(),
+                        w.packed.data_ptr(), w.sblk.data_ptr(), w.tensor_scale, b.data_ptr() if b is not None else None,
+                        out.data_ptr(), N, _ext.OUT_DTYPE[self.out_dtype], _ext.stream())
+                    assert rc == 0, f"tfp4_linear rc={rc}"
+                    return out
                 ops.quantize_nvfp4(x, self.act_tensor_scale, packed, sblk)
                 ops.gemm(packed, sblk, self.act_tensor_scale, w.packed, w.sblk, w.tensor_scale,
                          out, M, N, K, self.out_dtype, bias=self._bias_f32())
