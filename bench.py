@@ -265,6 +265,19 @@ def run_sweep(args):
                   flush=True)
         del lin
         torch.cuda.empty_cache()
+    # batch-1 engines: exact-activation GEMV (one launch) against quantize + split-K GEMM
+    for (K, N) in ((8192, 8192), (8192, 28672), (28672, 8192)):
+        for eng in ("gemv", "cublaslt"):
+            lin = thor_fp4.Linear(K, N, bias=False, out_dtype="bf16", device="cuda", engine=eng)
+            lin.refresh_weight()
+            for M in (1, 4, 8):
+                x = torch.randn(M, K, device="cuda").bfloat16()
+                us = timed(lambda: lin(x), max(args.steps, 50))
+                wbytes = N * K * (0.5 + 1.0 / 16)
+                print(f"| {K} -> {N} | {M} | engine={eng} ({lin.engine_kind}) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | {wbytes / us / 1e3:.0f} |",
+                      flush=True)
+            del lin
+            torch.cuda.empty_cache()
     # MXFP8 activations x MXFP4 weights against NVFP4 x NVFP4 on the same data
     M, K, N = 4096, 8192, 28672
     x = outliers(torch.randn(M, K, device="cuda"), 0.001, 50.0)

@@ -296,10 +296,14 @@ struct Cfg {
     static constexpr int SMEM_BUDGET = 227 * 1024 - 1024 - 256 - EPI_STAGE_BYTES;   // alignment slack, barriers, epilogue staging
     static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
     static_assert(STAGES >= 3, "pipeline too shallow");
-    // scale slots in tensor memory: at most 4, and never more than pipeline stages (a loader
-    // waits on the stage barrier of the K block NSLOT iterations back; with more slots than stages
-    // that barrier could run two phases ahead of the waiter)
-    static constexpr int NSLOT = NSLOT_FIT < (STAGES < 4 ? STAGES : 4) ? NSLOT_FIT : (STAGES < 4 ? STAGES : 4);
+    // scale slots in tensor memory: one per pipeline stage wherever that many fit behind the accumulators
+    // (every tile width but 192), so that K block i uses stage and slot i % STAGES alike; never more slots
+    // than stages (a loader waits on the stage barrier of the K block NSLOT iterations back; with more slots
+    // than stages that barrier could run two phases ahead of the waiter)
+    static constexpr int NSLOT = NSLOT_FIT < STAGES ? (NSLOT_FIT < 4 ? NSLOT_FIT : 4) : STAGES;
+    static constexpr bool SLOT_IS_STAGE = NSLOT == STAGES;
+    static_assert(BN == 192 || SLOT_IS_STAGE, "the unrolled MMA loop needs a scale slot per stage");
+    static_assert(NSLOT <= 8, "eight scale-slot barriers are laid out");
     static_assert(NSLOT >= 2, "need two scale slots");
     static_assert((W_BYTES % 1024) == 0 && (A_BYTES % 1024) == 0, "operand tiles must keep 1024-byte alignment");
     // instruction descriptor (block-scaled form): formats, N>>3 at bit 17, scale format at 23, M>>4 at 24
@@ -359,7 +363,93 @@ __device__ __forceinline__ void tc_st<16>(uint32_t taddr, const uint32_t* v) {
                    "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
 
-template <int KIND, int BN>
+// One K block of the single-CTA MMA stream in one statement (see duo_kblock in gemm_duo.cuh for why): up
+// to four MMAs, the look-ahead polls of the next K block's barriers between them, the commit that frees the
+// stage and, under a predicate, the commit that publishes the accumulator.  A = weight tile, B = token tile;
+// SFB_STEP = scale columns of the token side per MMA (4 per 128 tokens).
+template <int KIND, int SFB_STEP, uint32_t IDESC>
+__device__ __forceinline__ uint32_t bs_kblock(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last, uint32_t d,
+                                              uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t sfa, uint32_t sfb,
+                                              uint32_t full_next, uint32_t sf_next, uint32_t par_next, uint32_t empty_bar,
+                                              uint32_t tfull_bar) {
+    uint32_t ready;
+    if (KIND == 0) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+            ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g1, g2, g3;\n\t"
+            ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "setp.ne.b32 pa, %2, 0;\n\t"
+            "setp.gt.and.u32 q0, %3, 0, q;\n\t"
+            "setp.gt.and.u32 q1, %3, 1, q;\n\t"
+            "setp.gt.and.u32 q2, %3, 2, q;\n\t"
+            "setp.gt.and.u32 q3, %3, 3, q;\n\t"
+            "setp.ne.and.b32 ql, %4, 0, q;\n\t"
+            "setp.eq.b32 pt, 0, 0;\n\t"
+            "add.u32 a1, %6, 2;\n\tadd.u32 a2, %6, 4;\n\tadd.u32 a3, %6, 6;\n\t"
+            "add.u32 b1, %7, 2;\n\tadd.u32 b2, %7, 4;\n\tadd.u32 b3, %7, 6;\n\t"
+            "mov.b64 da0, {%6, %8};\n\tmov.b64 da1, {a1, %8};\n\tmov.b64 da2, {a2, %8};\n\tmov.b64 da3, {a3, %8};\n\t"
+            "mov.b64 db0, {%7, %8};\n\tmov.b64 db1, {b1, %8};\n\tmov.b64 db2, {b2, %8};\n\tmov.b64 db3, {b3, %8};\n\t"
+            "add.u32 f1, %9, 4;\n\tadd.u32 f2, %9, 8;\n\tadd.u32 f3, %9, 12;\n\t"
+            "add.u32 g1, %10, %17;\n\tadd.u32 g2, g1, %17;\n\tadd.u32 g3, g2, %17;\n\t"
+            "@q0 tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %16, [%9], [%10], pa;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 pf, [%11], %13;\n\t"
+            "@q1 tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %16, [f1], [g1], pt;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 ps, [%12], %13;\n\t"
+            "@q2 tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %16, [f2], [g2], pt;\n\t"
+            "@q3 tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %16, [f3], [g3], pt;\n\t"
+            "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%14];\n\t"
+            "@ql tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%15];\n\t"
+            "and.pred pf, pf, ps;\n\t"
+            "selp.u32 %0, 1, 0, pf;\n\t"
+            "}"
+            : "=r"(ready)
+            : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sfa), "r"(sfb),
+              "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(IDESC), "n"(SFB_STEP)
+            : "memory");
+    } else {
+        // one scale byte per row and MMA: byte j of the 32-bit scale columns (descriptor ids and address top bits)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+            ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g1, g2, g3;\n\t"
+            ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "setp.ne.b32 pa, %2, 0;\n\t"
+            "setp.gt.and.u32 q0, %3, 0, q;\n\t"
+            "setp.gt.and.u32 q1, %3, 1, q;\n\t"
+            "setp.gt.and.u32 q2, %3, 2, q;\n\t"
+            "setp.gt.and.u32 q3, %3, 3, q;\n\t"
+            "setp.ne.and.b32 ql, %4, 0, q;\n\t"
+            "setp.eq.b32 pt, 0, 0;\n\t"
+            "add.u32 a1, %6, 2;\n\tadd.u32 a2, %6, 4;\n\tadd.u32 a3, %6, 6;\n\t"
+            "add.u32 b1, %7, 2;\n\tadd.u32 b2, %7, 4;\n\tadd.u32 b3, %7, 6;\n\t"
+            "mov.b64 da0, {%6, %8};\n\tmov.b64 da1, {a1, %8};\n\tmov.b64 da2, {a2, %8};\n\tmov.b64 da3, {a3, %8};\n\t"
+            "mov.b64 db0, {%7, %8};\n\tmov.b64 db1, {b1, %8};\n\tmov.b64 db2, {b2, %8};\n\tmov.b64 db3, {b3, %8};\n\t"
+            "or.b32 f1, %9, 0x40000000;\n\tor.b32 f2, %9, 0x80000000;\n\tor.b32 f3, %9, 0xC0000000;\n\t"
+            "or.b32 g1, %10, 0x40000000;\n\tor.b32 g2, %10, 0x80000000;\n\tor.b32 g3, %10, 0xC0000000;\n\t"
+            "@q0 tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%5], da0, db0, %16, [%9], [%10], pa;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 pf, [%11], %13;\n\t"
+            "@q1 tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%5], da1, db1, %17, [f1], [g1], pt;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 ps, [%12], %13;\n\t"
+            "@q2 tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%5], da2, db2, %18, [f2], [g2], pt;\n\t"
+            "@q3 tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%5], da3, db3, %19, [f3], [g3], pt;\n\t"
+            "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%14];\n\t"
+            "@ql tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%15];\n\t"
+            "and.pred pf, pf, ps;\n\t"
+            "selp.u32 %0, 1, 0, pf;\n\t"
+            "}"
+            : "=r"(ready)
+            : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sfa), "r"(sfb),
+              "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(IDESC),
+              "n"(IDESC | (1u << 29) | (1u << 4)), "n"(IDESC | (2u << 29) | (2u << 4)), "n"(IDESC | (3u << 29) | (3u << 4))
+            : "memory");
+    }
+    return ready;
+}
+
+template <int KIND, int BN, bool DBG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                const GemmParams p) {
@@ -378,7 +468,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     uint64_t* tfull_bar = bars + 2 * STAGES;           // [ACC_STAGES]
     uint64_t* tempty_bar = tfull_bar + C::ACC_STAGES;  // [ACC_STAGES]
     uint64_t* sffull_bar = tempty_bar + C::ACC_STAGES; // [2] scale slot filled (one arrival per loader warp)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sffull_bar + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sffull_bar + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     uint8_t* epi_stage = reinterpret_cast<uint8_t*>(bars) + 256;
 
@@ -393,7 +483,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             mbar_init(smem_u32(&tfull_bar[a]), 1);
             mbar_init(smem_u32(&tempty_bar[a]), 4);   // one arrival per epilogue warp
         }
-        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sffull_bar[i]), 4);
+        for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&sffull_bar[i]), 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -406,6 +496,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // test hooks (tfp4_set_debug) exist only in the DBG instantiation
+    const int dbg = DBG ? p.debug : 0;
 
     // work item = (weight tile, token tile, K range); the K range is the fastest index
     const int64_t total_tiles = p.m_tiles * p.n_tiles * p.splits;
@@ -443,7 +535,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, 1)) { ok = false; break; }
                     const uint32_t bar = full0 + 8 * s;
-                    if (p.debug & 8) {
+                    if (dbg & 8) {
                         if (lane == 0) mbar_arrive(bar);
                     } else {
                         const int atoms = (kb == k_blocks - 1) ? ((KIND == 0) ? p.last_atoms : 1) : C::ATOMS;
@@ -469,11 +561,60 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         // The whole warp walks the loop (uniform control flow); lane 0 alone issues.
+        if constexpr (C::SLOT_IS_STAGE) {
+            // K loop unrolled over the stage ring (addresses = base + constant), one statement per K block with
+            // the look-ahead polls inside (bs_kblock); the blocking, bounded wait is only the fallback.
+            const uint32_t on = (lane == 0) ? 1u : 0u;
+            uint32_t mmask = 0, tcount = 0;               // phase bit per stage; work items done
+            int s_start = 0;                              // stage of the work item's first K block
+            bool ok = true, peek = false;
+            const uint64_t adesc_base = desc_sw128(smem_u32(sW)), bdesc_base = desc_sw128(smem_u32(sA));
+            const uint32_t desc_hi = (uint32_t)(adesc_base >> 32);
+            const uint32_t a_lo0 = (uint32_t)adesc_base, b_lo0 = (uint32_t)bdesc_base;
+            const uint32_t sf0 = tmem_base + C::SF_COL;
+            const uint32_t sffull0 = smem_u32(sffull_bar);
+            const uint32_t full_mma = (dbg & 4) ? 0u : 4u;
+            const uint32_t last_atoms = (dbg & 4) ? 0u : (uint32_t)p.last_atoms;
+            for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+                const uint32_t acc = tcount % C::ACC_STAGES;
+                const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_flag, 2)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t tfull_a = smem_u32(&tfull_bar[acc]);
+                const int kb0 = (int)(tile % p.splits) * p.kb_per_split;
+                const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+                const int nkb = kb1 - kb0;
+                for (int base = -s_start; base < nkb && ok; base += STAGES) {
+#pragma unroll
+                    for (int u = 0; u < STAGES; ++u) {
+                        const int r = base + u;
+                        if ((unsigned)r < (unsigned)nkb) {
+                            const uint32_t ph = (mmask >> u) & 1u;
+                            mmask ^= 1u << u;
+                            if (!peek) {
+                                if (!mbar_wait(sffull0 + 8 * u, ph, abort_flag, 5)) { ok = false; break; }
+                                if (!mbar_wait(full0 + 8 * u, ph, abort_flag, 3)) { ok = false; break; }
+                            }
+                            tc_fence_after();
+                            const bool last = r + 1 == nkb;
+                            const int un = (u + 1) % STAGES;
+                            const uint32_t sfw = sf0 + u * TMEM_SF_SLOT_COLS;
+                            const uint32_t ready = bs_kblock<KIND, 4 * C::SF_TILES, C::IDESC>(
+                                on, r > 0 ? 1u : 0u, (kb0 + r == k_blocks - 1) ? last_atoms : full_mma, last ? 1u : 0u, d_tmem,
+                                a_lo0 + u * (C::W_BYTES >> 4), b_lo0 + u * (C::A_BYTES >> 4), desc_hi, sfw, sfw + TMEM_SFA_OFF,
+                                full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u, empty0 + 8 * u, tfull_a);
+                            peek = __all_sync(0xffffffffu, ready != 0u) && !(dbg & 32);
+                        }
+                    }
+                }
+                s_start = (s_start + nkb) % STAGES;
+            }
+        } else {
         const uint32_t on = (lane == 0) ? 1u : 0u;
         uint32_t s = 0, ph = 0, tcount = 0, it = 0;
         bool ok = true, peek_full = false, peek_sf = false;
         long long c_full = 0, c_cp = 0, c_mma = 0;
-        const bool prof = (p.debug & 1024) != 0;
+        const bool prof = (dbg & 1024) != 0;
         const long long c_begin = clock64();
         const uint32_t w_base = smem_u32(sW), a_base = smem_u32(sA);
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
@@ -507,7 +648,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (prof) c2 = clock64();
                 const uint64_t adesc0 = desc_sw128(w_base + s * C::W_BYTES);
                 const uint64_t bdesc0 = desc_sw128(a_base + s * C::A_BYTES);
-                if (!(p.debug & 4)) {
+                if (!(dbg & 4)) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (j < n_mma) {
@@ -522,14 +663,14 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                 sfa_t = sfa_c | ((uint32_t)j << 30);
                             }
                             // advancing K by 64 (or 32) elements = 32 bytes inside the swizzle span
-                            if (p.debug & 64) {
+                            if (dbg & 64) {
                                 if (elect_one()) tc_mma<KIND>(d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t, (kb > kb0 || j > 0) ? 1u : 0u);
                             } else {
                                 tc_mma_if<KIND>(on, d_tmem, adesc0 + 2 * j, bdesc0 + 2 * j, idesc, sfw_t, sfa_t,
                                                 (kb > kb0 || j > 0) ? 1u : 0u);
                             }
                         }
-                        if (j == 2 && !(p.debug & 32)) {
+                        if (j == 2 && !(dbg & 32)) {
                             // issuing an MMA returns only when the pipe takes it, i.e. while its predecessor
                             // still runs: poll the next K block's barriers in that shadow (non-blocking),
                             // so that nothing but the commit sits between this block's last MMA and the
@@ -556,6 +697,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_full;
             p.stats[blockIdx.x * 4 + 2] = (unsigned long long)c_cp;
             p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_mma;
+        }
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -603,7 +745,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 tc_fence_after();
                 const uint32_t slot = it % C::NSLOT;
                 const uint32_t t_base = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_COL + slot * TMEM_SF_SLOT_COLS;
-                if (!(p.debug & 2)) {
+                if (!(dbg & 2)) {
                     uint32_t v[C::ATOMS * 4];
                     const uint32_t src_w = sfw_base + s * C::SFW_BYTES + lane * 16;
 #pragma unroll
@@ -773,14 +915,18 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
     p.stages = C::STAGES;
     if (!st->attr_set[KIND][bn_slot]) {
-        TFP4_CK(cudaFuncSetAttribute(gemm_bs_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TFP4_CK(cudaFuncSetAttribute(gemm_bs_kernel<KIND, BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     st->max_smem));
+        TFP4_CK(cudaFuncSetAttribute(gemm_bs_kernel<KIND, BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      st->max_smem));
         st->attr_set[KIND][bn_slot] = true;
     }
     const int64_t tiles = p.m_tiles * p.n_tiles;
     const int64_t tiles_all = tiles * p.splits;
     const unsigned grid_all = (unsigned)(tiles_all < st->sm_count ? tiles_all : st->sm_count);
-    gemm_bs_kernel<KIND, BN><<<grid_all, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
+    // the instantiation with the test hooks runs only while a debug mask is set
+    if (p.debug) gemm_bs_kernel<KIND, BN, true><<<grid_all, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
+    else gemm_bs_kernel<KIND, BN, false><<<grid_all, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
     if (p.splits > 1) {
         const int64_t MN = p.M * p.N;
         splitk_reduce_kernel<<<(unsigned)((MN / 4 + 255) / 256), 256, 0, stream>>>(p.ws, p.splits, MN, p.N, p.bias, p.out,
@@ -1010,7 +1156,22 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     {
         const int64_t tiles = p.m_tiles * p.n_tiles;
         int want = g_force_splits;
-        if (want == 0) want = (!pair && !duo && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
+        if (want == 0) {
+            want = (!pair && !duo && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
+            if (!pair && !duo && M <= 32 && p.k_blocks >= 8) {
+                // Weight-streaming regime (partial sums are negligible next to the weights): pick the split that
+                // minimises waves x (K blocks per work item + pipeline fill), which also evens out tile counts
+                // that do not divide the SM count (e.g. 224 tiles on 148 SMs).
+                int best = 1;
+                int64_t best_cost = INT64_MAX;
+                for (int sp = 1; sp <= 16 && sp <= p.k_blocks / 4; ++sp) {
+                    const int64_t waves = (tiles * sp + st->sm_count - 1) / st->sm_count;
+                    const int64_t cost = waves * ((p.k_blocks + sp - 1) / sp + 6);
+                    if (cost < best_cost) { best_cost = cost; best = sp; }
+                }
+                want = best;
+            }
+        }
         if (want > p.k_blocks / 4) want = p.k_blocks / 4;
         if (want > 16) want = 16;
         if (want > 1 && !pair && !duo) {
