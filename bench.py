@@ -265,6 +265,21 @@ def run_sweep(args):
                   flush=True)
         del lin
         torch.cuda.empty_cache()
+    # the activation quantizer alone over sizes (inputs rotate over > 300 MB)
+    for (R, K) in ((2048, 8192), (4096, 8192), (8192, 8192), (16384, 8192), (8192, 28672)):
+        n = max(2, int(300e6 / (R * K * 2)) + 1)
+        xq = [torch.randn(R, K, device="cuda").bfloat16() for _ in range(n)]
+        pq = torch.zeros(ops.packed_bytes(R, K), dtype=torch.uint8, device="cuda")
+        sq = torch.zeros(ops.scale_bytes(R, K), dtype=torch.uint8, device="cuda")
+        cnt = [0]
+
+        def qstep():
+            ops.quantize_nvfp4(xq[cnt[0] % n], 1.0, pq, sq)
+            cnt[0] += 1
+        us = timed(qstep, args.steps)
+        print(f"| quantize bf16 [{R}, {K}] | - | quant_nvfp4_kernel | {us:.1f} | - | {R * K * 2.5625 / us / 1e3:.0f} (algorithmic bytes) |", flush=True)
+        del xq, pq, sq
+        torch.cuda.empty_cache()
     # batch-1 engines: exact-activation GEMV (one launch) against quantize + split-K GEMM
     for (K, N) in ((8192, 8192), (8192, 28672), (28672, 8192)):
         for eng in ("gemv", "cublaslt"):

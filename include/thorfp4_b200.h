@@ -153,6 +153,8 @@ void tfp4_set_pair_mode(int mode);
 /* K split of small-batch GEMMs: 0 automatic, 1 never, n = about n K ranges (test hook). */
 void tfp4_set_splits(int n);
 void tfp4_set_debug(int bits);
+/* test hook: force the NVFP4 quantizer's tile height (64 or 128 rows; 0 = automatic) */
+void tfp4_set_quant_tile_rows(int rows);
 int tfp4_debug_stats(unsigned long long* out, int n_ctas);
 
 #ifdef __cplusplus

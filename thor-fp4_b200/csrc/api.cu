@@ -18,6 +18,7 @@ void gemm_set_token_tile(int);
 void gemm_set_debug(int);
 void gemm_set_pair_mode(int);
 void gemm_set_splits(int);
+void quant_set_tile_rows(int);
 int swiglu_quant_nvfp4(const void*, int64_t, int64_t, int, uint8_t*, uint8_t*, cudaStream_t);
 int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
                  int64_t, int, cudaStream_t);
@@ -135,6 +136,7 @@ int tfp4_gemm_noalloc(const void* pA, const void* sA, float tsA, const void* pB,
 int tfp4_gemm_noalloc_status(int reset) { return tfp4::gemm_noalloc_status(reset); }
 size_t tfp4_gemm_noalloc_capacity(void) { return tfp4::gemm_noalloc_capacity(); }
 
+void tfp4_set_quant_tile_rows(int rows) { tfp4::quant_set_tile_rows(rows); }
 int tfp4_status(void) { return tfp4::gemm_status_word(); }
 void tfp4_clear_status(void) { tfp4::gemm_clear_status(); }
 void tfp4_plan_stats(uint64_t* hits, uint64_t* misses) { tfp4::gemm_plan_stats(hits, misses); }

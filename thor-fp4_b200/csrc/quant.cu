@@ -395,6 +395,8 @@ int launch_quant_nvfp4_rows(const T* xp, int64_t R, int64_t K, float ts, uint8_t
     return TFP4_OK;
 }
 
+int g_quant_rows = 0;   // test hook: 64 / 128 forces the tile height, 0 = automatic
+
 template <typename T>
 int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* packed,
                        uint8_t* sblk, cudaStream_t stream) {
@@ -402,6 +404,8 @@ int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* p
     // the half-atom variant is kept for grids that would otherwise leave most SMs idle
     const int64_t tiles128 = ((K + QT_COLS - 1) / QT_COLS) * (pad128(R) / 128);
     const T* xp = static_cast<const T*>(x);
+    if (g_quant_rows == 64) return launch_quant_nvfp4_rows<T, 64>(xp, R, K, ts, packed, sblk, stream);
+    if (g_quant_rows == 128) return launch_quant_nvfp4_rows<T, 128>(xp, R, K, ts, packed, sblk, stream);
     if (tiles128 < 148) return launch_quant_nvfp4_rows<T, 64>(xp, R, K, ts, packed, sblk, stream);
     return launch_quant_nvfp4_rows<T, 128>(xp, R, K, ts, packed, sblk, stream);
 }
@@ -420,6 +424,8 @@ int launch_quant_mx(const void* x, int64_t R, int64_t K, int kind, uint8_t* pack
 bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
 }  // namespace
+
+void quant_set_tile_rows(int rows) { g_quant_rows = (rows == 64 || rows == 128) ? rows : 0; }
 
 // h = silu(gate) * up from the stacked GEMM output gu [R, 2K] (16-bit), quantized to NVFP4 with
 // per-tensor scale 1: codes [R, K/2] and scale tiles exactly as quant_nvfp4 would produce from h.
