@@ -89,3 +89,25 @@ def test_nvfp4_gated_mlp_matches_cpu_emulation(M):
     err = np.linalg.norm(y - ref) / np.linalg.norm(ref)
     assert err < 1e-3, err
     assert np.linalg.norm(y - y_unfused) / np.linalg.norm(y_unfused) < 1e-3
+
+
+@gpu
+def test_large_batch_layers_and_gated_block_replay_from_a_cuda_graph():
+    """Shapes that take the two-CTA kernel (cluster launch, TMA-store epilogue, cached output tensor maps) and the
+    one-pass activation kernel: warmed once eagerly, then captured and replayed; new inputs copied into the static
+    buffer give the eager results."""
+    import thor_fp4
+    from thor_fp4.fused import NVFP4GatedMLP
+    torch.manual_seed(5)
+    lin = thor_fp4.Linear(1024, 2048, bias=True, out_dtype="bf16").cuda()
+    mlp = NVFP4GatedMLP(1024, 2048, device="cuda", out_dtype="bf16", weight_std=0.05)
+    for mod, cols in ((lin, 1024), (mlp, 1024)):
+        x = torch.randn(768, cols, device="cuda").bfloat16()
+        eager = mod(x).clone()
+        g = thor_fp4.capture_module(mod, x)
+        assert torch.equal(g(x), eager)
+        x2 = torch.randn(768, cols, device="cuda").bfloat16()
+        want = mod(x2).clone()
+        assert torch.equal(g(x2), want)
+    from thor_fp4 import _ext
+    assert _ext.status() == 0
