@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--inter", type=int, default=28672, help="mlp workload: intermediate size")
+    ap.add_argument("--reduce-dtype", default="f32", choices=["f32", "bf16"],
+                    help="mlp workload on several ranks: type of the partial outputs that are all-reduced")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--ablate", action="store_true",
@@ -327,7 +329,7 @@ def run_mlp(args):
         dist.init_process_group("nccl", device_id=dev)
     M, H, I = args.M, args.K, args.inter
     torch.manual_seed(1234 + rank)
-    tp = TensorParallelGatedMLP(H, I, device=dev, reduce_dtype="f32" if world > 1 else "bf16", weight_std=0.02)
+    tp = TensorParallelGatedMLP(H, I, device=dev, reduce_dtype=args.reduce_dtype if world > 1 else "bf16", weight_std=0.02)
     tp.local.refresh_weight()
     xs = [torch.randn(M, H, device=dev).bfloat16() for _ in range(2)]
 
@@ -364,7 +366,7 @@ def run_mlp(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
             "config": {"workload": f"NVFP4 gated MLP: x bf16 [{M},{H}] -> quantize -> [Wg;Wu] GEMM ({2 * I // world} rows per rank) -> "
                                    f"silu*up + quantize -> Wd GEMM (K = {I // world} per rank) -> "
-                                   + ("all-reduce of f32 partials (NCCL)" if world > 1 else "bf16 out"),
+                                   + (f"all-reduce of {args.reduce_dtype} partials (NCCL), 4 token chunks overlapped" if world > 1 else "bf16 out"),
                        "tensor_parallel": world, "l2": "activations 268 MB and the 1.9 GB gate/up output exceed the 126 MB L2"},
             "per_gpu_frac_of_4x_bf16_burst": flop / world / (ms * 1e-3) / 1e12 / (4.0 * pk["bf16"]),
             "gpu_launches": 5 * args.steps, "clocks": clocks}))
