@@ -248,8 +248,8 @@ def run_sweep(args):
         x[:, ch] *= mul
         return x
 
-    print("| layer (K -> N) | M | kind | us per call | TFLOPS | weight-stream GB/s |")
-    print("|---|---|---|---|---|---|")
+    print("| layer (K -> N) | M | kind | us per call | TFLOPS | weight-stream GB/s | us per CUDA-graph replay |")
+    print("|---|---|---|---|---|---|---|")
     grids = [((8192, 8192), [1, 2048, 8192], "bf16", False)]
     grids += [((k, n), [1, 16, 128, 2048, 8192], "f16", True)
               for (k, n) in ((4096, 5120), (5120, 20480), (20480, 5120), (8192, 28672), (28672, 8192))]
@@ -263,7 +263,12 @@ def run_sweep(args):
             x = outliers(torch.randn(M, K, device="cuda"), 0.005, 30.0).bfloat16()
             us = timed(lambda: lin(x), args.steps)
             wbytes = N * K * (0.5 + 1.0 / 16)
-            print(f"| {K} -> {N} | {M} | nvfp4 x nvfp4 ({lin.engine_kind}) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | {wbytes / us / 1e3:.0f} |",
+            rep = "-"
+            if M <= 128:      # the same call replayed from a captured graph: device time without the eager host path
+                g = thor_fp4.capture_module(lin, x)
+                rep = f"{timed(lambda: g.graph.replay(), args.steps):.1f}"
+                del g
+            print(f"| {K} -> {N} | {M} | nvfp4 x nvfp4 ({lin.engine_kind}) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | {wbytes / us / 1e3:.0f} | {rep} |",
                   flush=True)
         del lin
         torch.cuda.empty_cache()
