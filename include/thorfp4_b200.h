@@ -93,6 +93,15 @@ int tfp4_linear(const void* x, int64_t M, int64_t K, int in_dtype, float act_ts,
 int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype,
                       uint8_t* packed, uint8_t* sblk, void* stream);
 
+/* Replaces the epilogue work of the reference's fused MX layers (csrc/fused_kernels.cu:74-123, src/thor_fp4/fused.py:81-135:
+ * bias[n], activation, MXFP8 re-quantization of the layer output) as one pass over the f16/bf16 GEMM output acc [R, N]:
+ * writes the e4m3 codes and UE8M0 scale tiles of act(acc + bias), block scale = the power of two at or above
+ * amax * (1/448) (the reference's fused-epilogue and mx8_mul recipe: nothing saturates; tfp4_quant_mx rounds the scale
+ * to the nearest power of two instead).  in_dtype 0 f32, 1 f16, 2 bf16; act: 0 identity, 1 gelu (erf form), 2 silu;
+ * bias may be null; N % 32 == 0. */
+int tfp4_act_quant_mx8(const void* acc, const float* bias, int64_t R, int64_t N, int in_dtype, int act,
+                       uint8_t* packed, uint8_t* sblk, void* stream);
+
 /* No counterpart in the reference.  tfp4_gemm_bias for callers that must not allocate at call time
  * (device memory fully pre-partitioned at start-up, a plug-in under a foreign allocator, a loop
  * that cannot afford the device-wide synchronisation of an allocation or a free): the kernel's scratch - status word, counters, split-K partial sums - sits in a

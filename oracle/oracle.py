@@ -58,6 +58,8 @@ def lib():
         L.orc_quant_nvfp4_rows.restype = ctypes.c_int
         L.orc_quant_mx_rows.argtypes = [_f32p, _i64, _i64, _i64, ctypes.c_int, _u8p, _u8p]
         L.orc_quant_mx_rows.restype = ctypes.c_int
+        L.orc_quant_mx8_ceil_rows.argtypes = [_f32p, _i64, _i64, _i64, _u8p, _u8p]
+        L.orc_quant_mx8_ceil_rows.restype = ctypes.c_int
         L.orc_mx8_mul.argtypes = [_u8p, _u8p, _u8p, _u8p, _u8p, _u8p, _i64, _i64]
         L.orc_mx8_mul.restype = ctypes.c_int
         L.orc_dequant_nvfp4_rows.argtypes = [_u8p, _u8p, ctypes.c_float, _i64, _i64, _i64, _f32p]
@@ -167,6 +169,18 @@ def dequantize_nvfp4(packed, sblk, ts, R, K, threads: int = 1):
     _run(lambda r0, r1: L.orc_dequant_nvfp4_rows(_u8(packed), _u8(sblk), ctypes.c_float(ts), r0, r1, K, _f32(out)),
          _ranges(R, threads), threads)
     return out
+
+
+def quantize_mx8_ceil(x: np.ndarray):
+    """(R,K) float32 -> MXFP8 codes and UE8M0 scale tiles with the ceil-pow2 block scale (fused-epilogue recipe)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    R, K = x.shape
+    packed = np.zeros(mx_packed_bytes(R, K, 1), np.uint8)
+    sblk = np.zeros(mx_scale_bytes(R, K), np.uint8)
+    rc = lib().orc_quant_mx8_ceil_rows(_f32(x), 0, R, K, _u8(packed), _u8(sblk))
+    if rc:
+        raise ValueError(f"orc_quant_mx8_ceil rc={rc}")
+    return packed, sblk
 
 
 def dequantize_mx(packed, sblk, kind, R, K):

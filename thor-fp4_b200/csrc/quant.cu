@@ -212,10 +212,16 @@ __device__ __forceinline__ uint32_t ue8m0_nearest(float v) {
     return b > 254u ? 254u : b;
 }
 
-template <typename T, int KIND>
+__device__ __forceinline__ uint32_t ue8m0_ceil(float v);
+
+// ACT >= 0: x is a GEMM output; the quantized tensor is act(x + bias[col]) (FP32 math; 0 identity, 1 gelu (erf form),
+// 2 silu) - the bias add, activation and re-quantization between two layers of an MX chain in one pass.  Like the
+// reference's fused epilogue and its mx8_mul, this form takes the block scale as the power of two at or above
+// amax * (1/448), so that no value saturates (the plain quantizer rounds the scale to the nearest power of two).
+template <typename T, int KIND, int ACT = -1>
 __global__ void __launch_bounds__(QT_THREADS)
 quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
-                uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
+                uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk, const float* __restrict__ bias = nullptr) {
     __shared__ __align__(16) uint8_t s_sf[2 * 512];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS;
@@ -237,6 +243,21 @@ quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
             const int64_t r = r0 + warp + 8 * (it + u);
             if (col_ok && r < R) {
                 load8<T>(x + r * K + col, f[u]);
+                if constexpr (ACT >= 0) {
+                    float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    if (bias != nullptr) {
+                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col));
+                        const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col + 4));
+                        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float v = f[u][i] + b[i];
+                        if (ACT == 1) f[u][i] = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+                        else if (ACT == 2) f[u][i] = v / (1.0f + expf(-v));
+                        else f[u][i] = v;
+                    }
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) f[u][i] = 0.f;
@@ -253,7 +274,8 @@ quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
                 for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[u][i]));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                const uint32_t scb = ue8m0_nearest(__fdiv_rn(amax, KIND == 0 ? 6.0f : 448.0f));
+                const uint32_t scb = (ACT >= 0) ? ue8m0_ceil(__fmul_rn(amax, 1.0f / 448.0f))
+                                                : ue8m0_nearest(__fdiv_rn(amax, KIND == 0 ? 6.0f : 448.0f));
                 // 1/ds = 2^(127 - scb), exactly representable for scb in [0, 254]
                 const int e = 127 - (int)scb;
                 const float inv = e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23)
@@ -424,6 +446,33 @@ int launch_quant_mx(const void* x, int64_t R, int64_t K, int kind, uint8_t* pack
 bool misaligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; }
 
 }  // namespace
+
+// act(acc + bias) -> MXFP8 codes and UE8M0 (ceil) scale tiles in one pass; acc = [R, N] f32/f16/bf16, N % 32 == 0
+int act_quant_mx8(const void* acc, const float* bias, int64_t R, int64_t N, int in_dtype, int act, uint8_t* packed,
+                  uint8_t* sblk, cudaStream_t stream) {
+    if (N <= 0 || (N % 32) != 0) {
+        fprintf(stderr, "thor_fp4: tfp4_act_quant_mx8 needs N %% 32 == 0 (got %ld)\n", (long)N);
+        return TFP4_ERR_BAD_K;
+    }
+    if (R <= 0) return TFP4_OK;
+    if (!acc || !packed || !sblk || in_dtype < 0 || in_dtype > 2 || act < 0 || act > 2 || misaligned(acc, in_dtype == IN_F32 ? 32 : 16) ||
+        misaligned(packed, 8) || misaligned(sblk, 8) || (bias && misaligned(bias, 16))) {
+        fprintf(stderr, "thor_fp4: tfp4_act_quant_mx8 bad argument (act 0..2, input 16-byte (f32: 32-byte) and bias 16-byte aligned)\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    dim3 grid((unsigned)((N + QT_COLS - 1) / QT_COLS), (unsigned)((R + QT_ROWS - 1) / QT_ROWS));
+#define TFP4_AQ(TT, A) quant_mx_kernel<TT, 1, A><<<grid, QT_THREADS, 0, stream>>>(static_cast<const TT*>(acc), R, N, packed, sblk, bias)
+    if (in_dtype == IN_BF16) {
+        if (act == 0) TFP4_AQ(__nv_bfloat16, 0); else if (act == 1) TFP4_AQ(__nv_bfloat16, 1); else TFP4_AQ(__nv_bfloat16, 2);
+    } else if (in_dtype == IN_F16) {
+        if (act == 0) TFP4_AQ(__half, 0); else if (act == 1) TFP4_AQ(__half, 1); else TFP4_AQ(__half, 2);
+    } else {
+        if (act == 0) TFP4_AQ(float, 0); else if (act == 1) TFP4_AQ(float, 1); else TFP4_AQ(float, 2);
+    }
+#undef TFP4_AQ
+    TFP4_CK(cudaGetLastError());
+    return TFP4_OK;
+}
 
 void quant_set_tile_rows(int rows) { g_quant_rows = (rows == 64 || rows == 128) ? rows : 0; }
 

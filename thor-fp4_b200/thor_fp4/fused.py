@@ -55,6 +55,7 @@ class MX8Act:
 
 
 _ACTS = {"gelu": F.gelu, "silu": F.silu, "ident": lambda t: t}
+_ACT_CODE = {"ident": 0, "gelu": 1, "silu": 2}
 
 
 class FusedLinear(nn.Module):
@@ -85,6 +86,7 @@ class FusedLinear(nn.Module):
         self._w: ops.MXTensor | None = None
         self._bufs: dict = {}
         self.max_chunk = max_chunk
+        self.fuse_epilogue = True     # False: torch elementwise ops + separate quantizer (the checker's path)
 
     def _apply(self, fn, recurse=True):
         self._w, self._bufs = None, {}
@@ -124,11 +126,21 @@ class FusedLinear(nn.Module):
             acc, out = bufs["acc"], bufs["out"]
             ops.gemm_mx(self.variant_idx, act_in.packed, act_in.sblk, self._w.packed, self._w.sblk,
                         acc, M, N, K, 1.0)
+            if self.fuse_epilogue:
+                # bias, activation and MXFP8 re-quantization in one pass over the GEMM output
+                b = self.bias.detach().float().contiguous() if self.bias is not None else None
+                rc = _ext.device_lib().tfp4_act_quant_mx8(
+                    acc.data_ptr(), b.data_ptr() if b is not None else None, M, N, _ext.IN_DTYPE[acc.dtype],
+                    _ACT_CODE[self.act], out.packed.data_ptr(), out.sblk.data_ptr(), _ext.stream())
+                assert rc == 0, f"tfp4_act_quant_mx8 rc={rc}"
+                return out
             y = acc.float()
             if self.bias is not None:
                 y = y + self.bias.float()
-            y = _ACTS[self.act](y)
-            ops.quantize_mx(y.contiguous(), "mxfp8", out.packed, out.sblk)
+            y = _ACTS[self.act](y).contiguous()
+            rc = _ext.device_lib().tfp4_act_quant_mx8(y.data_ptr(), None, M, N, _ext.IN_DTYPE[y.dtype], 0,
+                                                      out.packed.data_ptr(), out.sblk.data_ptr(), _ext.stream())
+            assert rc == 0, f"tfp4_act_quant_mx8 rc={rc}"
             return out
 
     def extra_repr(self) -> str:
