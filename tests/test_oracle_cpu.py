@@ -143,3 +143,29 @@ def test_exact16_fast_path_equivalence_exhaustive():
             fast = torch.where(tie, torch.where(lo % 2 == 0, lo, hi), fast)
             assert torch.equal(fast, ref), str(dt)
             assert not tie.any()
+
+
+def test_mx8_ceil_scale_quantizer_against_torch_float8():
+    """Ceil-pow2 block scale (the reference's fused-epilogue / mx8_mul recipe, csrc/thor_fp4_core.cu:612-652):
+    scale byte = smallest power of two >= amax/448, codes = e4m3(x / scale) - so nothing saturates, and the
+    codes equal torch's float8_e4m3fn cast of the scaled values."""
+    import torch
+    rng = np.random.default_rng(7)
+    R, K = 200, 256
+    x = (rng.standard_normal((R, K)) * np.exp(rng.uniform(-6, 6, (R, 1)))).astype(np.float32)
+    x[3, :32] = 0.0                                   # an all-zero block
+    x[5, 40] = 448.0 * 4                              # amax exactly on a power of two times 448
+    p, s = orc.quantize_mx8_ceil(x)
+    d = orc.dequantize_mx(p, s, "mxfp8", R, K)
+    blocks = x.reshape(R, K // 32, 32)
+    amax = np.abs(blocks).max(-1)
+    dblocks = d.reshape(R, K // 32, 32)
+    nz = amax > 0
+    scale = np.where(nz, 2.0 ** np.ceil(np.log2(np.where(nz, amax, 1.0) / 448.0)), 1.0)
+    want = torch.from_numpy((blocks / scale[..., None]).astype(np.float32)).to(torch.float8_e4m3fn).float().numpy() * scale[..., None]
+    assert np.array_equal(dblocks[nz], want[nz].astype(np.float32))
+    assert np.all(np.abs(dblocks) <= 448.0 * scale[..., None])
+    assert not dblocks[3, 0].any()
+    # within half an e4m3 step (2^-4 relative) of the input wherever the input is not tiny next to its block's amax
+    big = np.abs(blocks) > amax[..., None] * 2.0 ** -6
+    assert np.max(np.abs(dblocks - blocks)[big] / np.abs(blocks)[big]) <= 2.0 ** -4 + 1e-7
