@@ -509,48 +509,48 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             tc_fence_after();
             const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
             const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
-            // 32 columns are converted while the read of the next 32 is in flight
+            // One 32-column chunk: alpha, bias, cast, swizzled shared memory, TMA store.
+            auto emit = [&](const uint32_t (&v)[32], int c) {
+                const int64_t nn = n0 + c;
+                // 16-bit outputs alternate between two 2 KB blocks; f32 outputs have one 4 KB block
+                const uint32_t buf = my_buf + (out16 ? (nstore & 1u) * (C::EPI_BUF / 2) : 0u);
+                if (lane == 0) {
+                    if (out16) bulk_wait_read_1();       // the store issued from this block two chunks ago has read it
+                    else bulk_wait_read_0();
+                }
+                __syncwarp();
+                float f[32];
+                duo_scale(v, f, nn, p.N, p.alpha, p.bias);
+                if (out16) duo_put16_64(f, buf, lane, bf16);
+                else duo_put32(f, buf + (uint32_t)lane * 128u, lane);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
+                    // lies outside altogether still closes an (empty) group, so that the group counts above hold
+                    if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
+                    bulk_commit_group();
+                }
+                ++nstore;
+            };
+            // The warp's 128 columns are four chunks.  Two are read at once; the third is read while the second is
+            // emitted and the fourth right after, so the accumulator goes back to the MMA issuer after two chunks'
+            // worth of arithmetic instead of three.
             uint32_t va[32], vb[32];
             tc_ld32(t_lane, va);
-#pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 64) {
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    // columns c0 + 32*hh .. +31 are in va (hh = 0) or vb (hh = 1)
-                    tc_wait_ld();
-                    if (hh == 0) {
-                        tc_ld32(t_lane + (uint32_t)(c0 + 32), vb);
-                    } else if (c0 + 64 < 128) {
-                        tc_ld32(t_lane + (uint32_t)(c0 + 64), va);
-                    } else {
-                        // this warp's columns are all in registers: hand them back
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);
-                    }
-                    const int64_t nn = n0 + c0 + 32 * hh;
-                    // 16-bit outputs alternate between two 2 KB blocks; f32 outputs have one 4 KB block
-                    const uint32_t buf = my_buf + (out16 ? (nstore & 1u) * (C::EPI_BUF / 2) : 0u);
-                    if (lane == 0) {
-                        if (out16) bulk_wait_read_1();       // the store issued from this block two chunks ago has read it
-                        else bulk_wait_read_0();
-                    }
-                    __syncwarp();
-                    float f[32];
-                    duo_scale(hh == 0 ? va : vb, f, nn, p.N, p.alpha, p.bias);
-                    if (out16) duo_put16_64(f, buf, lane, bf16);
-                    else duo_put32(f, buf + (uint32_t)lane * 128u, lane);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) {
-                        // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
-                        // lies outside altogether still closes an (empty) group, so that the group counts above hold
-                        if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
-                        bulk_commit_group();
-                    }
-                    ++nstore;
-                }
-            }
+            tc_ld32(t_lane + 32u, vb);
+            tc_wait_ld();
+            emit(va, 0);
+            tc_ld32(t_lane + 64u, va);
+            emit(vb, 32);
+            tc_wait_ld();
+            tc_ld32(t_lane + 96u, vb);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);      // this warp's columns are all in registers
+            emit(va, 64);
+            emit(vb, 96);
         }
         if (lane == 0) bulk_wait_all();
     } else if (warp < 10) {
