@@ -159,12 +159,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 template <int KIND>
 __device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                        uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
@@ -205,11 +199,6 @@ __device__ __forceinline__ bool elect_one() {
 // 128-byte swizzle span: 8-row groups 1024 bytes apart, SWIZZLE_128B, version 1
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
     return (uint64_t)((saddr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-// descriptor of one 512-byte scale atom: 32 rows of 16 bytes, no swizzle,
-// 8-row groups 128 bytes apart
-__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3fffu) | (8ull << 32) | (1ull << 46);
 }
 
 // Epilogue of one tile, run by the four epilogue warps (128 threads) of a CTA.  The accumulator
@@ -312,15 +301,6 @@ struct Cfg {
         ((uint32_t)(BN >> 3) << 17) | ((KIND == 0 ? 0u : 1u) << 23) | ((uint32_t)(BM >> 4) << 24);
 };
 
-// tcgen05 instructions guarded by a predicate held in a register: the issuing warp keeps
-// warp-uniform control flow (so that descriptors stay in uniform registers) and exactly one
-// lane has `on` set.
-__device__ __forceinline__ void tc_cp_sf_if(uint32_t on, uint32_t taddr, uint64_t sdesc) {
-    asm volatile(
-        "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
-        "@q tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}"
-        ::"r"(taddr), "l"(sdesc), "r"(on) : "memory");
-}
 __device__ __forceinline__ void tc_commit_if(uint32_t on, uint32_t bar) {
     asm volatile(
         "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
