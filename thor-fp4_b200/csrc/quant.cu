@@ -51,11 +51,19 @@ __device__ __forceinline__ uint32_t pack_codes_rne(const float (&y)[8]) {
     return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
 }
 
-__device__ __noinline__ uint32_t pack_codes_literal(const float (&f)[8], float ds) {
+// Arguments by value: a reference to the caller's array would pin that array in local memory
+// (a store of all eight values per row on the common path, for a call that almost never happens).
+__device__ __noinline__ uint32_t pack_codes_literal_v(float f0, float f1, float f2, float f3, float f4, float f5,
+                                                      float f6, float f7, float ds) {
+    const float f[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
     uint32_t w = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) w |= e2m1_ties_up(__fdiv_rn(f[i], ds)) << (4 * i);
     return w;
+}
+__device__ __noinline__ uint32_t code_literal(float f, float ds) { return e2m1_ties_up(__fdiv_rn(f, ds)); }
+__device__ __forceinline__ uint32_t pack_codes_literal(const float (&f)[8], float ds) {
+    return pack_codes_literal_v(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], ds);
 }
 
 __device__ __forceinline__ float fma_pz(float a, float b) {  // a*b + (+0): maps -0 to +0
@@ -86,6 +94,10 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     const int64_t col = c0 + lane * 8;
     const bool col_ok = col < K;
     const int64_t Rpad = pad128(R);
+
+    // reciprocals of the per-tensor scale biased by +-2^-20 (bracket modes only)
+    const float rts = __frcp_rn(ts);
+    const float rts_hi = rts * 1.00000095367431640625f, rts_lo = rts * 0.99999904632568359375f;
 
     reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
     __syncthreads();
@@ -133,8 +145,19 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                 for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[u][i]));
                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
                 float pre = amax * (1.0f / 6.0f);
-                if (MODE != 0) pre = __fdiv_rn(pre, ts);   // (amax * (1/6)) / ts, the reference's operand order
-                const uint32_t sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
+                uint32_t sc;
+                if (MODE == 1 || MODE == 3) {
+                    // (amax * (1/6)) / ts without the IEEE division in the common case: two products with reciprocals of ts
+                    // biased by +-2^-20 bracket the quotient (and its float rounding); e4m3 rounding is monotonic, so when
+                    // both ends encode alike that is the encoding of the quotient.  Otherwise (about 2^-16 of the blocks)
+                    // the literal division decides.
+                    const uint32_t both = f32x2_to_e4m3x2(pre * rts_lo, pre * rts_hi);
+                    sc = both & 0x7fu;
+                    if (sc != ((both >> 8) & 0x7fu)) sc = f32x2_to_e4m3x2(__fdiv_rn(pre, ts), 0.f) & 0x7fu;
+                } else {
+                    if (MODE != 0) pre = __fdiv_rn(pre, ts);   // (amax * (1/6)) / ts, the reference's operand order
+                    sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
+                }
                 const float sf = e4m3_to_f32(sc);
                 const float ds = (MODE != 0) ? sf * ts : sf;
                 if ((lane & 1) == 0 && col_ok) {
@@ -148,7 +171,9 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                     for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
                     codes = pack_codes_rne(y);
                 } else if (MODE == 1 || MODE == 3) {
-                    const float rr = __frcp_rn(ds);
+                    // 1/ds to within one ulp is enough here: the +-2^-20 margins still bracket the true quotient
+                    float rr;
+                    asm("rcp.approx.f32 %0, %1;" : "=f"(rr) : "f"(ds));
                     const float r_hi = rr * 1.00000095367431640625f;   // 1 + 2^-20
                     const float r_lo = rr * 0.99999904632568359375f;   // 1 - 2^-20
                     float yh[8], yl[8];
@@ -162,7 +187,17 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                     }
                     codes = pack_codes_rne(yh);
                     const uint32_t cl = pack_codes_rne(yl);
-                    if (cl != codes || tiny) codes = pack_codes_literal(f[u], ds);
+                    if (MODE == 1 && tiny) {
+                        codes = pack_codes_literal(f[u], ds);
+                    } else if (cl != codes) {
+                        // only the elements whose two ends disagree take the division (16-bit inputs times a
+                        // short per-tensor scale land exactly on rounding boundaries far more often than chance)
+                        const uint32_t diff = cl ^ codes;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if ((diff >> (4 * i)) & 0xfu)
+                                codes = (codes & ~(0xfu << (4 * i))) | (code_literal(f[u][i], ds) << (4 * i));
+                    }
                 } else {
                     codes = pack_codes_literal(f[u], ds);
                 }
