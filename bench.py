@@ -285,6 +285,21 @@ def run_sweep(args):
             cnt[0] += 1
         us = timed(qstep, args.steps)
         print(f"| quantize bf16 [{R}, {K}] | - | quant_nvfp4_kernel | {us:.1f} | - | {R * K * 2.5625 / us / 1e3:.0f} (algorithmic bytes) |", flush=True)
+        if R == 16384:
+            # the same shape with a per-tensor scale (a decimal one, whose products with 16-bit inputs land on
+            # rounding boundaries, and an arbitrary one), and with FP32 input
+            for dt, nm, bpe in ((torch.bfloat16, "bf16", 2.5625), (torch.float32, "f32", 4.5625)):
+                xs = xq if dt == torch.bfloat16 else [t.float() for t in xq[:2]]
+                for ts in (0.37, 0.3712345):
+                    cnt[0] = 0
+
+                    def qstep_ts():
+                        ops.quantize_nvfp4(xs[cnt[0] % len(xs)], ts, pq, sq)
+                        cnt[0] += 1
+                    us = timed(qstep_ts, args.steps)
+                    print(f"| quantize {nm} [{R}, {K}] ts={ts} | - | quant_nvfp4_kernel | {us:.1f} | - | {R * K * bpe / us / 1e3:.0f} (algorithmic bytes) |",
+                          flush=True)
+                del xs
         del xq, pq, sq
         torch.cuda.empty_cache()
     # batch-1 engines: exact-activation GEMV (one launch) against quantize + split-K GEMM

@@ -72,6 +72,15 @@ __device__ __forceinline__ float fma_pz(float a, float b) {  // a*b + (+0): maps
     return d;
 }
 
+// two products a0*b, a1*b in one packed instruction, each + (+0) like fma_pz
+__device__ __forceinline__ void mul2_pz(float& d0, float& d1, float a0, float a1, float b) {
+    uint64_t av, bv, dv;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(av) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(bv) : "f"(b));
+    asm("{\n\t.reg .b64 z;\n\tmov.b64 z, 0;\n\tfma.rn.f32x2 %0, %1, %2, z;\n\t}" : "=l"(dv) : "l"(av), "l"(bv));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(dv));
+}
+
 // MODE 0: EXACT16 (16-bit input, ts == 1); 1: BRACKET; 2: LITERAL (always divide);
 // 3: BRACKET without the tiny-input check (16-bit input and ts <= 128: the smallest non-zero
 // input, 2^-133, divided by the largest ds, 448 * 128, stays far above the 2^-150 underflow bound).
@@ -179,11 +188,14 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                     float yh[8], yl[8];
                     bool tiny = false;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        yh[i] = fma_pz(f[u][i], r_hi);
-                        yl[i] = fma_pz(f[u][i], r_lo);
-                        // 0 < |x| < 2^-100 (bits 0x0d800000): quotient may underflow
-                        if (MODE == 1) tiny |= ((__float_as_uint(f[u][i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
+                    for (int i = 0; i < 8; i += 2) {
+                        mul2_pz(yh[i], yh[i + 1], f[u][i], f[u][i + 1], r_hi);
+                        mul2_pz(yl[i], yl[i + 1], f[u][i], f[u][i + 1], r_lo);
+                    }
+                    if (MODE == 1) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)   // 0 < |x| < 2^-100 (bits 0x0d800000): quotient may underflow
+                            tiny |= ((__float_as_uint(f[u][i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
                     }
                     codes = pack_codes_rne(yh);
                     const uint32_t cl = pack_codes_rne(yl);
