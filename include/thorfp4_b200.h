@@ -102,6 +102,13 @@ int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype,
 int tfp4_act_quant_mx8(const void* acc, const float* bias, int64_t R, int64_t N, int in_dtype, int act,
                        uint8_t* packed, uint8_t* sblk, void* stream);
 
+/* Replaces the forward pass of the reference's quantization-aware-training fake quantizer (src/thor_fp4/quant.py:32-53,
+ * a chain of torch kernels over FP32 temporaries) as one pass: y = dequantize(quantize(x)) over n elements taken as
+ * consecutive 16-element blocks, with the scale bytes and codes tfp4_quant would produce (ties up, IEEE division,
+ * blocks whose scale byte is 0 give zeros); no codes or scales are stored.  n % 16 == 0; in_dtype 0 f32, 1 f16,
+ * 2 bf16; out_dtype 0 f16, 1 bf16, 2 f32 (the reference returns f32; a 16-bit output is that value rounded once). */
+int tfp4_fake_quant(const void* x, int64_t n, int in_dtype, float tensor_scale, void* y, int out_dtype, void* stream);
+
 /* No counterpart in the reference.  tfp4_gemm_bias for callers that must not allocate at call time
  * (device memory fully pre-partitioned at start-up, a plug-in under a foreign allocator, a loop
  * that cannot afford the device-wide synchronisation of an allocation or a free): the kernel's scratch - status word, counters, split-K partial sums - sits in a

@@ -109,6 +109,44 @@ def test_convert_on_cpu_model_records_decisions():
     assert set(cal) == {"0", "2", "3"}
 
 
+def test_row_slices_and_checkpoint_of_a_quantized_tensor(tmp_path):
+    # a row slice starting on a 128-row boundary is a pointer offset into the code and scale buffers:
+    # it must equal the oracle's quantization of those rows alone (same per-tensor scale)
+    from thor_fp4.ops import NVFP4Tensor
+    rng = np.random.default_rng(5)
+    R, K = 700, 320                                      # ragged last tile, scale columns not a multiple of 4 tiles
+    x = (rng.standard_normal((R, K)) * np.logspace(-2, 1, K)).astype(np.float32)
+    ts = orc.two_level_scale(x)
+    p, sc = orc.quantize_nvfp4(x, ts)
+    t = NVFP4Tensor(torch.from_numpy(p), torch.from_numpy(sc), ts, (R, K))
+    for a, b in ((0, 128), (128, 512), (256, 300), (640, 700), (0, 700)):
+        v = t.rows(a, b)
+        po, so = orc.quantize_nvfp4(x[a:b], ts)
+        n = b - a
+        assert v.shape == (n, K) and v.tensor_scale == ts
+        assert np.array_equal(v.packed.numpy()[: n * K // 2], po[: n * K // 2])
+        want = orc.dequantize_nvfp4(po, so, ts, n, K)
+        got = orc.dequantize_nvfp4(v.packed.numpy(), v.sblk.numpy(), ts, n, K)
+        assert np.array_equal(got, want)
+        assert v.packed.data_ptr() == t.packed.data_ptr() + a * K // 2          # a view, not a copy
+    assert [r0 for r0, _ in t.row_chunks(256)] == [0, 256, 512]
+    assert [c.shape[0] for _, c in t.row_chunks(256)] == [256, 256, 188]
+    with pytest.raises(AssertionError):
+        t.rows(64, 128)
+    # checkpoint round trip: same bytes, same scale, refuses foreign or truncated files
+    f = tmp_path / "w.nvfp4.pt"
+    t.save(f)
+    u = NVFP4Tensor.load(f)
+    assert u.shape == t.shape and u.tensor_scale == t.tensor_scale
+    assert torch.equal(u.packed, t.packed) and torch.equal(u.sblk, t.sblk)
+    bad = dict(t.state_dict(), format="something else")
+    with pytest.raises(ValueError):
+        NVFP4Tensor.from_state_dict(bad)
+    short = dict(t.state_dict(), packed=t.packed[:-1])
+    with pytest.raises(ValueError):
+        NVFP4Tensor.from_state_dict(short)
+
+
 def test_sharding_helpers():
     from thor_fp4.parallel import shard_cols, shard_rows
     w = torch.arange(256 * 128, dtype=torch.float32).reshape(256, 128)

@@ -1,6 +1,8 @@
 """thor_fp4.Linear / convert / calibrate / verify / capture_module on the GPU: the same
 behaviours the reference's own tests pin (tests/test_linear.py, test_verify.py,
 test_convert.py, test_graphs_cascade.py, test_gemv.py there), against this engine."""
+import os
+
 import pytest
 import torch
 import torch.nn as nn
@@ -209,3 +211,49 @@ def test_plan_cache_is_allocation_free_after_warmup():
     h1, m1 = _ext.plan_stats()
     assert m1 == m0 and h1 == h0 + 5
     assert torch.cuda.memory_allocated() == mem0
+
+
+@gpu
+def test_chunked_sweep_over_row_slices_equals_full_gemm():
+    # a resident library swept in 256-row chunks (pointer offsets into codes and scale tiles) gives the
+    # same scores as one GEMM over the whole library; the planted neighbour is found in its own chunk
+    import thor_fp4
+    from thor_fp4 import ops
+    g = torch.Generator(device="cuda").manual_seed(11)
+    lib = torch.randn(1000, 512, device="cuda", generator=g)
+    lib = lib / lib.norm(dim=1, keepdim=True)
+    q = torch.randn(4, 512, device="cuda", generator=g)
+    q[2] = lib[777] * 3.0
+    L = thor_fp4.NVFP4Tensor.from_float(lib.contiguous())
+    Q = thor_fp4.NVFP4Tensor.from_float(q.contiguous(), 1.0)
+    full = Q.matmul_t(L, "f32")
+    parts = torch.empty_like(full)
+    for r0, chunk in L.row_chunks(256):
+        parts[:, r0:r0 + chunk.shape[0]] = Q.matmul_t(chunk, "f32")
+    torch.cuda.synchronize()
+    assert torch.equal(parts, full)
+    assert int(full[2].argmax()) == 777
+
+
+@gpu
+def test_quantized_checkpoint_restores_the_layer_bit_for_bit(tmp_path):
+    import thor_fp4
+    torch.manual_seed(2)
+    a = thor_fp4.Linear(256, 192, bias=True, out_dtype="bf16", device="cuda", act_tensor_scale=0.5)
+    with torch.no_grad():
+        a.bias.normal_()
+    x = torch.randn(33, 256, device="cuda").bfloat16()
+    ya = a(x).clone()
+    f = tmp_path / "layer.pt"
+    torch.save(a.quantized_state(), f)
+    b = thor_fp4.Linear(256, 192, bias=True, out_dtype="bf16", device="cuda")
+    b.load_quantized_state(torch.load(f, map_location="cpu", weights_only=True))
+    assert torch.equal(b(x), ya)
+    assert torch.equal(b._weight_fp4.packed, a._weight_fp4.packed) and torch.equal(b._weight_fp4.sblk, a._weight_fp4.sblk)
+    b.refresh_weight()        # the master weight is the dequantized value: re-quantizing it gives the same values
+    assert torch.equal(b._weight_fp4.sblk, a._weight_fp4.sblk)     # (codes may differ in the sign nibble of zeros)
+    assert torch.equal(b._weight_fp4.dequantize(), a._weight_fp4.dequantize())
+    assert torch.equal(b(x), ya)
+    assert os.path.getsize(f) < 0.4 * (256 * 192 * 4)
+    with pytest.raises(ValueError):
+        thor_fp4.Linear(256, 128, device="cuda").load_quantized_state(torch.load(f, map_location="cpu", weights_only=True))

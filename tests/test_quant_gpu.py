@@ -214,3 +214,74 @@ def test_full_size_round_trip_properties():
     assert torch.equal(s, s2)
     assert torch.equal(thor_fp4.dequantize_nvfp4(p2, s2, 1.0, R, K), d)
     assert torch.equal(thor_fp4.nvfp4_fake_quant(x[:256].float()), d[:256])
+
+
+# --------------------------------------------------------------------------- fused fake quantizer (QAT forward)
+@gpu
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("ts", [1.0, "two_level", 0.37, 3.7, 2.0 ** -7])
+def test_fake_quant_kernel_equals_oracle_and_torch_chain(dt, ts):
+    # one kernel against (a) the CPU oracle's quantize -> dequantize and (b) the torch restatement of the
+    # reference's fake quantizer (src/thor_fp4/quant.py:32-53) on the same tensor; bit-exact (-0 == +0)
+    import thor_fp4
+    from thor_fp4 import ops
+    x = _adversarial(300, 1024, dt)
+    x[5, 0], x[5, 17], x[5, 33] = 1.0, -2.0, 0.5          # the fake quantizer is defined on finite data
+    if ts == "two_level":
+        ts = max(x.float().abs().max().item() / (6.0 * 448.0), 1e-30)
+    y = ops.fake_quantize_nvfp4(x, float(ts))
+    torch.cuda.synchronize()
+    assert y.dtype == torch.float32 and y.shape == x.shape
+    yo = orc.nvfp4_fake_quant(x.float().cpu().numpy(), float(ts))
+    assert torch.equal(y.cpu(), torch.from_numpy(yo)), "differs from the oracle"
+    assert torch.equal(y, thor_fp4.nvfp4_fake_quant(x, float(ts))), "differs from the torch chain"
+
+
+@gpu
+@pytest.mark.parametrize("K", [320, 1024, 2048])
+@pytest.mark.parametrize("mode", ["block", "two"])
+def test_fake_quant_kernel_golden_vectors(golden, K, mode):
+    from thor_fp4 import ops
+    x = torch.from_numpy(golden[f"nv_K{K}_x"]).cuda()
+    ts = float(golden[f"nv_K{K}_{mode}_ts"])
+    assert torch.equal(ops.fake_quantize_nvfp4(x, ts).cpu(), torch.from_numpy(golden[f"nv_K{K}_{mode}_y"]))
+
+
+@gpu
+def test_fake_quant_kernel_shapes_outputs_and_errors():
+    import thor_fp4
+    from thor_fp4 import ops
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(3, 5, 48, device="cuda", generator=g)              # any shape, flat 16-element blocks
+    y = ops.fake_quantize_nvfp4(x, 0.5)
+    assert torch.equal(y, thor_fp4.nvfp4_fake_quant(x, 0.5))
+    xb = x.bfloat16()
+    yb = ops.fake_quantize_nvfp4(xb, 1.0, out_dtype=torch.bfloat16)     # per-tensor scale 1: values fit bf16 exactly
+    assert yb.dtype == torch.bfloat16 and torch.equal(yb.float(), thor_fp4.nvfp4_fake_quant(xb, 1.0))
+    big = torch.randn(1 << 22, device="cuda", generator=g) * 4.0         # several grid-stride rounds, ragged tail
+    big = big[: (1 << 22) - 16 * 37]
+    assert torch.equal(ops.fake_quantize_nvfp4(big, 1.3), thor_fp4.nvfp4_fake_quant(big, 1.3))
+    assert ops.fake_quantize_nvfp4(torch.zeros(0, 16, device="cuda")).numel() == 0
+    with pytest.raises(AssertionError):
+        ops.fake_quantize_nvfp4(torch.zeros(3, 5, device="cuda"))
+
+
+@gpu
+def test_qat_forward_uses_the_kernel_and_gradient_is_straight_through():
+    # reference tests/test_qat.py pattern: fake-quantized forward, identity backward
+    import thor_fp4
+    from thor_fp4 import quant
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(64, 32).cuda()
+    q = quant.qat_linear(lin, two_level=True).cuda()
+    x = torch.randn(8, 64, device="cuda", requires_grad=True)
+    y = q(x)
+    wts = quant.two_level_scale(q.weight)
+    want = torch.nn.functional.linear(quant.nvfp4_fake_quant(x.detach()), quant.nvfp4_fake_quant(q.weight.detach(), wts), q.bias)
+    assert torch.equal(y, want)
+    y.sum().backward()
+    assert x.grad is not None and q.weight.grad is not None
+    assert torch.allclose(q.weight.grad, x.detach().new_ones(8, 32).t() @ quant.nvfp4_fake_quant(x.detach()))
+    v = torch.randn(4, 32, device="cuda", requires_grad=True)
+    quant.qat(v, 0.7).backward(torch.full_like(v, 2.0))
+    assert torch.equal(v.grad, torch.full_like(v, 2.0))

@@ -20,6 +20,7 @@ void gemm_set_pair_mode(int);
 void gemm_set_splits(int);
 void quant_set_tile_rows(int);
 int act_quant_mx8(const void*, const float*, int64_t, int64_t, int, int, uint8_t*, uint8_t*, cudaStream_t);
+int fake_quant_nvfp4(const void*, int64_t, int, float, void*, int, cudaStream_t);
 int swiglu_quant_nvfp4(const void*, int64_t, int64_t, int, uint8_t*, uint8_t*, cudaStream_t);
 int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
                  int64_t, int, cudaStream_t);
@@ -129,6 +130,10 @@ int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype, uint8_
 int tfp4_act_quant_mx8(const void* acc, const float* bias, int64_t R, int64_t N, int in_dtype, int act, uint8_t* packed,
                        uint8_t* sblk, void* stream) {
     return tfp4::act_quant_mx8(acc, bias, R, N, in_dtype, act, packed, sblk, S(stream));
+}
+
+int tfp4_fake_quant(const void* x, int64_t n, int in_dtype, float tensor_scale, void* y, int out_dtype, void* stream) {
+    return tfp4::fake_quant_nvfp4(x, n, in_dtype, tensor_scale, y, out_dtype, S(stream));
 }
 
 int tfp4_gemm_noalloc(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB,

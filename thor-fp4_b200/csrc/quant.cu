@@ -81,6 +81,79 @@ __device__ __forceinline__ void mul2_pz(float& d0, float& d1, float a0, float a1
     asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(dv));
 }
 
+// One half block (8 consecutive elements held by this lane, the other 8 by lane ^ 1): the block's scale
+// byte `sc`; returns the decode scale ds = dec(sc) * ts.  Every lane of the warp must call it (one shuffle).
+// rts_lo / rts_hi: 1/ts biased by -+2^-20 (bracket modes only).
+template <int MODE>
+__device__ __forceinline__ float block_scale8(const float (&f)[8], float ts, float rts_lo, float rts_hi, uint32_t& sc) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    float pre = amax * (1.0f / 6.0f);
+    if (MODE == 1 || MODE == 3) {
+        // (amax * (1/6)) / ts without the IEEE division in the common case: two products with reciprocals of ts
+        // biased by +-2^-20 bracket the quotient (and its float rounding); e4m3 rounding is monotonic, so when
+        // both ends encode alike that is the encoding of the quotient.  Otherwise (about 2^-16 of the blocks)
+        // the literal division decides.
+        const uint32_t both = f32x2_to_e4m3x2(pre * rts_lo, pre * rts_hi);
+        sc = both & 0x7fu;
+        if (sc != ((both >> 8) & 0x7fu)) sc = f32x2_to_e4m3x2(__fdiv_rn(pre, ts), 0.f) & 0x7fu;
+    } else {
+        if (MODE != 0) pre = __fdiv_rn(pre, ts);   // (amax * (1/6)) / ts, the reference's operand order
+        sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
+    }
+    const float sf = e4m3_to_f32(sc);
+    return (MODE != 0) ? sf * ts : sf;
+}
+
+// The eight e2m1 codes of this lane's elements (element i in nibble i) for the decode scale ds.
+template <int MODE>
+__device__ __forceinline__ uint32_t block_codes8(const float (&f)[8], float ds) {
+    uint32_t codes = 0;
+    if (MODE == 0) {
+        const float rb = __frcp_rn(ds) * 1.000000476837158203125f;   // * (1 + 2^-21)
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[i], rb);
+        codes = pack_codes_rne(y);
+    } else if (MODE == 1 || MODE == 3) {
+        // 1/ds to within one ulp is enough here: the +-2^-20 margins still bracket the true quotient
+        float rr;
+        asm("rcp.approx.f32 %0, %1;" : "=f"(rr) : "f"(ds));
+        const float r_hi = rr * 1.00000095367431640625f;   // 1 + 2^-20
+        const float r_lo = rr * 0.99999904632568359375f;   // 1 - 2^-20
+        float yh[8], yl[8];
+        bool tiny = false;
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            mul2_pz(yh[i], yh[i + 1], f[i], f[i + 1], r_hi);
+            mul2_pz(yl[i], yl[i + 1], f[i], f[i + 1], r_lo);
+        }
+        if (MODE == 1) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)   // 0 < |x| < 2^-100 (bits 0x0d800000): quotient may underflow
+                tiny |= ((__float_as_uint(f[i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
+        }
+        codes = pack_codes_rne(yh);
+        const uint32_t cl = pack_codes_rne(yl);
+        if (MODE == 1 && tiny) {
+            codes = pack_codes_literal(f, ds);
+        } else if (cl != codes) {
+            // only the elements whose two ends disagree take the division (16-bit inputs times a
+            // short per-tensor scale land exactly on rounding boundaries far more often than chance)
+            const uint32_t diff = cl ^ codes;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if ((diff >> (4 * i)) & 0xfu)
+                    codes = (codes & ~(0xfu << (4 * i))) | (code_literal(f[i], ds) << (4 * i));
+        }
+    } else {
+        codes = pack_codes_literal(f, ds);
+    }
+    return codes;
+}
+
 // MODE 0: EXACT16 (16-bit input, ts == 1); 1: BRACKET; 2: LITERAL (always divide);
 // 3: BRACKET without the tiny-input check (16-bit input and ts <= 128: the smallest non-zero
 // input, 2^-133, divided by the largest ds, 448 * 128, stays far above the 2^-150 underflow bound).
@@ -149,70 +222,13 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
             const int64_t r = r0 + rl;
             uint32_t codes = 0;
             if (r < R) {   // warp-uniform: every lane takes part in the shuffles
-                float amax = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[u][i]));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                float pre = amax * (1.0f / 6.0f);
                 uint32_t sc;
-                if (MODE == 1 || MODE == 3) {
-                    // (amax * (1/6)) / ts without the IEEE division in the common case: two products with reciprocals of ts
-                    // biased by +-2^-20 bracket the quotient (and its float rounding); e4m3 rounding is monotonic, so when
-                    // both ends encode alike that is the encoding of the quotient.  Otherwise (about 2^-16 of the blocks)
-                    // the literal division decides.
-                    const uint32_t both = f32x2_to_e4m3x2(pre * rts_lo, pre * rts_hi);
-                    sc = both & 0x7fu;
-                    if (sc != ((both >> 8) & 0x7fu)) sc = f32x2_to_e4m3x2(__fdiv_rn(pre, ts), 0.f) & 0x7fu;
-                } else {
-                    if (MODE != 0) pre = __fdiv_rn(pre, ts);   // (amax * (1/6)) / ts, the reference's operand order
-                    sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
-                }
-                const float sf = e4m3_to_f32(sc);
-                const float ds = (MODE != 0) ? sf * ts : sf;
+                const float ds = block_scale8<MODE>(f[u], ts, rts_lo, rts_hi, sc);
                 if ((lane & 1) == 0 && col_ok) {
                     const int sl = lane >> 1;   // scale column inside the tile, 0..15
                     s_sf[(sl >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (sl & 3)] = (uint8_t)sc;
                 }
-                if (MODE == 0) {
-                    const float rb = __frcp_rn(ds) * 1.000000476837158203125f;   // * (1 + 2^-21)
-                    float y[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
-                    codes = pack_codes_rne(y);
-                } else if (MODE == 1 || MODE == 3) {
-                    // 1/ds to within one ulp is enough here: the +-2^-20 margins still bracket the true quotient
-                    float rr;
-                    asm("rcp.approx.f32 %0, %1;" : "=f"(rr) : "f"(ds));
-                    const float r_hi = rr * 1.00000095367431640625f;   // 1 + 2^-20
-                    const float r_lo = rr * 0.99999904632568359375f;   // 1 - 2^-20
-                    float yh[8], yl[8];
-                    bool tiny = false;
-#pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
-                        mul2_pz(yh[i], yh[i + 1], f[u][i], f[u][i + 1], r_hi);
-                        mul2_pz(yl[i], yl[i + 1], f[u][i], f[u][i + 1], r_lo);
-                    }
-                    if (MODE == 1) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)   // 0 < |x| < 2^-100 (bits 0x0d800000): quotient may underflow
-                            tiny |= ((__float_as_uint(f[u][i]) & 0x7fffffffu) - 1u) < 0x0d7fffffu;
-                    }
-                    codes = pack_codes_rne(yh);
-                    const uint32_t cl = pack_codes_rne(yl);
-                    if (MODE == 1 && tiny) {
-                        codes = pack_codes_literal(f[u], ds);
-                    } else if (cl != codes) {
-                        // only the elements whose two ends disagree take the division (16-bit inputs times a
-                        // short per-tensor scale land exactly on rounding boundaries far more often than chance)
-                        const uint32_t diff = cl ^ codes;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            if ((diff >> (4 * i)) & 0xfu)
-                                codes = (codes & ~(0xfu << (4 * i))) | (code_literal(f[u][i], ds) << (4 * i));
-                    }
-                } else {
-                    codes = pack_codes_literal(f[u], ds);
-                }
+                codes = block_codes8<MODE>(f[u], ds);
             }
             if (col_ok && r < Rpad)
                 *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
@@ -238,6 +254,67 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
         const int atom = threadIdx.x >> 5, off = atom * 512 + 16 * (threadIdx.x & 31) + (ra >> 3);
         if (atom < n_atoms)
             *reinterpret_cast<uint2*>(tile + off) = *reinterpret_cast<const uint2*>(s_sf + off);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Fake quantizer (the forward pass of quantization-aware training): y = dequantize(quantize(x)) in
+// one pass, no codes or scales stored.  Follows src/thor_fp4/quant.py:32-53: the value is
+// code * sign * (dec(sc) * ts) with the same scale byte and codes as the quantizer above, and a
+// block whose scale byte is 0 gives zeros.  The tensor is flat: consecutive 16-element blocks,
+// a lane holds 8 elements, lane pairs share a block.
+// ---------------------------------------------------------------------------
+constexpr int FQ_THREADS = 256;
+constexpr int FQ_UNROLL = 4;   // chunks of 8 elements in flight per thread
+
+template <typename T, typename TO, int MODE>
+__global__ void __launch_bounds__(FQ_THREADS)
+fake_quant_nvfp4_kernel(const T* __restrict__ x, int64_t n_chunks, float ts, TO* __restrict__ y) {
+    const float rts = __frcp_rn(ts);
+    const float rts_hi = rts * 1.00000095367431640625f, rts_lo = rts * 0.99999904632568359375f;
+    const int64_t per_cta = (int64_t)FQ_THREADS * FQ_UNROLL;
+    // n_chunks is even and a CTA's first chunk is even, so a lane and its partner (lane ^ 1) are inside
+    // or outside together; chunks past the end are processed as zeros (every lane takes the shuffle)
+    for (int64_t base = (int64_t)blockIdx.x * per_cta; base < n_chunks; base += (int64_t)gridDim.x * per_cta) {
+        Raw8<T> raw[FQ_UNROLL];
+#pragma unroll
+        for (int u = 0; u < FQ_UNROLL; ++u) {
+            const int64_t c = base + u * FQ_THREADS + threadIdx.x;
+            raw[u] = c < n_chunks ? fetch8<T>(x + c * 8) : zero8<T>();
+        }
+#pragma unroll
+        for (int u = 0; u < FQ_UNROLL; ++u) {
+            const int64_t c = base + u * FQ_THREADS + threadIdx.x;
+            float f[8];
+            widen8(raw[u], f);
+            uint32_t sc;
+            const float ds = block_scale8<MODE>(f, ts, rts_lo, rts_hi, sc);
+            const uint32_t codes = block_codes8<MODE>(f, ds);
+            const float dz = sc != 0u ? ds : 0.f;     // scale byte 0: the block decodes to zeros
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                e2m1x2_to_f32x2((codes >> (8 * i)) & 0xffu, o[2 * i], o[2 * i + 1]);
+                o[2 * i] *= dz;
+                o[2 * i + 1] *= dz;
+            }
+            if (c < n_chunks) {
+                if constexpr (sizeof(TO) == 4) {
+                    float4* dst = reinterpret_cast<float4*>(y + c * 8);
+                    dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+                    dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+                } else {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const TO a = cast_out<TO>(o[2 * i]), b = cast_out<TO>(o[2 * i + 1]);
+                        w[i] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&a)) |
+                               ((uint32_t)(*reinterpret_cast<const uint16_t*>(&b)) << 16);
+                    }
+                    *reinterpret_cast<uint4*>(y + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
     }
 }
 
@@ -479,6 +556,40 @@ int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* p
     return launch_quant_nvfp4_rows<T, 128>(xp, R, K, ts, packed, sblk, stream);
 }
 
+template <typename T, typename TO>
+int launch_fake_quant(const void* x, int64_t n, float ts, void* y, cudaStream_t stream) {
+    const int64_t n_chunks = n / 8;
+    const int64_t per_cta = (int64_t)FQ_THREADS * FQ_UNROLL;
+    int64_t ctas = (n_chunks + per_cta - 1) / per_cta;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (ctas > (int64_t)sms * 16) ctas = (int64_t)sms * 16;   // grid-stride beyond 16 CTAs per SM
+    const T* xp = static_cast<const T*>(x);
+    TO* yp = static_cast<TO*>(y);
+    const bool ts_sane = (ts >= 0x1p-100f) && (ts <= 0x1p30f);
+    if (!ts_sane) {
+        fake_quant_nvfp4_kernel<T, TO, 2><<<(unsigned)ctas, FQ_THREADS, 0, stream>>>(xp, n_chunks, ts, yp);
+    } else if (sizeof(T) == 2 && ts == 1.0f) {
+        fake_quant_nvfp4_kernel<T, TO, 0><<<(unsigned)ctas, FQ_THREADS, 0, stream>>>(xp, n_chunks, ts, yp);
+    } else if (sizeof(T) == 2 && ts <= 128.0f) {
+        fake_quant_nvfp4_kernel<T, TO, 3><<<(unsigned)ctas, FQ_THREADS, 0, stream>>>(xp, n_chunks, ts, yp);
+    } else {
+        fake_quant_nvfp4_kernel<T, TO, 1><<<(unsigned)ctas, FQ_THREADS, 0, stream>>>(xp, n_chunks, ts, yp);
+    }
+    TFP4_CK(cudaGetLastError());
+    return TFP4_OK;
+}
+
+template <typename T>
+int launch_fake_quant_in(const void* x, int64_t n, float ts, void* y, int out_dtype, cudaStream_t stream) {
+    switch (out_dtype) {
+        case OUT_F32: return launch_fake_quant<T, float>(x, n, ts, y, stream);
+        case OUT_F16: return launch_fake_quant<T, __half>(x, n, ts, y, stream);
+        default: return launch_fake_quant<T, __nv_bfloat16>(x, n, ts, y, stream);
+    }
+}
+
 template <typename T>
 int launch_quant_mx(const void* x, int64_t R, int64_t K, int kind, uint8_t* packed, uint8_t* sblk,
                     cudaStream_t stream) {
@@ -567,6 +678,24 @@ int quant_nvfp4(const void* x, int64_t R, int64_t K, int in_dtype, float ts, uin
         case IN_F32: return launch_quant_nvfp4<float>(x, R, K, ts, packed, sblk, stream);
         case IN_F16: return launch_quant_nvfp4<__half>(x, R, K, ts, packed, sblk, stream);
         default: return launch_quant_nvfp4<__nv_bfloat16>(x, R, K, ts, packed, sblk, stream);
+    }
+}
+
+int fake_quant_nvfp4(const void* x, int64_t n, int in_dtype, float ts, void* y, int out_dtype, cudaStream_t stream) {
+    if (n < 0 || (n % 16) != 0) {
+        fprintf(stderr, "thor_fp4: tfp4_fake_quant needs a multiple of 16 elements (got %ld)\n", (long)n);
+        return TFP4_ERR_BAD_K;
+    }
+    if (n == 0) return TFP4_OK;
+    if (!x || !y || in_dtype < 0 || in_dtype > 2 || out_dtype < 0 || out_dtype > 2 ||
+        misaligned(x, in_dtype == IN_F32 ? 32 : 16) || misaligned(y, out_dtype == OUT_F32 ? 32 : 16)) {
+        fprintf(stderr, "thor_fp4: tfp4_fake_quant bad argument (buffers 16-byte, f32 ones 32-byte aligned)\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    switch (in_dtype) {
+        case IN_F32: return launch_fake_quant_in<float>(x, n, ts, y, out_dtype, stream);
+        case IN_F16: return launch_fake_quant_in<__half>(x, n, ts, y, out_dtype, stream);
+        default: return launch_fake_quant_in<__nv_bfloat16>(x, n, ts, y, out_dtype, stream);
     }
 }
 

@@ -41,6 +41,7 @@ SIGNATURES = {
                             i64, c_int, c_void]),
     "tfp4_act_quant_mx8": (c_int, [c_void, c_void, i64, i64, c_int, c_int, c_void, c_void, c_void]),
     "tfp4_swiglu_quant": (c_int, [c_void, i64, i64, c_int, c_void, c_void, c_void]),
+    "tfp4_fake_quant": (c_int, [c_void, i64, c_int, c_float, c_void, c_int, c_void]),
     "tfp4_gemm_noalloc": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
                                   i64, i64, i64, c_int, c_void]),
     "tfp4_gemm_noalloc_status": (c_int, [c_int]),

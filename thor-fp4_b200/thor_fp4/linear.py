@@ -139,6 +139,38 @@ class Linear(nn.Module):
             self._weight_fp4 = NVFP4Tensor.from_float(w, self._tensor_scale_requested)
         return self
 
+    # ------------------------------------------------------------------ quantized checkpoint
+    def quantized_state(self) -> dict:
+        """The layer as the GEMM sees it: NVFP4 weight (codes, scale tiles, per-tensor scale), bias and the
+        activation scale.  About 3.6x smaller than the FP32 state_dict; restoring it re-quantizes nothing."""
+        if self.engine_kind == "mx8":
+            raise RuntimeError("quantized_state covers NVFP4 weights; this layer holds an MXFP4 weight")
+        if self._weight_fp4 is None:
+            self.refresh_weight()
+        return {"weight_fp4": self._weight_fp4.state_dict(),
+                "bias": None if self.bias is None else self.bias.detach(),
+                "act_tensor_scale": float(self.act_tensor_scale), "out_dtype": self.out_dtype}
+
+    def load_quantized_state(self, state: dict):
+        """Install a quantized_state(): the codes are used as they are; the FP32 master weight becomes their
+        dequantized value (re-quantizing it with the stored per-tensor scale gives the same scale bytes and values
+        back; a value that had rounded to a negative zero comes back as a positive zero code)."""
+        if self.engine_kind == "mx8":
+            raise RuntimeError("load_quantized_state covers NVFP4 weights; this layer holds an MXFP4 weight")
+        w = NVFP4Tensor.from_state_dict(state["weight_fp4"], device=self.weight.device)
+        if tuple(w.shape) != (self.out_features, self.in_features):
+            raise ValueError(f"checkpoint weight is {tuple(w.shape)}, layer is {(self.out_features, self.in_features)}")
+        if (state.get("bias") is None) != (self.bias is None):
+            raise ValueError("checkpoint and layer disagree on having a bias")
+        with torch.no_grad():
+            self.weight.copy_(w.dequantize())
+            if self.bias is not None:
+                self.bias.copy_(state["bias"].to(self.bias.device))
+        self.act_tensor_scale = float(state.get("act_tensor_scale", self.act_tensor_scale))
+        self._tensor_scale_requested = w.tensor_scale
+        self._weight_fp4 = w
+        return self
+
     def _bias_f32(self):
         b = self.bias
         if b is None:

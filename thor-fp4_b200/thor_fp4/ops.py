@@ -15,7 +15,7 @@ from . import _ext
 
 __all__ = [
     "pad_rows", "packed_bytes", "scale_bytes", "mx_packed_bytes", "mx_scale_bytes",
-    "quantize_nvfp4", "quantize_mx", "mx8_mul", "dequantize_nvfp4", "block_scales",
+    "quantize_nvfp4", "fake_quantize_nvfp4", "quantize_mx", "mx8_mul", "dequantize_nvfp4", "block_scales",
     "gemm", "gemm_mx", "gemv", "NVFP4Tensor", "MXTensor",
 ]
 
@@ -80,6 +80,29 @@ def swiglu_quantize_nvfp4(gu: torch.Tensor, packed: torch.Tensor | None = None,
                              _ext.stream())
     assert rc == 0, f"tfp4_swiglu_quant rc={rc}"
     return packed, sblk
+
+
+_FQ_OUT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def fake_quantize_nvfp4(x: torch.Tensor, tensor_scale: float = 1.0, out: torch.Tensor | None = None,
+                        out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """dequantize(quantize(x)) in one kernel, no codes stored: the values of quant.nvfp4_fake_quant
+    (src/thor_fp4/quant.py:32-53 of the reference project) for a CUDA tensor of any shape whose element
+    count is a multiple of 16 (consecutive 16-element blocks of the flattened tensor)."""
+    assert x.is_cuda, "fake_quantize_nvfp4 needs a CUDA tensor"
+    L = _ext.device_lib()
+    if x.dtype not in _ext.IN_DTYPE:
+        x = x.float()
+    x = x.contiguous()
+    assert x.numel() % 16 == 0, "element count must be a multiple of 16"
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    assert out.is_cuda and out.is_contiguous() and out.numel() == x.numel() and out.dtype in _FQ_OUT
+    rc = L.tfp4_fake_quant(x.data_ptr(), x.numel(), _ext.IN_DTYPE[x.dtype], float(tensor_scale),
+                           out.data_ptr(), _FQ_OUT[out.dtype], _ext.stream())
+    assert rc == 0, f"tfp4_fake_quant failed ({rc})"
+    return out
 
 
 def quantize_mx(x: torch.Tensor, kind: str = "mxfp4",
@@ -242,6 +265,63 @@ class NVFP4Tensor:
     def nbytes(self) -> int:
         R, K = self.shape
         return R * K // 2 + R * (K // 16)
+
+    # ---- row slices: views into the same code and scale buffers (no copy) ----
+    def rows(self, start: int, stop: int | None = None) -> "NVFP4Tensor":
+        """Rows [start, stop) as a tensor over the same buffers.  Codes are row-major and scale tiles cover
+        128 rows each, so a slice that starts on a multiple of 128 is a pointer offset into both buffers
+        (how a resident library is swept chunk by chunk).  The last tile of the slice may hold rows of the
+        parent past `stop`; consumers read only `stop - start` rows of results."""
+        R, K = self.shape
+        stop = R if stop is None else stop
+        assert 0 <= start < stop <= R, f"bad row range [{start}, {stop}) of {R}"
+        assert start % 128 == 0, "a row slice must start on a multiple of 128 (scale tiles are 128 rows tall)"
+        n = stop - start
+        tile_bytes = ((K // 16 + 3) // 4) * 512                 # scale bytes per 128-row tile
+        p = self.packed[start * (K // 2): (start + pad_rows_host(n)) * (K // 2)]
+        sb = self.sblk[(start // 128) * tile_bytes: ((start + pad_rows_host(n)) // 128) * tile_bytes]
+        return NVFP4Tensor(p, sb, self.tensor_scale, (n, K))
+
+    def row_chunks(self, rows_per_chunk: int):
+        """Iterate (first_row, slice) over consecutive row slices; rows_per_chunk % 128 == 0."""
+        assert rows_per_chunk > 0 and rows_per_chunk % 128 == 0
+        for r0 in range(0, self.shape[0], rows_per_chunk):
+            yield r0, self.rows(r0, min(self.shape[0], r0 + rows_per_chunk))
+
+    # ---- checkpoint: the quantized tensor as it sits in memory ----
+    FORMAT = "nvfp4/e2m1-low-nibble-first/ue4m3-tiles-128x4/v1"
+
+    def state_dict(self) -> dict:
+        """Codes, scale tiles, per-tensor scale and shape: everything a GEMM needs, no FP32 copy."""
+        return {"format": self.FORMAT, "shape": tuple(self.shape), "tensor_scale": float(self.tensor_scale),
+                "packed": self.packed, "sblk": self.sblk}
+
+    @classmethod
+    def from_state_dict(cls, state: dict, device=None) -> "NVFP4Tensor":
+        if state.get("format") != cls.FORMAT:
+            raise ValueError(f"not an NVFP4 tensor checkpoint: format={state.get('format')!r}")
+        R, K = (int(v) for v in state["shape"])
+        packed, sblk = state["packed"], state["sblk"]
+        want_p, want_s = pad_rows_host(R) * (K // 2), (pad_rows_host(R) // 128) * ((K // 16 + 3) // 4) * 512
+        if (packed.dtype != torch.uint8 or sblk.dtype != torch.uint8 or K % 64 != 0
+                or packed.numel() != want_p or sblk.numel() != want_s):
+            raise ValueError(f"NVFP4 checkpoint buffers do not match shape ({R}, {K}): "
+                             f"{packed.numel()} code bytes (want {want_p}), {sblk.numel()} scale bytes (want {want_s})")
+        if device is not None:
+            packed, sblk = packed.to(device), sblk.to(device)
+        return cls(packed.contiguous(), sblk.contiguous(), float(state["tensor_scale"]), (R, K))
+
+    def save(self, path) -> None:
+        torch.save({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.state_dict().items()}, path)
+
+    @classmethod
+    def load(cls, path, device=None) -> "NVFP4Tensor":
+        return cls.from_state_dict(torch.load(path, map_location="cpu", weights_only=True), device)
+
+
+def pad_rows_host(R: int) -> int:
+    """Rows padded to whole 128-row scale tiles (host arithmetic, same value as pad_rows)."""
+    return (int(R) + 127) // 128 * 128
 
 
 class MXTensor:

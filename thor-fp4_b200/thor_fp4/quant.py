@@ -1,7 +1,7 @@
 """Torch-side quantizer arithmetic: fake quantizers, the two-level scale, PTQ
 calibration and QAT wrappers (API of src/thor_fp4/quant.py:15-148 in the reference
 project).  Device-agnostic torch code used by tests, verify() and QAT; the
-inference path never calls it.
+inference path never calls it.  The QAT forward (STE) runs the fused device kernel on CUDA tensors.
 
 Value semantics follow the device kernels: block scale = UE4M3 round trip of
 amax * (1/6) / ts (that operand order), codes = nearest e2m1 with midpoint ties
@@ -70,10 +70,14 @@ def mx_fake_quant(x: torch.Tensor, kind: str = "mxfp4", blk: int = 32) -> torch.
 
 
 class STE(torch.autograd.Function):
-    """Fake-quantized forward, identity gradient."""
+    """Fake-quantized forward, identity gradient.  On a CUDA tensor the forward is one fused kernel
+    (ops.fake_quantize_nvfp4, same values as nvfp4_fake_quant); on CPU the torch arithmetic above."""
 
     @staticmethod
     def forward(ctx, x, tensor_scale=1.0):
+        if x.is_cuda and x.dtype in (torch.float32, torch.float16, torch.bfloat16) and x.numel() % 16 == 0:
+            from . import ops
+            return ops.fake_quantize_nvfp4(x, float(tensor_scale))
         return nvfp4_fake_quant(x, tensor_scale)
 
     @staticmethod
