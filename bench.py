@@ -299,7 +299,17 @@ def run_sweep(args):
                     us = timed(qstep_ts, args.steps)
                     print(f"| quantize {nm} [{R}, {K}] ts={ts} | - | quant_nvfp4_kernel | {us:.1f} | - | {R * K * bpe / us / 1e3:.0f} (algorithmic bytes) |",
                           flush=True)
-                del xs
+                # the QAT forward (quantize -> dequantize in one kernel, f32 output) on the same inputs
+                yq = torch.empty(R, K, device="cuda")
+                cnt[0] = 0
+
+                def fq_step():
+                    ops.fake_quantize_nvfp4(xs[cnt[0] % len(xs)], 0.3712345, yq)
+                    cnt[0] += 1
+                us = timed(fq_step, args.steps)
+                print(f"| fake-quantize {nm} [{R}, {K}] ts=0.3712345 | - | fake_quant_nvfp4_kernel | {us:.1f} | - | {R * K * (bpe - 0.5625 + 4) / us / 1e3:.0f} (in + f32 out) |",
+                      flush=True)
+                del xs, yq
         del xq, pq, sq
         torch.cuda.empty_cache()
     # batch-1 engines: exact-activation GEMV (one launch) against quantize + split-K GEMM

@@ -166,6 +166,11 @@ void tfp4_set_token_tile(int bn);
  * for ablation timing (bit0 stores, bit1 scale copies, bit2 MMAs, bit3 loads, bit4 tensor-memory
  * reads; bit 1024 records per-CTA cycle counters read back with tfp4_debug_stats: 4 values per CTA). */
 void tfp4_set_pair_mode(int mode);
+/* No counterpart in the reference.  1 (default): the GEMM kernels and the split-K reduction are launched with
+ * programmatic stream serialization, so their prologue overlaps the tail of the kernel before them in the stream
+ * (normally the activation quantizer) and they wait for its completion before touching global memory; 0: plain
+ * stream order (A/B timing). */
+void tfp4_set_dependent_launch(int on);
 /* K split of small-batch GEMMs: 0 automatic, 1 never, n = about n K ranges (test hook). */
 void tfp4_set_splits(int n);
 void tfp4_set_debug(int bits);

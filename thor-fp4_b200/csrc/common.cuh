@@ -141,6 +141,13 @@ __device__ __forceinline__ void load8<__half>(const __half* p, float (&f)[8]) {
 }
 
 // raw 8-element fetch (kept in registers while older rows are processed) and its widening
+// Programmatic dependent launch.  griddep_launch: the next kernel in the stream, if it was launched with the
+// programmatic-serialization attribute, may start its prologue once every CTA of this grid has got here.
+// griddep_wait: blocks until the preceding grid has completed and its writes are visible (returns at once
+// when the kernel was launched without the attribute).
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 template <typename T> struct Raw8 { uint4 a; };
 template <> struct Raw8<float> { uint4 a, b; };
 

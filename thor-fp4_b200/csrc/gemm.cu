@@ -476,6 +476,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched only this CTA's shared and tensor memory; the operands may still be being
+    // written by the kernel before this one (programmatic dependent launch), so wait for it here
+    griddep_wait();
+    griddep_launch();
     // test hooks (tfp4_set_debug) exist only in the DBG instantiation
     const int dbg = DBG ? p.debug : 0;
 
@@ -770,6 +774,7 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t MN, int64
                      const float* __restrict__ bias, void* __restrict__ out, int out_dtype) {
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= MN) return;
+    griddep_wait();     // launched while the GEMM still runs; its partial sums are complete after this
     float4 acc = *reinterpret_cast<const float4*>(ws + i);
     for (int s = 1; s < splits; ++s) {
         const float4 v = *reinterpret_cast<const float4*>(ws + (int64_t)s * MN + i);
@@ -885,6 +890,8 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint6
     return TFP4_OK;
 }
 
+int g_pdl = 1;          // 1: GEMM and split-K reduction are launched as programmatic dependents of the kernel before them
+
 template <int KIND, int BN>
 int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaStream_t stream) {
     using C = Cfg<KIND, BN>;
@@ -904,15 +911,31 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     const int64_t tiles = p.m_tiles * p.n_tiles;
     const int64_t tiles_all = tiles * p.splits;
     const unsigned grid_all = (unsigned)(tiles_all < st->sm_count ? tiles_all : st->sm_count);
+    // Launched with programmatic stream serialization: the kernel may become resident and run its prologue
+    // (barriers, tensor-memory allocation) while the kernel before it in the stream - normally the activation
+    // quantizer - drains; it waits for that kernel's completion before its first global access.  The same
+    // holds for the reduction after a split-K GEMM.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid_all);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
     // the instantiation with the test hooks runs only while a debug mask is set
-    if (p.debug) gemm_bs_kernel<KIND, BN, true><<<grid_all, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
-    else gemm_bs_kernel<KIND, BN, false><<<grid_all, GEMM_THREADS, smem, stream>>>(plan.tmW, plan.tmA, p);
-    if (p.splits > 1) {
+    cudaError_t e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_bs_kernel<KIND, BN, true>, plan.tmW, plan.tmA, p)
+                            : cudaLaunchKernelEx(&cfg, gemm_bs_kernel<KIND, BN, false>, plan.tmW, plan.tmA, p);
+    if (e == cudaSuccess && p.splits > 1) {
         const int64_t MN = p.M * p.N;
-        splitk_reduce_kernel<<<(unsigned)((MN / 4 + 255) / 256), 256, 0, stream>>>(p.ws, p.splits, MN, p.N, p.bias, p.out,
-                                                                                   p.out_dtype);
+        cfg.gridDim = dim3((unsigned)((MN / 4 + 255) / 256));
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = 0;
+        e = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const float*)p.ws, (int)p.splits, MN, (int64_t)p.N,
+                               (const float*)p.bias, (void*)p.out, (int)p.out_dtype);
     }
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: GEMM launch failed: %s\n", cudaGetErrorString(e));
         return TFP4_ERR_LAUNCH;
@@ -998,13 +1021,15 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int d
     cfg.blockDim = dim3(DUO_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // prologue overlaps the quantizer's tail
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl ? 2 : 1;
     // the instantiation with the test hooks runs only while a debug mask is set
     cudaError_t e;
     if (kind == 0)
@@ -1288,6 +1313,7 @@ int gemm_warm() {
 
 void gemm_set_debug(int d) { g_debug = d; }
 void gemm_set_pair_mode(int m) { g_pair_mode = m; }
+void gemm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 // per-CTA cycle counters of the MMA-issuing thread, written when debug bit 1024 is set:
 // {total, waiting for operands, waiting for the accumulator, issuing}

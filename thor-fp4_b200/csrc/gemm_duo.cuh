@@ -356,6 +356,10 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     cluster_sync_all();      // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched only this CTA's shared and tensor memory; the operands may still be being
+    // written by the kernel before this one (programmatic dependent launch), so wait for it here
+    griddep_wait();
+    griddep_launch();
 
     const int64_t tiles_m = (p.M + C::TILE_M - 1) / C::TILE_M;
     const int64_t tiles_n = (p.N + C::TILE_N - 1) / C::TILE_N;

@@ -175,6 +175,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     cluster_sync_all();      // the peer's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched only this CTA's shared and tensor memory; the operands may still be being
+    // written by the kernel before this one (programmatic dependent launch), so wait for it here
+    griddep_wait();
+    griddep_launch();
 
     const int64_t n_pairs = (p.n_tiles + 1) / 2;        // 256-row weight tiles
     const int64_t total_tiles = p.m_tiles * n_pairs;

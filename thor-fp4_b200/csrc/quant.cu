@@ -167,6 +167,7 @@ __global__ void __launch_bounds__(QT_THREADS)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
     __shared__ __align__(16) uint8_t s_sf[4 * 512];
+    griddep_launch();   // the GEMM that consumes this tensor may set itself up while the tail of this grid runs
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.y * ROWS;
     const int ra = (int)(r0 & 127);                    // first row of this CTA inside its scale atom
@@ -347,6 +348,7 @@ __global__ void __launch_bounds__(QT_THREADS)
 quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
                 uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk, const float* __restrict__ bias = nullptr) {
     __shared__ __align__(16) uint8_t s_sf[2 * 512];
+    griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.y * QT_ROWS;
     const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;

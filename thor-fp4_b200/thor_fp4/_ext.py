@@ -59,6 +59,7 @@ SIGNATURES = {
     "tfp4_plan_stats": (None, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
     "tfp4_set_token_tile": (None, [c_int]),
     "tfp4_set_pair_mode": (None, [c_int]),
+    "tfp4_set_dependent_launch": (None, [c_int]),
     "tfp4_set_splits": (None, [c_int]),
     "tfp4_set_debug": (None, [c_int]),
     "tfp4_set_quant_tile_rows": (None, [c_int]),
