@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--ablate", action="store_true",
                     help="time the GEMM with parts of the kernel switched off through the library's test hooks and print a table")
+    ap.add_argument("--plain-launch", action="store_true",
+                    help="A/B: plain stream order instead of programmatic dependent launches between the kernels")
     ap.add_argument("--profile", action="store_true",
                     help="short run for a profiler: no CPU leg, no end-to-end leg, no sustained-load clock sampling")
     args = ap.parse_args()
@@ -613,6 +615,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the engine has no CPU fallback (use --impl reference for the CPU arm)")
+    if args.plain_launch:
+        from thor_fp4 import _ext
+        _ext.core().tfp4_set_dependent_launch(0)
     if args.ablate:
         run_ablation(args)
         return

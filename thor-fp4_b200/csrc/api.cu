@@ -18,6 +18,7 @@ void gemm_set_token_tile(int);
 void gemm_set_debug(int);
 void gemm_set_pair_mode(int);
 void gemm_set_pdl(int);
+void quant_set_pdl(int);
 void gemm_set_splits(int);
 void quant_set_tile_rows(int);
 int act_quant_mx8(const void*, const float*, int64_t, int64_t, int, int, uint8_t*, uint8_t*, cudaStream_t);
@@ -155,7 +156,10 @@ void tfp4_plan_stats(uint64_t* hits, uint64_t* misses) { tfp4::gemm_plan_stats(h
 void tfp4_set_token_tile(int bn) { tfp4::gemm_set_token_tile(bn); }
 void tfp4_set_debug(int bits) { tfp4::gemm_set_debug(bits); }
 void tfp4_set_pair_mode(int mode) { tfp4::gemm_set_pair_mode(mode); }
-void tfp4_set_dependent_launch(int on) { tfp4::gemm_set_pdl(on); }
+void tfp4_set_dependent_launch(int on) {
+    tfp4::gemm_set_pdl(on);
+    tfp4::quant_set_pdl(on);
+}
 void tfp4_set_splits(int n) { tfp4::gemm_set_splits(n); }
 int tfp4_debug_stats(unsigned long long* out, int n_ctas) { return tfp4::gemm_debug_stats(out, n_ctas); }
 

@@ -167,7 +167,12 @@ __global__ void __launch_bounds__(QT_THREADS)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
     __shared__ __align__(16) uint8_t s_sf[4 * 512];
-    griddep_launch();   // the GEMM that consumes this tensor may set itself up while the tail of this grid runs
+    // Programmatic dependent launch on both sides: this grid may have been made resident while the kernel
+    // before it (the GEMM producing x, or the GEMM still reading the previous contents of packed / sblk) was
+    // finishing, so it waits for that kernel here; and the GEMM that consumes this tensor may set itself up
+    // while the tail of this grid runs.
+    griddep_wait();
+    griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.y * ROWS;
     const int ra = (int)(r0 & 127);                    // first row of this CTA inside its scale atom
@@ -524,22 +529,32 @@ mx8_mul_kernel(const uint8_t* __restrict__ ap, const uint8_t* __restrict__ as,
     }
 }
 
+int g_quant_pdl = 1;   // 1: the NVFP4 quantizer is launched as a programmatic dependent of the kernel before it
+
 template <typename T, int ROWS>
 int launch_quant_nvfp4_rows(const T* xp, int64_t R, int64_t K, float ts, uint8_t* packed, uint8_t* sblk,
                             cudaStream_t stream) {
     // the grid covers the padded rows so that the rows past R of the last 128-row tile get their zeros
     dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)(pad128(R) / ROWS));
     const bool ts_sane = (ts >= 0x1p-100f) && (ts <= 0x1p30f);   // false for NaN too
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(QT_THREADS);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_quant_pdl ? 1 : 0;
     if (!ts_sane) {
-        quant_nvfp4_kernel<T, 2, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 2, ROWS>, xp, R, K, ts, packed, sblk));
     } else if (sizeof(T) == 2 && ts == 1.0f) {
-        quant_nvfp4_kernel<T, 0, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 0, ROWS>, xp, R, K, ts, packed, sblk));
     } else if (sizeof(T) == 2 && ts <= 128.0f) {
-        quant_nvfp4_kernel<T, 3, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 3, ROWS>, xp, R, K, ts, packed, sblk));
     } else {
-        quant_nvfp4_kernel<T, 1, ROWS><<<grid, QT_THREADS, 0, stream>>>(xp, R, K, ts, packed, sblk);
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 1, ROWS>, xp, R, K, ts, packed, sblk));
     }
-    TFP4_CK(cudaGetLastError());
     return TFP4_OK;
 }
 
@@ -651,13 +666,21 @@ int swiglu_quant_nvfp4(const void* gu, int64_t R, int64_t K, int in_dtype, uint8
         return TFP4_ERR_BAD_ARG;
     }
     dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)(pad128(R) / 128));
+    cudaLaunchAttribute attr[1];       // dependent of the gate/up GEMM before it (waits for it before its first load)
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(QT_THREADS);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_quant_pdl ? 1 : 0;
     if (in_dtype == IN_BF16)
-        quant_nvfp4_kernel<__nv_bfloat16, 0, 128, true><<<grid, QT_THREADS, 0, stream>>>(
-            static_cast<const __nv_bfloat16*>(gu), R, K, 1.0f, packed, sblk);
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<__nv_bfloat16, 0, 128, true>,
+                                   static_cast<const __nv_bfloat16*>(gu), R, K, 1.0f, packed, sblk));
     else
-        quant_nvfp4_kernel<__half, 0, 128, true><<<grid, QT_THREADS, 0, stream>>>(static_cast<const __half*>(gu), R, K, 1.0f,
-                                                                                  packed, sblk);
-    TFP4_CK(cudaGetLastError());
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<__half, 0, 128, true>, static_cast<const __half*>(gu), R, K, 1.0f,
+                                   packed, sblk));
     return TFP4_OK;
 }
 
@@ -682,6 +705,8 @@ int quant_nvfp4(const void* x, int64_t R, int64_t K, int in_dtype, float ts, uin
         default: return launch_quant_nvfp4<__nv_bfloat16>(x, R, K, ts, packed, sblk, stream);
     }
 }
+
+void quant_set_pdl(int on) { g_quant_pdl = on ? 1 : 0; }
 
 int fake_quant_nvfp4(const void* x, int64_t n, int in_dtype, float ts, void* y, int out_dtype, cudaStream_t stream) {
     if (n < 0 || (n % 16) != 0) {
