@@ -66,121 +66,137 @@ scales_gemv_kernel(const uint8_t* __restrict__ sblk, int64_t R, int64_t S, uint8
 
 // ---------------------------------------------------------------------------
 // GEMV: out (M<=8, N) = x (M, K) @ dequant(W)^T, activations exact, FP32
-// accumulation (csrc/thor_fp4_core.cu:412-518).  Bandwidth-bound: a warp
-// streams RPW weight rows with one 16-byte load per lane per row (32 codes)
-// plus the two scale bytes from the un-scattered (N, K/16) copy; the M x 1024
-// activation chunk sits in shared memory transposed so that lane l reads word
-// j*32 + l without bank conflicts.  Each 16-code block is accumulated against
-// the activations first and scaled once.
+// accumulation (csrc/thor_fp4_core.cu:412-518).  Weight-streaming kernel:
+//   * a lane owns a fixed run of CPL codes (16 bytes = two blocks for M <= 2, 8 bytes = one block
+//     above) of the K axis and keeps the matching activations of all M rows in registers, so the
+//     inner loop reads nothing but weights: one 16-/8-byte load plus the block scale bytes per row;
+//   * a warp covers 32 * CPL consecutive codes of a row per load (512 / 256 contiguous bytes); the
+//     8 warps of a CTA take the K chunks round-robin (K = 8192, M <= 2: one chunk each, activations
+//     loaded once);
+//   * a CTA owns a contiguous, balanced range of weight rows and walks it four rows at a time with
+//     the next four rows' loads already in flight;
+//   * per row: 16 codes are accumulated against the activations, scaled once by dec(scale) * ts,
+//     reduced over the warp by shuffles, and added by lane 0 to this warp's slot in shared memory;
+//     the 8 slots are summed in a fixed order at the end (deterministic).
 // ---------------------------------------------------------------------------
 constexpr int GV_THREADS = 256;
-constexpr int GV_RPW = 4;        // weight rows per warp
-constexpr int GV_KC = 1024;      // activation chunk = 32 lanes x 32 codes
+constexpr int GV_WARPS = GV_THREADS / 32;
+constexpr int GV_RU = 4;            // rows per step (two steps in flight)
+constexpr int GV_MAX_ROWS = 64;     // rows per CTA (shared-memory slots)
 
-template <typename XT>
-__device__ __forceinline__ float to_f32(XT v);
-template <>
-__device__ __forceinline__ float to_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
-template <>
-__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <int LB> struct GvRaw;
+template <> struct GvRaw<16> { uint4 w; uint32_t sc; };
+template <> struct GvRaw<8> { uint2 w; uint32_t sc; };
 
-template <typename XT, int MT>
-__global__ void __launch_bounds__(GV_THREADS)
+template <int LB>
+__device__ __forceinline__ GvRaw<LB> gv_fetch(const uint8_t* wp, const uint8_t* sp, bool on) {
+    GvRaw<LB> r;
+    if constexpr (LB == 16) {
+        r.w = on ? __ldg(reinterpret_cast<const uint4*>(wp)) : make_uint4(0u, 0u, 0u, 0u);
+        r.sc = on ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(sp)) : 0u;
+    } else {
+        r.w = on ? __ldg(reinterpret_cast<const uint2*>(wp)) : make_uint2(0u, 0u);
+        r.sc = on ? (uint32_t)__ldg(sp) : 0u;
+    }
+    return r;
+}
+
+template <typename XT, int MT, int LB>
+__global__ void __launch_bounds__(GV_THREADS, (MT <= 2) ? 2 : 1)
 gemv_nvfp4_kernel(const XT* __restrict__ x, int M, const uint8_t* __restrict__ pB,
                   const uint8_t* __restrict__ sgemv, float ts, int64_t N, int64_t K,
                   void* __restrict__ out, int out_dtype) {
-    __shared__ float xs[MT * GV_KC];
+    constexpr int CPL = 2 * LB;          // codes per lane per row
+    constexpr int BPL = CPL / 16;        // scale blocks per lane per row
+    constexpr int CHUNK = 32 * CPL;      // codes per warp per row
+    __shared__ float sacc[GV_WARPS][GV_MAX_ROWS][MT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t S = K >> 4;
-    const int64_t n0 = ((int64_t)blockIdx.x * (GV_THREADS / 32) + warp) * GV_RPW;
-    float acc[GV_RPW][MT];
-#pragma unroll
-    for (int rr = 0; rr < GV_RPW; ++rr)
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[rr][m] = 0.f;
+    // balanced contiguous row range of this CTA (at most GV_MAX_ROWS rows: the grid is sized for that)
+    const int64_t n_begin = (N * (int64_t)blockIdx.x) / gridDim.x;
+    const int64_t n_end = (N * ((int64_t)blockIdx.x + 1)) / gridDim.x;
+    const int rows = (int)(n_end - n_begin);
+    for (int i = threadIdx.x; i < GV_WARPS * GV_MAX_ROWS * MT; i += GV_THREADS) (&sacc[0][0][0])[i] = 0.f;
+    __syncthreads();
 
-    for (int64_t c0 = 0; c0 < K; c0 += GV_KC) {
-        const int ce = (int)((K - c0 < GV_KC) ? (K - c0) : GV_KC);
-        __syncthreads();
-        for (int i = threadIdx.x; i < MT * GV_KC; i += GV_THREADS) {
-            const int m = i / GV_KC, kk = i - m * GV_KC;
-            float v = 0.f;
-            if (m < M && kk < ce) v = to_f32<XT>(x[(int64_t)m * K + c0 + kk]);
-            xs[m * GV_KC + (kk & 31) * 32 + (kk >> 5)] = v;
-        }
-        __syncthreads();
-        const int k_lane = lane * 32;
-        if (k_lane < ce) {
-            uint4 w[GV_RPW];
-            uint32_t sc[GV_RPW];
-#pragma unroll
-            for (int rr = 0; rr < GV_RPW; ++rr) {
-                const int64_t n = n0 + rr;
-                if (n < N) {
-                    w[rr] = __ldg(reinterpret_cast<const uint4*>(pB + n * (K >> 1) + ((c0 + k_lane) >> 1)));
-                    sc[rr] = *reinterpret_cast<const unsigned short*>(sgemv + n * S + ((c0 + k_lane) >> 4));
-                } else {
-                    w[rr] = make_uint4(0u, 0u, 0u, 0u);
-                    sc[rr] = 0u;
-                }
-            }
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {       // two 16-code blocks per lane
-                float part[GV_RPW][MT];
-#pragma unroll
-                for (int rr = 0; rr < GV_RPW; ++rr)
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) part[rr][m] = 0.f;
-#pragma unroll
-                for (int b = 0; b < 8; ++b) {            // 8 bytes = 16 codes
-                    const int j = half * 16 + 2 * b;     // element index inside the lane's 32
-                    float xa[MT], xb[MT];
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        xa[m] = xs[m * GV_KC + j * 32 + lane];
-                        xb[m] = xs[m * GV_KC + (j + 1) * 32 + lane];
-                    }
-#pragma unroll
-                    for (int rr = 0; rr < GV_RPW; ++rr) {
-                        const uint32_t word = half == 0 ? (b < 4 ? w[rr].x : w[rr].y) : (b < 4 ? w[rr].z : w[rr].w);
-                        float lo, hi;
-                        e2m1x2_to_f32x2((word >> (8 * (b & 3))) & 0xffu, lo, hi);
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            part[rr][m] = fmaf(lo, xa[m], part[rr][m]);
-                            part[rr][m] = fmaf(hi, xb[m], part[rr][m]);
-                        }
-                    }
-                }
-#pragma unroll
-                for (int rr = 0; rr < GV_RPW; ++rr) {
-                    const float s = e4m3_to_f32((sc[rr] >> (8 * half)) & 0xffu) * ts;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) acc[rr][m] = fmaf(part[rr][m], s, acc[rr][m]);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int rr = 0; rr < GV_RPW; ++rr) {
-        const int64_t n = n0 + rr;
+    const int n_chunks = (int)((K + CHUNK - 1) / CHUNK);
+    for (int c = warp; c < n_chunks; c += GV_WARPS) {
+        const int64_t k0 = (int64_t)c * CHUNK + lane * CPL;
+        const bool on = k0 < K;          // K % 64 == 0: a lane's run is inside or outside as a whole
+        float xr[MT][CPL];
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            float v = acc[rr][m];
 #pragma unroll
-            for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-            if (lane == 0 && n < N && m < M) {
-                const int64_t o = (int64_t)m * N + n;
-                if (out_dtype == OUT_F16) reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
-                else if (out_dtype == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
-                else reinterpret_cast<float*>(out)[o] = v;
+            for (int j = 0; j < CPL; j += 8) {
+                float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (on && m < M) load8<XT>(x + (int64_t)m * K + k0 + j, f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xr[m][j + i] = f[i];
             }
         }
+        const uint8_t* wp = pB + n_begin * (K >> 1) + (k0 >> 1);
+        const uint8_t* sp = sgemv + n_begin * S + (k0 >> 4);
+        GvRaw<LB> cur[GV_RU], nxt[GV_RU];
+#pragma unroll
+        for (int u = 0; u < GV_RU; ++u) cur[u] = gv_fetch<LB>(wp + (int64_t)u * (K >> 1), sp + (int64_t)u * S, on && u < rows);
+        for (int r0 = 0; r0 < rows; r0 += GV_RU) {
+#pragma unroll
+            for (int u = 0; u < GV_RU; ++u) {
+                const int rn = r0 + GV_RU + u;
+                nxt[u] = gv_fetch<LB>(wp + (int64_t)rn * (K >> 1), sp + (int64_t)rn * S, on && rn < rows);
+            }
+#pragma unroll
+            for (int u = 0; u < GV_RU; ++u) {
+                uint32_t words[LB / 4];
+                if constexpr (LB == 16) { words[0] = cur[u].w.x; words[1] = cur[u].w.y; words[2] = cur[u].w.z; words[3] = cur[u].w.w; }
+                else { words[0] = cur[u].w.x; words[1] = cur[u].w.y; }
+                float acc[MT];
+#pragma unroll
+                for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+#pragma unroll
+                for (int blk = 0; blk < BPL; ++blk) {
+                    float part[MT];
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) part[m] = 0.f;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) {        // 8 bytes = 16 codes = one scale block
+                        float lo, hi;
+                        e2m1x2_to_f32x2((words[blk * 2 + (b >> 2)] >> (8 * (b & 3))) & 0xffu, lo, hi);
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            part[m] = fmaf(lo, xr[m][blk * 16 + 2 * b], part[m]);
+                            part[m] = fmaf(hi, xr[m][blk * 16 + 2 * b + 1], part[m]);
+                        }
+                    }
+                    const float sc = e4m3_to_f32((cur[u].sc >> (8 * blk)) & 0xffu) * ts;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) acc[m] = fmaf(part[m], sc, acc[m]);
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float v = acc[m];
+#pragma unroll
+                    for (int off = 16; off; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                    if (lane == 0 && r0 + u < rows) sacc[warp][r0 + u][m] += v;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < GV_RU; ++u) cur[u] = nxt[u];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows * MT; i += GV_THREADS) {
+        const int r = i / MT, m = i - r * MT;
+        if (m >= M) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GV_WARPS; ++w) v += sacc[w][r][m];
+        const int64_t o = (int64_t)m * N + n_begin + r;
+        if (out_dtype == OUT_F16) reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
+        else if (out_dtype == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(out)[o] = v;
     }
 }
-
 unsigned blocks_for(int64_t total, int threads) {
     int64_t b = (total + threads - 1) / threads;
     const int64_t cap = 148 * 16;
@@ -190,14 +206,22 @@ unsigned blocks_for(int64_t total, int threads) {
 template <typename XT>
 int launch_gemv(const void* x, int64_t M, int64_t K, const uint8_t* pB, const uint8_t* sg, float ts,
                 void* out, int64_t N, int out_dtype, cudaStream_t stream) {
-    const int rows_per_cta = (GV_THREADS / 32) * GV_RPW;
-    const unsigned grid = (unsigned)((N + rows_per_cta - 1) / rows_per_cta);
+    // two CTAs per SM for M <= 2 (one above: the activations of 4 / 8 rows fill the registers); more CTAs
+    // when the rows per CTA would exceed the shared-memory slots
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t ctas = (int64_t)sms * (M <= 2 ? 2 : 1);
+    const int64_t need = (N + GV_MAX_ROWS - 1) / GV_MAX_ROWS;
+    if (ctas < need) ctas = need;
+    if (ctas > N) ctas = N;
+    const unsigned grid = (unsigned)ctas;
     const XT* xp = static_cast<const XT*>(x);
     const int m = (int)M;
-    if (M <= 1) gemv_nvfp4_kernel<XT, 1><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
-    else if (M <= 2) gemv_nvfp4_kernel<XT, 2><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
-    else if (M <= 4) gemv_nvfp4_kernel<XT, 4><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
-    else gemv_nvfp4_kernel<XT, 8><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
+    if (M <= 1) gemv_nvfp4_kernel<XT, 1, 16><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
+    else if (M <= 2) gemv_nvfp4_kernel<XT, 2, 16><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
+    else if (M <= 4) gemv_nvfp4_kernel<XT, 4, 8><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
+    else gemv_nvfp4_kernel<XT, 8, 8><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
     TFP4_CK(cudaGetLastError());
     return TFP4_OK;
 }
@@ -250,6 +274,10 @@ int gemv(const void* x, int64_t M, int64_t K, int in_dtype, const uint8_t* packe
     if (N <= 0 || !x || !packedB || !sgemvB || !out || in_dtype < 0 || in_dtype > 2 || out_dtype < 0 ||
         out_dtype > 2 || (reinterpret_cast<uintptr_t>(packedB) & 15) || (reinterpret_cast<uintptr_t>(sgemvB) & 1)) {
         fprintf(stderr, "thor_fp4 gemv: bad argument (weights must be 16-byte aligned)\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    if (reinterpret_cast<uintptr_t>(x) & (in_dtype == IN_F32 ? 31 : 15)) {
+        fprintf(stderr, "thor_fp4 gemv: activations must be 16-byte (f32: 32-byte) aligned\n");
         return TFP4_ERR_BAD_ARG;
     }
     switch (in_dtype) {
