@@ -34,7 +34,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "mlp", "sweep"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "mlp", "sweep", "gemv"])
     ap.add_argument("--M", type=int, default=8192)
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--K", type=int, default=8192)
@@ -345,6 +345,40 @@ def run_sweep(args):
     print(f"| {K} -> {N} | {M} | nvfp4 x nvfp4 (GEMM only) | {us:.1f} | {2.0 * M * N * K / us / 1e6:.1f} | rel. error vs fp32 matmul {err:.4f} |")
 
 
+def run_gemv(args):
+    """Exact-activation GEMV engine alone (ops.gemv on a resident NVFP4 weight), M = 1, 2, 4, 8; three weights
+    in rotation so that every call streams its weight from HBM (3 x 37.7 MB at 8192 x 8192 stays under the L2
+    size only for the smallest layer, stated per row)."""
+    import thor_fp4
+    from thor_fp4 import ops
+    print("| layer (K -> N) | M | input | us per call | weight-stream GB/s | fraction of measured copy |")
+    print("|---|---|---|---|---|---|")
+    pk = peaks()
+    for (K, N) in ((args.K, args.N),) if (args.K, args.N) != (8192, 8192) else ((8192, 8192), (8192, 28672), (28672, 8192)):
+        Ws = [thor_fp4.NVFP4Tensor.from_float(torch.randn(N, K, device="cuda") * 0.02) for _ in range(4)]
+        for w in Ws:
+            w.gemv_scales()
+        for M in (1, 2, 4, 8):
+            for dt, nm in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+                x = torch.randn(M, K, device="cuda").to(dt)
+                out = torch.empty(M, N, device="cuda")
+                for w in Ws:
+                    ops.gemv(x, w, "f32", out=out)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(args.steps):
+                    for w in Ws:
+                        ops.gemv(x, w, "f32", out=out)
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / (args.steps * len(Ws))
+                gbs = N * K * 0.5625 / us / 1e3
+                print(f"| {K} -> {N} | {M} | {nm} | {us:.1f} | {gbs:.0f} | {gbs / pk['hbm_gbs']:.2f} |", flush=True)
+        del Ws
+        torch.cuda.empty_cache()
+
+
 def run_mlp(args):
     """--workload mlp: the NVFP4 SwiGLU block (hidden --K, intermediate --inter, --M tokens), tensor-parallel over the
     ranks: gate/up split by rows, down by columns, one all-reduce of the f32 partial outputs per step (strong scaling:
@@ -623,6 +657,9 @@ def main():
         return
     if args.workload == "sweep":
         run_sweep(args)
+        return
+    if args.workload == "gemv":
+        run_gemv(args)
         return
     if args.workload == "mlp":
         if args.M == 8192 and args.K == 8192 and args.N == 8192:
