@@ -93,6 +93,23 @@ __device__ __forceinline__ void e2m1x2_to_f32x2(uint32_t byte, float& lo, float&
     hi = f.y;
 }
 
+// one word of eight e2m1 codes -> eight floats (element i from nibble i); the word is split into its bytes
+// inside one statement so that the byte selection can fold into the conversions
+__device__ __forceinline__ void e2m1x8_to_f32x8(uint32_t word, float (&o)[8]) {
+    uint32_t h0, h1, h2, h3;
+    asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\tmov.b32 {t0, t1, t2, t3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, t0;\n\tcvt.rn.f16x2.e2m1x2 %1, t1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, t2;\n\tcvt.rn.f16x2.e2m1x2 %3, t3;\n\t}"
+        : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(word));
+    const uint32_t h[4] = {h0, h1, h2, h3};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+        o[2 * i] = f.x;
+        o[2 * i + 1] = f.y;
+    }
+}
+
 // e2m1 code with the reference's rule: sign = (v < 0), magnitude clamped to 6,
 // midpoints of {0,.5,1,1.5,2,3,4,6} round UP (csrc/thor_fp4_core.cu:77-92)
 __device__ __forceinline__ uint32_t e2m1_ties_up(float v) {

@@ -159,13 +159,13 @@ gemv_nvfp4_kernel(const XT* __restrict__ x, int M, const uint8_t* __restrict__ p
 #pragma unroll
                     for (int m = 0; m < MT; ++m) part[m] = 0.f;
 #pragma unroll
-                    for (int b = 0; b < 8; ++b) {        // 8 bytes = 16 codes = one scale block
-                        float lo, hi;
-                        e2m1x2_to_f32x2((words[blk * 2 + (b >> 2)] >> (8 * (b & 3))) & 0xffu, lo, hi);
+                    for (int h = 0; h < 2; ++h) {        // two words = 16 codes = one scale block
+                        float wv[8];
+                        e2m1x8_to_f32x8(words[blk * 2 + h], wv);
 #pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            part[m] = fmaf(lo, xr[m][blk * 16 + 2 * b], part[m]);
-                            part[m] = fmaf(hi, xr[m][blk * 16 + 2 * b + 1], part[m]);
+                        for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                            for (int m = 0; m < MT; ++m) part[m] = fmaf(wv[i], xr[m][blk * 16 + 8 * h + i], part[m]);
                         }
                     }
                     const float sc = e4m3_to_f32((cur[u].sc >> (8 * blk)) & 0xffu) * ts;
