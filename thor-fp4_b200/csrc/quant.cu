@@ -43,12 +43,17 @@ constexpr int QT_COLS = 256;   // columns per CTA tile = 8 elements x 32 lanes
 constexpr int QT_THREADS = 256;
 constexpr int QT_UNROLL = 4;   // rows in flight per warp
 
+// eight floats -> eight e2m1 codes (hardware round-to-nearest-even, saturating), element i in nibble i; the four
+// byte results are joined inside one statement so that the packing can fold into the conversions
 __device__ __forceinline__ uint32_t pack_codes_rne(const float (&y)[8]) {
-    uint32_t b0 = f32x2_to_e2m1x2_rne(y[0], y[1]);
-    uint32_t b1 = f32x2_to_e2m1x2_rne(y[2], y[3]);
-    uint32_t b2 = f32x2_to_e2m1x2_rne(y[4], y[5]);
-    uint32_t b3 = f32x2_to_e2m1x2_rne(y[6], y[7]);
-    return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    uint32_t w;
+    asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\tcvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\tcvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+        "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+        : "=r"(w)
+        : "f"(y[0]), "f"(y[1]), "f"(y[2]), "f"(y[3]), "f"(y[4]), "f"(y[5]), "f"(y[6]), "f"(y[7]));
+    return w;
 }
 
 // Arguments by value: a reference to the caller's array would pin that array in local memory
