@@ -180,7 +180,7 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t r0 = (int64_t)blockIdx.y * ROWS;
-    const int ra = (int)(r0 & 127);                    // first row of this CTA inside its scale atom
+    const int ra = (ROWS == 128) ? 0 : (int)(r0 & 127);   // first row of this CTA inside its scale atom
     constexpr int UNROLL = (MODE == 0 && !GATED) ? 4 : 2;   // rows in flight per warp
     const int64_t ld = GATED ? 2 * K : K;              // input row stride in elements
     const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
@@ -193,6 +193,11 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     const float rts_hi = rts * 1.00000095367431640625f, rts_lo = rts * 0.99999904632568359375f;
 
     reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
+    // MODE 0: the multiplier of a block depends only on its scale byte (127 values): RN(1 / dec(sc)) * (1 + 2^-21),
+    // computed once per CTA with the arithmetic the per-row code used, then one shared-memory read per row
+    __shared__ float s_rb[128];
+    if (MODE == 0 && threadIdx.x < 128)
+        s_rb[threadIdx.x] = __frcp_rn(e4m3_to_f32(threadIdx.x)) * 1.000000476837158203125f;
     __syncthreads();
 
     // warp w handles tile rows w, w+8, ..., w+120, UNROLL rows per step; the raw loads of
@@ -239,7 +244,15 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                     const int sl = lane >> 1;   // scale column inside the tile, 0..15
                     s_sf[(sl >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (sl & 3)] = (uint8_t)sc;
                 }
-                codes = block_codes8<MODE>(f[u], ds);
+                if constexpr (MODE == 0) {
+                    const float rb = s_rb[sc];
+                    float y[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
+                    codes = pack_codes_rne(y);
+                } else {
+                    codes = block_codes8<MODE>(f[u], ds);
+                }
             }
             if (col_ok && r < Rpad)
                 *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
