@@ -226,8 +226,13 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                 widen8(cur[NSRC - 1][u], up);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
+                    // silu(g) = g / (1 + e^-g) with the hardware exponential and reciprocal (a few FP32 ulps, far
+                    // below the rounding of h to T that follows; e^-g = inf gives -0 like the exact division)
                     const float gte = f[u][i];
-                    const float hv = (gte / (1.0f + expf(-gte))) * up[i];
+                    float ex, rc;
+                    asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(gte * -1.4426950408889634f));
+                    asm("rcp.approx.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + ex));
+                    const float hv = (gte * rc) * up[i];
                     f[u][i] = static_cast<float>(static_cast<T>(hv));     // h is held in T
                 }
             }
