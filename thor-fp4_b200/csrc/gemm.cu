@@ -1109,7 +1109,10 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // there are enough tiles to occupy most CTA pairs (smaller batches do better on single-CTA tiles with split K)
     const int64_t duo_tiles = ((M + 255) / 256) * ((N + 255) / 256);
     const bool duo_ok = M > 128 && N >= 64 && g_force_bn == 0 && g_force_splits <= 1 && st->sm_count >= 2;
-    const bool duo = duo_ok && (g_pair_mode == 2 || (g_pair_mode == -1 && duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5));
+    // measured: from 192 tokens on the two-CTA kernel is level with or ahead of the single-CTA one even when its
+    // 256x256 tiles fill only part of the GPU (8192 x 8192 at 256 tokens: 18.6 against 20.7 us)
+    const bool duo = duo_ok && (g_pair_mode == 2 ||
+                                (g_pair_mode == -1 && (M >= 192 || duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5)));
     const uint32_t box_a = duo ? 128u : (pair ? (uint32_t)(bn / 2) : (uint32_t)bn);
     PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : (pair ? -bn : bn), dev};
     auto it = g_plans.find(key);

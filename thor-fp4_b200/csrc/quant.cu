@@ -38,6 +38,8 @@ namespace tfp4 {
 
 namespace {
 
+template <bool B> struct BoolTag { static constexpr bool value = B; };
+
 constexpr int QT_ROWS = 128;   // rows per CTA tile = one scale-atom height
 constexpr int QT_COLS = 256;   // columns per CTA tile = 8 elements x 32 lanes
 constexpr int QT_THREADS = 256;
@@ -168,7 +170,7 @@ __device__ __forceinline__ uint32_t block_codes8(const float (&f)[8], float ds) 
 // unfused block holds it, and quantized with the same code path (one pass instead of an elementwise
 // kernel with FP32 temporaries followed by the quantizer).
 template <typename T, int MODE, int ROWS, bool GATED = false>
-__global__ void __launch_bounds__(QT_THREADS)
+__global__ void __launch_bounds__(QT_THREADS, sizeof(T) == 2 ? 4 : 3)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                    uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
     __shared__ __align__(16) uint8_t s_sf[4 * 512];
@@ -203,71 +205,77 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     // warp w handles tile rows w, w+8, ..., w+120, UNROLL rows per step; the raw loads of
     // the next step are issued before the current step is processed (loads always in flight)
     constexpr int NSRC = GATED ? 2 : 1;
-    auto fetch_rows = [&](int it, Raw8<T> (&dst)[NSRC][UNROLL]) {
+    // the tile loop, instantiated twice: tiles wholly inside the tensor (no row or column checks) and edge tiles
+    auto run_tile = [&](auto full_tag) {
+        constexpr bool FULL = decltype(full_tag)::value;
+        auto fetch_rows = [&](int it, Raw8<T> (&dst)[NSRC][UNROLL]) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int64_t r = r0 + warp + 8 * (it + u);
+            for (int u = 0; u < UNROLL; ++u) {
+                const int64_t r = r0 + warp + 8 * (it + u);
 #pragma unroll
-            for (int g = 0; g < NSRC; ++g)
-                dst[g][u] = (col_ok && r < R) ? fetch8<T>(x + r * ld + g * K + col) : zero8<T>();
+                for (int g = 0; g < NSRC; ++g)
+                    dst[g][u] = (FULL || (col_ok && r < R)) ? fetch8<T>(x + r * ld + g * K + col) : zero8<T>();
+            }
+        };
+        Raw8<T> cur[NSRC][UNROLL], nxt[NSRC][UNROLL];
+        fetch_rows(0, cur);
+#pragma unroll 1
+        for (int it = 0; it < ROWS / 8; it += UNROLL) {
+            if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, nxt);
+            float f[UNROLL][8];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                widen8(cur[0][u], f[u]);
+                if constexpr (GATED) {
+                    float up[8];
+                    widen8(cur[NSRC - 1][u], up);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        // silu(g) = g / (1 + e^-g) with the hardware exponential and reciprocal (a few FP32 ulps, far
+                        // below the rounding of h to T that follows; e^-g = inf gives -0 like the exact division)
+                        const float gte = f[u][i];
+                        float ex, rc;
+                        asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(gte * -1.4426950408889634f));
+                        asm("rcp.approx.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + ex));
+                        const float hv = (gte * rc) * up[i];
+                        f[u][i] = static_cast<float>(static_cast<T>(hv));     // h is held in T
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int rl = warp + 8 * (it + u);
+                const int64_t r = r0 + rl;
+                uint32_t codes = 0;
+                if (FULL || r < R) {   // warp-uniform: every lane takes part in the shuffles
+                    uint32_t sc;
+                    const float ds = block_scale8<MODE>(f[u], ts, rts_lo, rts_hi, sc);
+                    if ((lane & 1) == 0 && (FULL || col_ok)) {
+                        const int sl = lane >> 1;   // scale column inside the tile, 0..15
+                        s_sf[(sl >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (sl & 3)] = (uint8_t)sc;
+                    }
+                    if constexpr (MODE == 0) {
+                        const float rb = s_rb[sc];
+                        float y[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
+                        codes = pack_codes_rne(y);
+                    } else {
+                        codes = block_codes8<MODE>(f[u], ds);
+                    }
+                }
+                if (FULL || (col_ok && r < Rpad))
+                    *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                for (int g = 0; g < NSRC; ++g) cur[g][u] = nxt[g][u];
+            }
         }
     };
-    Raw8<T> cur[NSRC][UNROLL], nxt[NSRC][UNROLL];
-    fetch_rows(0, cur);
-#pragma unroll 1
-    for (int it = 0; it < ROWS / 8; it += UNROLL) {
-        if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, nxt);
-        float f[UNROLL][8];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            widen8(cur[0][u], f[u]);
-            if constexpr (GATED) {
-                float up[8];
-                widen8(cur[NSRC - 1][u], up);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    // silu(g) = g / (1 + e^-g) with the hardware exponential and reciprocal (a few FP32 ulps, far
-                    // below the rounding of h to T that follows; e^-g = inf gives -0 like the exact division)
-                    const float gte = f[u][i];
-                    float ex, rc;
-                    asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(gte * -1.4426950408889634f));
-                    asm("rcp.approx.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + ex));
-                    const float hv = (gte * rc) * up[i];
-                    f[u][i] = static_cast<float>(static_cast<T>(hv));     // h is held in T
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int rl = warp + 8 * (it + u);
-            const int64_t r = r0 + rl;
-            uint32_t codes = 0;
-            if (r < R) {   // warp-uniform: every lane takes part in the shuffles
-                uint32_t sc;
-                const float ds = block_scale8<MODE>(f[u], ts, rts_lo, rts_hi, sc);
-                if ((lane & 1) == 0 && col_ok) {
-                    const int sl = lane >> 1;   // scale column inside the tile, 0..15
-                    s_sf[(sl >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (sl & 3)] = (uint8_t)sc;
-                }
-                if constexpr (MODE == 0) {
-                    const float rb = s_rb[sc];
-                    float y[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
-                    codes = pack_codes_rne(y);
-                } else {
-                    codes = block_codes8<MODE>(f[u], ds);
-                }
-            }
-            if (col_ok && r < Rpad)
-                *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-            for (int g = 0; g < NSRC; ++g) cur[g][u] = nxt[g][u];
-        }
-    }
+    if (r0 + ROWS <= R && c0 + QT_COLS <= K) run_tile(BoolTag<true>{});
+    else run_tile(BoolTag<false>{});
     __syncthreads();
     // scale bytes out: whole 512-byte atoms (ROWS == 128) or this CTA's half of each atom
     const int64_t D = K >> 6;                          // atoms per 128-row tile
@@ -408,7 +416,12 @@ quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
                     for (int i = 0; i < 8; ++i) {
                         const float v = f[u][i] + b[i];
                         if (ACT == 1) f[u][i] = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
-                        else if (ACT == 2) f[u][i] = v / (1.0f + expf(-v));
+                        else if (ACT == 2) {   // silu with the hardware exponential and reciprocal (a few FP32 ulps)
+                            float ex, rc;
+                            asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(v * -1.4426950408889634f));
+                            asm("rcp.approx.f32 %0, %1;" : "=f"(rc) : "f"(1.0f + ex));
+                            f[u][i] = v * rc;
+                        }
                         else f[u][i] = v;
                     }
                 }
