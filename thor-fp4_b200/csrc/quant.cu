@@ -217,11 +217,10 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                     dst[g][u] = (FULL || (col_ok && r < R)) ? fetch8<T>(x + r * ld + g * K + col) : zero8<T>();
             }
         };
-        Raw8<T> cur[NSRC][UNROLL], nxt[NSRC][UNROLL];
-        fetch_rows(0, cur);
-#pragma unroll 1
-        for (int it = 0; it < ROWS / 8; it += UNROLL) {
-            if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, nxt);
+        // two row buffers used alternately (the loads of one step are in flight while the other is processed),
+        // without register copies between them
+        auto process = [&](int it, Raw8<T> (&cur)[NSRC][UNROLL]) {
+
             float f[UNROLL][8];
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
@@ -267,10 +266,29 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                 if (FULL || (col_ok && r < Rpad))
                     *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
             }
+        };
+        Raw8<T> buf_a[NSRC][UNROLL], buf_b[NSRC][UNROLL];
+        fetch_rows(0, buf_a);
+        if constexpr (GATED || MODE == 0) {
+            // (four rows per step, or twice the loads plus the activation arithmetic: these variants spill with
+            // the loop body instantiated twice and gain nothing from it; they copy the prefetched rows instead)
+#pragma unroll 1
+            for (int it = 0; it < ROWS / 8; it += UNROLL) {
+                if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, buf_b);
+                process(it, buf_a);
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
+                for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
-                for (int g = 0; g < NSRC; ++g) cur[g][u] = nxt[g][u];
+                    for (int g = 0; g < NSRC; ++g) buf_a[g][u] = buf_b[g][u];
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (int it = 0; it < ROWS / 8; it += 2 * UNROLL) {
+                fetch_rows(it + UNROLL, buf_b);
+                process(it, buf_a);
+                if (it + 2 * UNROLL < ROWS / 8) fetch_rows(it + 2 * UNROLL, buf_a);
+                process(it + UNROLL, buf_b);
             }
         }
     };
