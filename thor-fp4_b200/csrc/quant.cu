@@ -257,7 +257,7 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
                         const float rb = s_rb[sc];
                         float y[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) y[i] = fma_pz(f[u][i], rb);
+                        for (int i = 0; i < 8; i += 2) mul2_pz(y[i], y[i + 1], f[u][i], f[u][i + 1], rb);
                         codes = pack_codes_rne(y);
                     } else {
                         codes = block_codes8<MODE>(f[u], ds);
