@@ -171,7 +171,8 @@ void tfp4_set_pair_mode(int mode);
  * (normally the activation quantizer) and they wait for its completion before touching global memory; 0: plain
  * stream order (A/B timing). */
 void tfp4_set_dependent_launch(int on);
-/* K split of small-batch GEMMs: 0 automatic, 1 never, n = about n K ranges (test hook). */
+/* K split of small-batch GEMMs: 0 automatic (tiles that fill whole waves of CTAs stay whole, the rest are cut),
+ * -1 automatic with every tile cut alike, 1 never, n = about n K ranges for every tile (test hook). */
 void tfp4_set_splits(int n);
 void tfp4_set_debug(int bits);
 /* test hook: force the NVFP4 quantizer's tile height (64 or 128 rows; 0 = automatic) */

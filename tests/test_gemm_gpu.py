@@ -307,3 +307,44 @@ def test_gemm_split_k_matches_oracle(shape, splits, od):
     assert torch.equal(out, again)          # fixed summation order
     ref = _oracle_out(a, b, bias.cpu().numpy())
     assert _fro(out.float().cpu().numpy(), ref) < (TOL if od == "f32" else 3e-3)
+
+
+@gpu
+@pytest.mark.parametrize("M", [1, 16, 100])
+@pytest.mark.parametrize("od", ["f32", "bf16"])
+def test_gemm_uneven_split_whole_and_cut_tiles(M, od):
+    """More output tiles than SMs (160 weight tiles): the tiles that fill a whole wave stay whole, the remaining
+    ones are cut along K.  The result must equal the never-split and the all-tiles-cut runs up to the f32
+    summation order, be repeatable, and carry the bias exactly once on both kinds of tile."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    N, K = 20480, 5120
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.02
+    a = thor_fp4.NVFP4Tensor.from_float(x, 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    del w
+    bias = torch.randn(N, device="cuda", generator=g)
+    outs = {}
+    try:
+        for mode in (0, 0, 1, -1):
+            _ext.core().tfp4_set_splits(mode)
+            out = torch.full((M, N), float("nan"), dtype=_ext.OUT_TORCH[od], device="cuda")
+            ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, od, bias=bias)
+            torch.cuda.synchronize()
+            outs.setdefault(mode, []).append(out)
+    finally:
+        _ext.core().tfp4_set_splits(0)
+    assert _ext.status() == 0
+    assert torch.equal(outs[0][0], outs[0][1])
+    tol = 2e-6 if od == "f32" else 3e-3
+    for mode in (1, -1):
+        d = (outs[0][0].float() - outs[mode][0].float()).norm() / outs[mode][0].float().norm()
+        assert d.item() < tol, (mode, d.item())
+    assert torch.isfinite(outs[0][0].float()).all()
+    # first (whole) and last (cut) weight tiles against the dequantized reference
+    ref = a.dequantize() @ b.dequantize().t() + bias
+    for cols in (slice(0, 256), slice(N - 256, N)):
+        d = (outs[0][0][:, cols].float() - ref[:, cols]).norm() / ref[:, cols].norm()
+        assert d.item() < (1e-4 if od == "f32" else 5e-3)

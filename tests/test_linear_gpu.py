@@ -257,3 +257,30 @@ def test_quantized_checkpoint_restores_the_layer_bit_for_bit(tmp_path):
     assert os.path.getsize(f) < 0.4 * (256 * 192 * 4)
     with pytest.raises(ValueError):
         thor_fp4.Linear(256, 128, device="cuda").load_quantized_state(torch.load(f, map_location="cpu", weights_only=True))
+
+
+@gpu
+@pytest.mark.parametrize("M", [1, 100, 700])
+def test_dependent_launch_chain_equals_plain_stream_order(M):
+    # quantizer -> GEMM -> split-K reduction chained by programmatic dependent launch (default) must give the
+    # bytes of plain stream order, eagerly, back to back on changing inputs, and replayed from a CUDA graph
+    import thor_fp4
+    from thor_fp4 import _ext
+    torch.manual_seed(M)
+    lin = thor_fp4.Linear(1024, 768, bias=True, out_dtype="bf16", device="cuda")
+    xs = [torch.randn(M, 1024, device="cuda").bfloat16() for _ in range(4)]
+    L = _ext.core()
+    try:
+        L.tfp4_set_dependent_launch(0)
+        want = [lin(x).clone() for x in xs]
+        L.tfp4_set_dependent_launch(1)
+        got = [lin(x).clone() for x in xs]            # each call overwrites the buffers the previous one read
+        torch.cuda.synchronize()
+        for a, b in zip(want, got):
+            assert torch.equal(a, b)
+        g = thor_fp4.capture_module(lin, xs[0])
+        for i in (1, 2, 3, 0):
+            y = g(xs[i])
+            assert torch.equal(y, want[i])
+    finally:
+        L.tfp4_set_dependent_launch(1)

@@ -70,11 +70,37 @@ struct GemmParams {
     int32_t stages;
     int32_t splits;          // K is cut into this many ranges; > 1: partial sums go to `ws` (f32, [split][M][N])
     int32_t kb_per_split;
+    int32_t whole_tiles;     // the first `whole_tiles` output tiles are one work item each (all of K, final output);
+                             // the tiles after them are cut into `splits` K ranges (0: every tile is cut)
     float* ws;
     int32_t debug;           // test hook: bit0 no stores, bit1 no scale copies, bit2 no MMA, bit3 no loads, bit4 no tmem loads
     int* status;             // host-visible status word (0 = ok)
     unsigned long long* stats;   // host-visible per-CTA cycle counters (debug bit 1024), 4 per CTA
 };
+
+// Work item -> (output tile, K range).  Items [0, whole_tiles) are whole tiles; item whole_tiles + j is K range
+// j % splits of tile whole_tiles + j / splits.  Cutting only the tiles that do not fill a last wave of CTAs evens
+// out tile counts such as 224 on 148 SMs without paying partial sums for every tile.
+struct WorkItem {
+    int64_t tl;      // output tile (weight-tile major)
+    int32_t sp;      // K range index
+    int32_t kb0, kb1;
+    bool partial;    // f32 partial sums to the workspace instead of the final output
+};
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int64_t item) {
+    WorkItem w;
+    if (item < p.whole_tiles) {
+        w.tl = item; w.sp = 0; w.kb0 = 0; w.kb1 = p.k_blocks; w.partial = false;
+    } else {
+        const int64_t j = item - p.whole_tiles;
+        w.tl = p.whole_tiles + j / p.splits;
+        w.sp = (int32_t)(j % p.splits);
+        w.kb0 = w.sp * p.kb_per_split;
+        w.kb1 = (w.kb0 + p.kb_per_split < p.k_blocks) ? w.kb0 + p.kb_per_split : p.k_blocks;
+        w.partial = p.splits > 1;
+    }
+    return w;
+}
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -484,7 +510,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int dbg = DBG ? p.debug : 0;
 
     // work item = (weight tile, token tile, K range); the K range is the fastest index
-    const int64_t total_tiles = p.m_tiles * p.n_tiles * p.splits;
+    const int64_t total_tiles = p.whole_tiles + (p.m_tiles * p.n_tiles - p.whole_tiles) * p.splits;   // work items
     const int k_blocks = p.k_blocks;
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
 
@@ -497,10 +523,10 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int64_t sp = tile % p.splits, tl = tile / p.splits;
+                const WorkItem wi = decode_item(p, tile);
+                const int64_t tl = wi.tl;
                 const int64_t nt = tl / p.m_tiles, mt = tl - nt * p.m_tiles;
-                const int kb0 = (int)sp * p.kb_per_split;
-                const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+                const int kb0 = wi.kb0, kb1 = wi.kb1;
                 const int64_t a_tile0 = (mt * BN) >> 7;     // first 128-row scale tile of this token tile
                 int a_tiles = 0;
 #pragma unroll
@@ -565,8 +591,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_flag, 2)) { ok = false; break; }
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 const uint32_t tfull_a = smem_u32(&tfull_bar[acc]);
-                const int kb0 = (int)(tile % p.splits) * p.kb_per_split;
-                const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+                const WorkItem wi = decode_item(p, tile);
+                const int kb0 = wi.kb0, kb1 = wi.kb1;
                 const int nkb = kb1 - kb0;
                 for (int base = -s_start; base < nkb && ok; base += STAGES) {
 #pragma unroll
@@ -609,9 +635,9 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t d_tmem = tmem_base + acc * BN;
             // token tiles of 192 start at row 0 or 64 of a 128-row scale atom: rows 32c..32c+31 of
             // an atom sit in scale column c, so the token-side scale address moves by 0 or 2 columns
-            const uint32_t sf_off = (BN == 192) ? (uint32_t)(((((tile / p.splits) % p.m_tiles) * BN) & 127) >> 5) : 0u;
-            const int kb0 = (int)(tile % p.splits) * p.kb_per_split;
-            const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+            const WorkItem wi = decode_item(p, tile);
+            const uint32_t sf_off = (BN == 192) ? (uint32_t)((((wi.tl % p.m_tiles) * BN) & 127) >> 5) : 0u;
+            const int kb0 = wi.kb0, kb1 = wi.kb1;
             for (int kb = kb0; kb < kb1; ++kb) {
                 long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
                 if (prof) c0 = clock64();
@@ -689,13 +715,14 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         uint32_t tcount = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-            const int64_t sp = tile % p.splits, tl = tile / p.splits;
+            const WorkItem wi = decode_item(p, tile);
+            const int64_t sp = wi.sp, tl = wi.tl;
             const int64_t nt = tl / p.m_tiles, mt = tl - nt * p.m_tiles;
             const uint32_t acc = tcount % C::ACC_STAGES;
             const uint32_t acc_ph = (tcount / C::ACC_STAGES) & 1u;
             if (!mbar_wait_parked(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
-            if (p.splits > 1)   // partial sum of this K range, f32, bias and cast happen in the reduction
+            if (wi.partial)   // partial sum of this K range, f32, bias and cast happen in the reduction
                 drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.ws + sp * p.M * p.N, OUT_F32, nullptr);
             else
                 drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.out, p.out_dtype, p.bias);
@@ -718,8 +745,8 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         bool ok = true;
         const uint32_t sfw_base = smem_u32(sSFW), sfa_base = smem_u32(sSFA);
         for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int kb0 = (int)(tile % p.splits) * p.kb_per_split;
-            const int kb1 = (kb0 + p.kb_per_split < k_blocks) ? kb0 + p.kb_per_split : k_blocks;
+            const WorkItem wi = decode_item(p, tile);
+            const int kb0 = wi.kb0, kb1 = wi.kb1;
             for (int kb = kb0; kb < kb1; ++kb) {
                 if (!mbar_wait(full0 + 8 * s, ph, abort_flag, 6)) { ok = false; break; }
                 if (it >= C::NSLOT) {
@@ -770,10 +797,13 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 // Sum of the split-K partial tiles: out[m, n] = cast( sum_s ws[s][m][n] + bias[n] ), four elements
 // per thread, splits added in a fixed order (deterministic).
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t MN, int64_t N,
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t M, int64_t N, int64_t n0,
                      const float* __restrict__ bias, void* __restrict__ out, int out_dtype) {
-    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i >= MN) return;
+    // columns [n0, N) of every row are the cut tiles (the columns before them were written by whole-tile items)
+    const int64_t width = N - n0, MN = M * N;
+    const int64_t e = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (e >= M * width) return;
+    const int64_t i = (e / width) * N + n0 + (e % width);
     griddep_wait();     // launched while the GEMM still runs; its partial sums are complete after this
     float4 acc = *reinterpret_cast<const float4*>(ws + i);
     for (int s = 1; s < splits; ++s) {
@@ -909,7 +939,7 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
         st->attr_set[KIND][bn_slot] = true;
     }
     const int64_t tiles = p.m_tiles * p.n_tiles;
-    const int64_t tiles_all = tiles * p.splits;
+    const int64_t tiles_all = p.whole_tiles + (tiles - p.whole_tiles) * p.splits;
     const unsigned grid_all = (unsigned)(tiles_all < st->sm_count ? tiles_all : st->sm_count);
     // Launched with programmatic stream serialization: the kernel may become resident and run its prologue
     // (barriers, tensor-memory allocation) while the kernel before it in the stream - normally the activation
@@ -929,11 +959,12 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     cudaError_t e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_bs_kernel<KIND, BN, true>, plan.tmW, plan.tmA, p)
                             : cudaLaunchKernelEx(&cfg, gemm_bs_kernel<KIND, BN, false>, plan.tmW, plan.tmA, p);
     if (e == cudaSuccess && p.splits > 1) {
-        const int64_t MN = p.M * p.N;
-        cfg.gridDim = dim3((unsigned)((MN / 4 + 255) / 256));
+        const int64_t n0 = (p.whole_tiles / p.m_tiles) * BM;     // whole_tiles is a multiple of m_tiles
+        const int64_t elems = p.M * (p.N - n0);
+        cfg.gridDim = dim3((unsigned)((elems / 4 + 255) / 256));
         cfg.blockDim = dim3(256);
         cfg.dynamicSmemBytes = 0;
-        e = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const float*)p.ws, (int)p.splits, MN, (int64_t)p.N,
+        e = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const float*)p.ws, (int)p.splits, (int64_t)p.M, (int64_t)p.N, n0,
                                (const float*)p.bias, (void*)p.out, (int)p.out_dtype);
     }
     if (e != cudaSuccess) {
@@ -1160,13 +1191,14 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // becomes a work item writing an f32 partial tile, summed by a second kernel
     p.splits = 1;
     p.kb_per_split = p.k_blocks;
+    p.whole_tiles = 0;
     p.ws = nullptr;
     {
         const int64_t tiles = p.m_tiles * p.n_tiles;
-        int want = g_force_splits;
+        int want = g_force_splits > 0 ? g_force_splits : 0;
         if (want == 0) {
             want = (!pair && !duo && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
-            if (!pair && !duo && M <= 32 && p.k_blocks >= 8) {
+            if (!pair && !duo && M <= 128 && p.k_blocks >= 8) {
                 // Weight-streaming regime (partial sums are negligible next to the weights): pick the split that
                 // minimises waves x (K blocks per work item + pipeline fill), which also evens out tile counts
                 // that do not divide the SM count (e.g. 224 tiles on 148 SMs).
@@ -1174,10 +1206,24 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
                 int64_t best_cost = INT64_MAX;
                 for (int sp = 1; sp <= 16 && sp <= p.k_blocks / 4; ++sp) {
                     const int64_t waves = (tiles * sp + st->sm_count - 1) / st->sm_count;
-                    const int64_t cost = waves * ((p.k_blocks + sp - 1) / sp + 6);
+                    // a cut tile also writes and re-reads M x 128 f32 partial sums (weighted as M / 32 K blocks of time, fitted to measurements)
+                    // and the reduction kernel costs about four K blocks of time
+                    const int64_t cost = waves * ((p.k_blocks + sp - 1) / sp + 6 + (sp > 1 ? M / 32 : 0)) + (sp > 1 ? 4 : 0);
                     if (cost < best_cost) { best_cost = cost; best = sp; }
                 }
                 want = best;
+                // Uneven cut: tiles that fill whole waves of CTAs stay whole (no partial sums, no reduction for
+                // them); only the remainder is cut, into as many K ranges as make its last wave short.
+                const int64_t whole = (tiles / st->sm_count) * st->sm_count;
+                if (g_force_splits == 0 && p.m_tiles == 1 && whole > 0 && whole < tiles) {
+                    const int64_t r = tiles - whole;
+                    for (int sp = 2; sp <= 16 && sp <= p.k_blocks / 4; ++sp) {
+                        const int64_t waves = (r * sp + st->sm_count - 1) / st->sm_count;
+                        const int64_t cost = (whole / st->sm_count) * (p.k_blocks + 6) +
+                                             waves * ((p.k_blocks + sp - 1) / sp + 6 + M / 32) + 4;
+                        if (cost < best_cost) { best_cost = cost; want = sp; p.whole_tiles = (int32_t)whole; }
+                    }
+                }
             }
         }
         if (want > p.k_blocks / 4) want = p.k_blocks / 4;
@@ -1304,7 +1350,7 @@ int gemm_noalloc_status(int reset) {
 
 size_t gemm_noalloc_capacity() { return kNoAllocScratchBytes - kNoAllocHeaderBytes; }
 
-void gemm_set_splits(int n) { g_force_splits = n < 0 ? 0 : n; }
+void gemm_set_splits(int n) { g_force_splits = n < -1 ? 0 : n; }   // -1: automatic, every tile cut alike (A/B)
 
 int gemm_warm() {
     std::lock_guard<std::mutex> lk(g_mu);
