@@ -63,6 +63,16 @@ __device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
     return r;
 }
 
+// four floats -> four e4m3 bytes in one word (byte i = enc(v_i)); both conversions and the packing in one statement
+__device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float v0, float v1, float v2, float v3) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 t0, t1;\n\tcvt.rn.satfinite.e4m3x2.f32 t0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 t1, %4, %3;\n\tmov.b32 %0, {t0, t1};\n\t}"
+        : "=r"(r)
+        : "f"(v0), "f"(v1), "f"(v2), "f"(v3));
+    return r;
+}
+
 // e4m3 byte -> float (exact)
 __device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
     uint32_t h2;

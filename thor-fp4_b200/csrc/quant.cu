@@ -477,10 +477,8 @@ quant_mx_kernel(const T* __restrict__ x, int64_t R, int64_t K,
 #pragma unroll
                     for (int i = 0; i < 8; ++i) w0 |= e2m1_ties_up(f[u][i] * inv) << (4 * i);
                 } else {
-                    w0 = f32x2_to_e4m3x2(f[u][0] * inv, f[u][1] * inv) |
-                         (f32x2_to_e4m3x2(f[u][2] * inv, f[u][3] * inv) << 16);
-                    w1 = f32x2_to_e4m3x2(f[u][4] * inv, f[u][5] * inv) |
-                         (f32x2_to_e4m3x2(f[u][6] * inv, f[u][7] * inv) << 16);
+                    w0 = f32x4_to_e4m3x4(f[u][0] * inv, f[u][1] * inv, f[u][2] * inv, f[u][3] * inv);
+                    w1 = f32x4_to_e4m3x4(f[u][4] * inv, f[u][5] * inv, f[u][6] * inv, f[u][7] * inv);
                 }
             }
             if (col_ok && r < Rpad) {
