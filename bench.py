@@ -24,6 +24,16 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT / "thor-fp4_b200"))
 sys.path.insert(0, str(ROOT))
 
+# The reference arm is CPU work on all host threads.  torchrun exports OMP_NUM_THREADS=1 to its workers when the
+# variable is unset, which would pin the BLAS matmul of that arm to one thread: give it the cores before numpy loads.
+if "--impl" in sys.argv[1:] and "reference" in sys.argv[1:]:
+    try:
+        _ncpu = len(os.sched_getaffinity(0))
+    except AttributeError:
+        _ncpu = os.cpu_count() or 1
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(_ncpu)
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
