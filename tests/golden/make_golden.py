@@ -7,15 +7,16 @@ seeded inputs shaped after the reference's own quantizer tests
 and the values the reference returns.  The CPU oracle and the CUDA library are
 then checked against these vectors without the reference being present.
 
-usage: python tests/golden/make_golden.py [reference-checkout]   (default /root/reference)
+usage: python tests/golden/make_golden.py [reference-checkout]   (default: $THOR_FP4_REFERENCE)
 """
+import os
 import sys
 from pathlib import Path
 
 import numpy as np
 import torch
 
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("THOR_FP4_REFERENCE", "/root/reference"))
 sys.path.insert(0, str(ref / "src"))
 from thor_fp4.quant import mx_fake_quant, nvfp4_fake_quant, two_level_scale  # noqa: E402
 
