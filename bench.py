@@ -324,6 +324,22 @@ def run_sweep(args):
                 del xs, yq
         del xq, pq, sq
         torch.cuda.empty_cache()
+    # the MX quantizer (UE8M0 scale per 32 elements) on the activation shapes of the mixed-format path
+    for (R, K) in ((4096, 8192), (16384, 8192)):
+        n = max(2, int(300e6 / (R * K * 2)) + 1)
+        xq = [torch.randn(R, K, device="cuda").bfloat16() for _ in range(n)]
+        pq = torch.zeros(ops.mx_packed_bytes(R, K, "mxfp8"), dtype=torch.uint8, device="cuda")
+        sq = torch.zeros(ops.mx_scale_bytes(R, K), dtype=torch.uint8, device="cuda")
+        cnt = [0]
+
+        def mx_step():
+            ops.quantize_mx(xq[cnt[0] % n], "mxfp8", pq, sq)
+            cnt[0] += 1
+        us = timed(mx_step, args.steps)
+        print(f"| quantize_mx mxfp8 bf16 [{R}, {K}] | - | quant_mx_kernel | {us:.1f} | - | {R * K * (2 + 1 + 1 / 32) / us / 1e3:.0f} (algorithmic bytes) |",
+              flush=True)
+        del xq, pq, sq
+        torch.cuda.empty_cache()
     # batch-1 engines: exact-activation GEMV (one launch) against quantize + split-K GEMM
     for (K, N) in ((8192, 8192), (8192, 28672), (28672, 8192)):
         for eng in ("gemv", "cublaslt"):
