@@ -284,3 +284,28 @@ def test_dependent_launch_chain_equals_plain_stream_order(M):
             assert torch.equal(y, want[i])
     finally:
         L.tfp4_set_dependent_launch(1)
+
+
+@gpu
+def test_two_streams_interleaved_layer_calls_give_serial_results():
+    # two layers driven from two streams at once (dependent launches chain only within a stream): every result
+    # must equal the one computed alone
+    import thor_fp4
+    torch.manual_seed(9)
+    a = thor_fp4.Linear(2048, 1024, bias=True, out_dtype="bf16", device="cuda")
+    b = thor_fp4.Linear(1024, 1536, bias=False, out_dtype="f16", device="cuda")
+    xa = [torch.randn(64, 2048, device="cuda").bfloat16() for _ in range(6)]
+    xb = [torch.randn(300, 1024, device="cuda").bfloat16() for _ in range(6)]
+    want_a = [a(x).clone() for x in xa]
+    want_b = [b(x).clone() for x in xb]
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    got_a, got_b = [], []
+    for i in range(6):
+        with torch.cuda.stream(s1):
+            got_a.append(a(xa[i]).clone())
+        with torch.cuda.stream(s2):
+            got_b.append(b(xb[i]).clone())
+    torch.cuda.synchronize()
+    for w, g in zip(want_a + want_b, got_a + got_b):
+        assert torch.equal(w, g)
