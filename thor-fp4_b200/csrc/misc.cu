@@ -102,7 +102,7 @@ __device__ __forceinline__ GvRaw<LB> gv_fetch(const uint8_t* wp, const uint8_t* 
 }
 
 template <typename XT, int MT, int LB>
-__global__ void __launch_bounds__(GV_THREADS, (MT <= 2) ? 2 : 1)
+__global__ void __launch_bounds__(GV_THREADS, (MT <= 4) ? 2 : 1)
 gemv_nvfp4_kernel(const XT* __restrict__ x, int M, const uint8_t* __restrict__ pB,
                   const uint8_t* __restrict__ sgemv, float ts, int64_t N, int64_t K,
                   void* __restrict__ out, int out_dtype) {
@@ -206,12 +206,12 @@ unsigned blocks_for(int64_t total, int threads) {
 template <typename XT>
 int launch_gemv(const void* x, int64_t M, int64_t K, const uint8_t* pB, const uint8_t* sg, float ts,
                 void* out, int64_t N, int out_dtype, cudaStream_t stream) {
-    // two CTAs per SM for M <= 2 (one above: the activations of 4 / 8 rows fill the registers); more CTAs
+    // two CTAs per SM for M <= 4 (one for 5..8 rows, whose activations fill the registers); more CTAs
     // when the rows per CTA would exceed the shared-memory slots
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int64_t ctas = (int64_t)sms * (M <= 2 ? 2 : 1);
+    int64_t ctas = (int64_t)sms * (M <= 4 ? 2 : 1);
     const int64_t need = (N + GV_MAX_ROWS - 1) / GV_MAX_ROWS;
     if (ctas < need) ctas = need;
     if (ctas > N) ctas = N;
