@@ -221,6 +221,7 @@ int launch_gemv(const void* x, int64_t M, int64_t K, const uint8_t* pB, const ui
     if (M <= 1) gemv_nvfp4_kernel<XT, 1, 16><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
     else if (M <= 2) gemv_nvfp4_kernel<XT, 2, 16><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
     else if (M <= 4) gemv_nvfp4_kernel<XT, 4, 8><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
+    else if (M <= 6) gemv_nvfp4_kernel<XT, 6, 8><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
     else gemv_nvfp4_kernel<XT, 8, 8><<<grid, GV_THREADS, 0, stream>>>(xp, m, pB, sg, ts, N, K, out, out_dtype);
     TFP4_CK(cudaGetLastError());
     return TFP4_OK;
