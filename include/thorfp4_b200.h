@@ -161,8 +161,9 @@ void tfp4_clear_status(void);
 void tfp4_plan_stats(uint64_t* hits, uint64_t* misses);
 void tfp4_set_token_tile(int bn);
 
-/* Further test / profiling hooks (no counterpart in the reference): pair_mode 1 = use the
- * two-CTA (cta_group::2) kernel whenever the shape allows, anything else = never; debug bits switch off parts of the GEMM kernel
+/* Further test / profiling hooks (no counterpart in the reference): pair_mode -1 (default) = the two-CTA
+ * (cta_group::2) kernel for batches above 128 tokens with enough tiles, 0 = single-CTA kernel only, 1 or 2 = the
+ * two-CTA kernel whenever the shape allows it; debug bits switch off parts of the GEMM kernel
  * for ablation timing (bit0 stores, bit1 scale copies, bit2 MMAs, bit3 loads, bit4 tensor-memory
  * reads; bit 1024 records per-CTA cycle counters read back with tfp4_debug_stats: 4 values per CTA). */
 void tfp4_set_pair_mode(int mode);

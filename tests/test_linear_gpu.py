@@ -309,3 +309,55 @@ def test_two_streams_interleaved_layer_calls_give_serial_results():
     torch.cuda.synchronize()
     for w, g in zip(want_a + want_b, got_a + got_b):
         assert torch.equal(w, g)
+
+
+@gpu
+def test_two_streams_both_split_k_give_serial_results():
+    # two small-batch layers (both on the split-K path, each with f32 partial sums) driven from two streams at
+    # once: each stream owns its partial-sum block, so every result must equal the one computed alone
+    import thor_fp4
+    from thor_fp4 import _ext
+    torch.manual_seed(10)
+    a = thor_fp4.Linear(8192, 1024, bias=True, out_dtype="bf16", device="cuda")
+    b = thor_fp4.Linear(4096, 1536, bias=False, out_dtype="f16", device="cuda")
+    xa = [torch.randn(64, 8192, device="cuda").bfloat16() for _ in range(8)]
+    xb = [torch.randn(100, 4096, device="cuda").bfloat16() for _ in range(8)]
+    want_a = [a(x).clone() for x in xa]
+    want_b = [b(x).clone() for x in xb]
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    got_a, got_b = [], []
+    for i in range(8):
+        with torch.cuda.stream(s1):
+            got_a.append(a(xa[i]).clone())
+        with torch.cuda.stream(s2):
+            got_b.append(b(xb[i]).clone())
+    torch.cuda.synchronize()
+    assert _ext.status() == 0
+    for w, g in zip(want_a + want_b, got_a + got_b):
+        assert torch.equal(w, g)
+
+
+@gpu
+def test_captured_small_batch_graph_survives_larger_split_k_shapes():
+    # a graph captured at a small batch keeps its own partial-sum block: running larger split-K shapes afterwards
+    # (which need more workspace) neither frees nor reuses it, so the replay still gives the eager result
+    import thor_fp4
+    torch.manual_seed(11)
+    small = thor_fp4.Linear(4096, 512, bias=True, out_dtype="bf16", device="cuda")
+    x16 = torch.randn(16, 4096, device="cuda").bfloat16()
+    want = small(x16).clone()
+    g = thor_fp4.capture_module(small, x16)
+    assert torch.equal(g(x16), want)
+    wide = thor_fp4.Linear(5120, 20480, bias=False, out_dtype="bf16", device="cuda")
+    for M in (32, 128):
+        y = wide(torch.randn(M, 5120, device="cuda").bfloat16())
+        assert torch.isfinite(y.float()).all()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        wide(torch.randn(128, 5120, device="cuda").bfloat16())
+    torch.cuda.synchronize()
+    x2 = torch.randn(16, 4096, device="cuda").bfloat16()
+    want2 = small(x2).clone()
+    assert torch.equal(g(x2), want2)
+    assert torch.equal(g(x16), want)

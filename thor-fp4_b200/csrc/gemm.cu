@@ -3,13 +3,12 @@
 //   out[m, n] = cast( alpha * sum_k deq(act)[m, k] * deq(W)[n, k] + bias[n] )
 //
 // This replaces the reference's cuBLASLt call (csrc/thor_fp4_core.cu:697-757) and its CUTLASS
-// variants (csrc/cutlass_kernels.cu:191-224).  Three kernels share the PTX wrappers below:
+// variants (csrc/cutlass_kernels.cu:191-224).  Two kernels share the PTX wrappers below:
 //   * gemm_duo_kernel (gemm_duo.cuh): CTA pairs, 256-token x 256-feature tiles, the path of every
 //     batch above 128 tokens with enough tiles to fill the GPU;
 //   * gemm_bs_kernel (this file): one CTA per tile, computed as (W @ act^T) - the 128-row MMA "M" side
 //     is a tile of WEIGHT rows and the "N" side a tile of BN tokens, so a batch of any size only pads
-//     the narrow side; with split K (f32 partial tiles + splitk_reduce_kernel) it is the small-batch path;
-//   * gemm_pair_kernel (gemm_pair.cuh): an earlier two-CTA form, opt-in, kept for comparison.
+//     the narrow side; with split K (f32 partial tiles + splitk_reduce_kernel) it is the small-batch path.
 //
 // gemm_bs_kernel, per CTA (persistent over output tiles, 320 threads):
 //   warp 0      producer: per 128-byte K block one TMA tile of W codes, one of
@@ -68,14 +67,16 @@ struct GemmParams {
     int32_t k_blocks;
     int32_t last_atoms;      // NVFP4: 64-element MMAs in the last K block (1..4); MX: 32-element ones
     int32_t stages;
-    int32_t splits;          // K is cut into this many ranges; > 1: partial sums go to `ws` (f32, [split][M][N])
+    int32_t splits;          // K is cut into this many ranges; > 1: partial sums go to `ws` (f32, [split][M][N - ws_n0]:
+                             // only the columns of the cut tiles are held)
     int32_t kb_per_split;
     int32_t whole_tiles;     // the first `whole_tiles` output tiles are one work item each (all of K, final output);
                              // the tiles after them are cut into `splits` K ranges (0: every tile is cut)
     float* ws;
+    int64_t ws_n0;           // first output column of the cut tiles (a multiple of 128; 0 when every tile is cut)
     int32_t debug;           // test hook: bit0 no stores, bit1 no scale copies, bit2 no MMA, bit3 no loads, bit4 no tmem loads
     int* status;             // host-visible status word (0 = ok)
-    unsigned long long* stats;   // host-visible per-CTA cycle counters (debug bit 1024), 4 per CTA
+    unsigned long long* stats;   // host-visible per-CTA cycle counters (debug bit 1024): 4 per CTA, then 2 more per CTA from entry 1024
 };
 
 // Work item -> (output tile, K range).  Items [0, whole_tiles) are whole tiles; item whole_tiles + j is K range
@@ -236,7 +237,9 @@ constexpr int EPI_STAGE_BYTES = 2 * 16384;
 template <int BN>
 __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t tmem_acc, int ew, int lane,
                                            int64_t n_base, int64_t m0, uint8_t* stage,
-                                           void* out_ptr, int out_dtype, const float* bias) {
+                                           void* out_ptr, int out_dtype, const float* bias, int64_t ld, int64_t col0) {
+    // out_ptr is a row-major matrix with `ld` elements per row whose first column is output column `col0`
+    // (the final output: ld = N, col0 = 0; a split-K partial block: the cut columns only)
     const int64_t n = n_base + ew * 32 + lane;
     const float bias_n = (bias != nullptr && n < p.N) ? bias[n] : 0.f;
     const float alpha = p.alpha;
@@ -272,7 +275,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, uint32_t tmem_ac
             const int64_t nn = n_base + (int64_t)piece * (16 / esize);
             if (m < p.M && nn < p.N) {
                 const uint4 val = *reinterpret_cast<const uint4*>(buf + row * row_bytes + piece * 16);
-                *reinterpret_cast<uint4*>(out + (m * p.N + nn) * esize) = val;
+                *reinterpret_cast<uint4*>(out + (m * ld + (nn - col0)) * esize) = val;
             }
         }
     };
@@ -723,9 +726,11 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (!mbar_wait_parked(smem_u32(&tfull_bar[acc]), acc_ph, abort_flag, 4)) { ok = false; break; }
             tc_fence_after();
             if (wi.partial)   // partial sum of this K range, f32, bias and cast happen in the reduction
-                drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.ws + sp * p.M * p.N, OUT_F32, nullptr);
+                drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage,
+                               p.ws + sp * p.M * (p.N - p.ws_n0), OUT_F32, nullptr, p.N - p.ws_n0, p.ws_n0);
             else
-                drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.out, p.out_dtype, p.bias);
+                drain_tile<BN>(p, tmem_base + acc * BN, ew, lane, nt * BM, mt * BN, epi_stage, p.out, p.out_dtype, p.bias,
+                               p.N, 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
@@ -800,14 +805,15 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t M, int64_t N, int64_t n0,
                      const float* __restrict__ bias, void* __restrict__ out, int out_dtype) {
     // columns [n0, N) of every row are the cut tiles (the columns before them were written by whole-tile items)
-    const int64_t width = N - n0, MN = M * N;
+    // (the partial sums hold those columns only: [split][M][N - n0])
+    const int64_t width = N - n0, MW = M * width;
     const int64_t e = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (e >= M * width) return;
+    if (e >= MW) return;
     const int64_t i = (e / width) * N + n0 + (e % width);
     griddep_wait();     // launched while the GEMM still runs; its partial sums are complete after this
-    float4 acc = *reinterpret_cast<const float4*>(ws + i);
+    float4 acc = *reinterpret_cast<const float4*>(ws + e);
     for (int s = 1; s < splits; ++s) {
-        const float4 v = *reinterpret_cast<const float4*>(ws + (int64_t)s * MN + i);
+        const float4 v = *reinterpret_cast<const float4*>(ws + (int64_t)s * MW + e);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     if (bias != nullptr) {
@@ -827,13 +833,14 @@ splitk_reduce_kernel(const float* __restrict__ ws, int splits, int64_t M, int64_
     }
 }
 
-#include "gemm_pair.cuh"
 #include "gemm_duo.cuh"
 
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+constexpr int kStatsWords = 256 * 6;    // debug counters: 4 per CTA for up to 256 CTAs, then 2 more per CTA
 
 struct DeviceState {
     int sm_count = 0;
@@ -842,9 +849,13 @@ struct DeviceState {
     int* status_dev = nullptr;
     unsigned long long* stats_host = nullptr;
     unsigned long long* stats_dev = nullptr;
-    float* ws = nullptr;          // split-K partial sums, grown on demand
-    size_t ws_bytes = 0;
-    bool pair_attr_set[2][2] = {{false, false}, {false, false}};
+    // Split-K partial sums.  One block per owner: a stream for eager calls, a capture sequence for calls recorded
+    // into a CUDA graph (the graph may later replay on any stream, so its kernels must not share a block with
+    // eager calls of other streams).  A block that has become too small is replaced, never freed: kernels already
+    // launched and graphs already captured keep its address.
+    struct WsBlock { float* ptr = nullptr; size_t bytes = 0; };
+    std::map<uint64_t, WsBlock> ws_by_owner;
+    size_t ws_retired_bytes = 0;
     bool duo_attr_set = false;
     bool attr_set[2][5] = {{false, false, false, false, false}, {false, false, false, false, false}};
 };
@@ -895,7 +906,7 @@ int ensure_device(DeviceState** out, bool with_pinned = true) {
         TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.status_host), sizeof(int), cudaHostAllocMapped));
         *st.status_host = 0;
         TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.status_dev), st.status_host, 0));
-        TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.stats_host), 256 * 4 * sizeof(unsigned long long), cudaHostAllocMapped));
+        TFP4_CK(cudaHostAlloc(reinterpret_cast<void**>(&st.stats_host), kStatsWords * sizeof(unsigned long long), cudaHostAllocMapped));
         TFP4_CK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&st.stats_dev), st.stats_host, 0));
     }
     *out = &st;
@@ -959,7 +970,7 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     cudaError_t e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_bs_kernel<KIND, BN, true>, plan.tmW, plan.tmA, p)
                             : cudaLaunchKernelEx(&cfg, gemm_bs_kernel<KIND, BN, false>, plan.tmW, plan.tmA, p);
     if (e == cudaSuccess && p.splits > 1) {
-        const int64_t n0 = (p.whole_tiles / p.m_tiles) * BM;     // whole_tiles is a multiple of m_tiles
+        const int64_t n0 = p.ws_n0;
         const int64_t elems = p.M * (p.N - n0);
         cfg.gridDim = dim3((unsigned)((elems / 4 + 255) / 256));
         cfg.blockDim = dim3(256);
@@ -969,40 +980,6 @@ int launch(DeviceState* st, const Plan& plan, GemmParams& p, int bn_slot, cudaSt
     }
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: GEMM launch failed: %s\n", cudaGetErrorString(e));
-        return TFP4_ERR_LAUNCH;
-    }
-    return TFP4_OK;
-}
-
-template <int KIND, int BN>
-int launch_pair(DeviceState* st, const Plan& plan, GemmParams& p, int slot, cudaStream_t stream) {
-    using C = PairCfg<KIND, BN>;
-    size_t smem = (size_t)C::STAGES * C::STAGE_BYTES + 512 + EPI_STAGE_BYTES + 1024;
-    if (smem < 120 * 1024) smem = 120 * 1024;
-    if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
-    p.stages = C::STAGES;
-    if (!st->pair_attr_set[KIND][slot]) {
-        TFP4_CK(cudaFuncSetAttribute(gemm_pair_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     st->max_smem));
-        st->pair_attr_set[KIND][slot] = true;
-    }
-    const int64_t tiles = p.m_tiles * ((p.n_tiles + 1) / 2);
-    const int64_t pairs = st->sm_count / 2;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
-    cfg.blockDim = dim3(GEMM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND, BN>, plan.tmW, plan.tmA, p);
-    if (e != cudaSuccess) {
-        fprintf(stderr, "thor_fp4_b200: pair GEMM launch failed: %s\n", cudaGetErrorString(e));
         return TFP4_ERR_LAUNCH;
     }
     return TFP4_OK;
@@ -1079,15 +1056,52 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int d
 // scratch supplied by the caller of gemm_block_scaled_ws instead of the library's own
 struct ExtScratch {
     int* status;                 // device-visible status word
-    unsigned long long* stats;   // 256 x 4 counters (may be null)
+    unsigned long long* stats;   // kStatsWords counters (may be null)
     float* ws;                   // split-K partial sums
     size_t ws_bytes;
 };
 
+// The split-K workspace of the stream (or capture sequence) this call belongs to, at least `need` bytes.
+// Allocates only when that owner has no block yet or its block is too small - i.e. on the first call of a
+// shape, like the plan itself; the old block stays allocated (it may be referenced by work in flight or by a
+// captured graph).  While the stream is being captured the allocation is made with the thread's capture mode
+// relaxed for the duration of the cudaMalloc, which is executed immediately and is not part of the graph.
+int workspace_for(DeviceState* st, cudaStream_t stream, size_t need, float** out) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    unsigned long long cap_id = 0;
+    if (cudaStreamGetCaptureInfo(stream, &cap, &cap_id) != cudaSuccess) {
+        cudaGetLastError();
+        cap = cudaStreamCaptureStatusNone;
+    }
+    const bool capturing = cap == cudaStreamCaptureStatusActive;
+    const uint64_t owner = capturing ? ((1ull << 63) | (uint64_t)cap_id) : (uint64_t)reinterpret_cast<uintptr_t>(stream);
+    DeviceState::WsBlock& blk = st->ws_by_owner[owner];
+    if (blk.bytes < need) {
+        const size_t gran = (size_t)4 << 20;
+        size_t bytes = ((need + gran - 1) / gran) * gran;
+        if (bytes < ((size_t)8 << 20)) bytes = (size_t)8 << 20;
+        float* ptr = nullptr;
+        cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+        if (capturing) cudaThreadExchangeStreamCaptureMode(&mode);
+        const cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ptr), bytes);
+        if (capturing) cudaThreadExchangeStreamCaptureMode(&mode);
+        if (e != cudaSuccess) {
+            fprintf(stderr, "thor_fp4_b200: cudaMalloc of %zu bytes of split-K workspace failed: %s\n", bytes, cudaGetErrorString(e));
+            cudaGetLastError();
+            return TFP4_ERR_CUDA;
+        }
+        st->ws_retired_bytes += blk.bytes;     // the superseded block is kept, not freed
+        blk.ptr = ptr;
+        blk.bytes = bytes;
+    }
+    *out = blk.ptr;
+    return TFP4_OK;
+}
+
 int g_force_bn = 0;
 int g_force_splits = 0;    // 0 automatic, 1 never split K, n split into (about) n ranges
-int g_pair_mode = -1;   // -1: automatic (256x256 two-CTA kernel for NVFP4 batches above 128 tokens); 0: single-CTA kernel only;
-                        // 1: the older two-CTA kernel (weights on the MMA's M side); 2: same as automatic
+int g_pair_mode = -1;   // -1: automatic (256x256 two-CTA kernel for batches above 128 tokens with enough tiles); 0: single-CTA
+                        // kernel only; 1 or 2: the two-CTA kernel whenever the shape allows it
 int g_debug = 0;
 
 }  // namespace
@@ -1133,19 +1147,16 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     }
     int dev = 0;
     cudaGetDevice(&dev);
-    // two-CTA kernel: needs at least one 256-row weight tile pair and a wide token tile
-    // (opt-in: cross-CTA barrier round trips currently keep it behind the single-CTA kernel)
-    const bool pair = g_pair_mode == 1 && (bn == 256 || bn == 192) && N >= 256 && st->sm_count >= 2;
     // 256 x 256 tiles on CTA pairs: NVFP4, no forced tile width or K split; chosen automatically once
     // there are enough tiles to occupy most CTA pairs (smaller batches do better on single-CTA tiles with split K)
     const int64_t duo_tiles = ((M + 255) / 256) * ((N + 255) / 256);
     const bool duo_ok = M > 128 && N >= 64 && g_force_bn == 0 && g_force_splits <= 1 && st->sm_count >= 2;
     // measured: from 192 tokens on the two-CTA kernel is level with or ahead of the single-CTA one even when its
     // 256x256 tiles fill only part of the GPU (8192 x 8192 at 256 tokens: 18.6 against 20.7 us)
-    const bool duo = duo_ok && (g_pair_mode == 2 ||
+    const bool duo = duo_ok && (g_pair_mode >= 1 ||
                                 (g_pair_mode == -1 && (M >= 192 || duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5)));
-    const uint32_t box_a = duo ? 128u : (pair ? (uint32_t)(bn / 2) : (uint32_t)bn);
-    PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : (pair ? -bn : bn), dev};
+    const uint32_t box_a = duo ? 128u : (uint32_t)bn;
+    PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : bn, dev};
     auto it = g_plans.find(key);
     if (it == g_plans.end()) {
         ++g_plan_misses;
@@ -1193,12 +1204,13 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.kb_per_split = p.k_blocks;
     p.whole_tiles = 0;
     p.ws = nullptr;
+    p.ws_n0 = 0;
     {
         const int64_t tiles = p.m_tiles * p.n_tiles;
         int want = g_force_splits > 0 ? g_force_splits : 0;
         if (want == 0) {
-            want = (!pair && !duo && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
-            if (!pair && !duo && M <= 128 && p.k_blocks >= 8) {
+            want = (!duo && tiles * 2 <= st->sm_count && p.k_blocks >= 8) ? (int)(st->sm_count / tiles) : 1;
+            if (!duo && M <= 128 && p.k_blocks >= 8) {
                 // Weight-streaming regime (partial sums are negligible next to the weights): pick the split that
                 // minimises waves x (K blocks per work item + pipeline fill), which also evens out tile counts
                 // that do not divide the SM count (e.g. 224 tiles on 148 SMs).
@@ -1228,27 +1240,39 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
         }
         if (want > p.k_blocks / 4) want = p.k_blocks / 4;
         if (want > 16) want = 16;
-        if (want > 1 && !pair && !duo) {
-            p.kb_per_split = (p.k_blocks + want - 1) / want;
-            p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+        if (duo) want = 1;
+        // partial sums are held for the cut tiles' columns only (the automatic plans cut at most about one wave of
+        // CTAs worth of tiles: <= 148 x 128 columns x 128 tokens x 4 bytes = 9.7 MB); a scratch that is too small
+        // for the automatic cut gets fewer K ranges (down to none), a forced cut that does not fit is refused
+        const size_t cap = ext != nullptr ? ext->ws_bytes : ((size_t)1 << 30);
+        size_t need = 0;
+        for (;; --want) {
+            p.splits = 1;
+            p.kb_per_split = p.k_blocks;
+            if (want > 1) {
+                p.kb_per_split = (p.k_blocks + want - 1) / want;
+                p.splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+            }
+            if (p.splits <= 1) {
+                p.splits = 1;
+                p.whole_tiles = 0;
+                need = 0;
+                break;
+            }
+            p.ws_n0 = (int64_t)(p.whole_tiles / p.m_tiles) * BM;     // whole_tiles is a multiple of m_tiles
+            need = (size_t)p.splits * (size_t)M * (size_t)(N - p.ws_n0) * sizeof(float);
+            if (need <= cap) break;
+            if (g_force_splits > 0) {      // an explicitly requested cut is not silently changed
+                fprintf(stderr, "thor_fp4: split-K into %d ranges needs %zu bytes of scratch, %zu available\n", p.splits, need, cap);
+                return TFP4_ERR_BAD_ARG;
+            }
         }
         if (p.splits > 1) {
-            const size_t need = (size_t)p.splits * (size_t)M * (size_t)N * sizeof(float);
             if (ext != nullptr) {
-                if (need > ext->ws_bytes) {
-                    fprintf(stderr, "thor_fp4: split-K needs %zu bytes of scratch, %zu available\n", need, ext->ws_bytes);
-                    return TFP4_ERR_BAD_ARG;
-                }
                 p.ws = ext->ws;
             } else {
-                if (st->ws_bytes < need) {      // like the reference's scratch: grows on first / larger shapes
-                    if (st->ws) cudaFree(st->ws);
-                    st->ws = nullptr;
-                    st->ws_bytes = 0;
-                    TFP4_CK(cudaMalloc(reinterpret_cast<void**>(&st->ws), need));
-                    st->ws_bytes = need;
-                }
-                p.ws = st->ws;
+                rc = workspace_for(st, stream, need, &p.ws);
+                if (rc) return rc;
             }
         }
     }
@@ -1257,10 +1281,6 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
     if (duo) return launch_duo(st, pl, p, kind, dev, stream);
-    if (pair) {
-        if (kind == 0) return bn == 256 ? launch_pair<0, 256>(st, pl, p, 0, stream) : launch_pair<0, 192>(st, pl, p, 1, stream);
-        return bn == 256 ? launch_pair<1, 256>(st, pl, p, 0, stream) : launch_pair<1, 192>(st, pl, p, 1, stream);
-    }
 #define TFP4_GO(KINDV)                                                          \
     switch (bn) {                                                               \
         case 32: return launch<KINDV, 32>(st, pl, p, 0, stream);                \

@@ -1,6 +1,6 @@
 // gemm_duo.cuh -- the large-batch NVFP4 GEMM: a cluster of two CTAs computes a 256-token x
 // 256-feature tile with tcgen05.mma.cta_group::2.  Included by gemm.cu inside its anonymous
-// namespace, after the single-CTA kernel, its PTX wrappers and gemm_pair.cuh.
+// namespace, after the single-CTA kernel and its PTX wrappers.
 //
 // Why this shape.  Measured on B200: one 128x256x64 NVFP4 MMA takes 128 cycles whatever feeds it
 // (and one 256x256x64 MMA of a CTA pair the same 128), a barrier hop inside a CTA costs ~180
@@ -63,6 +63,21 @@ struct DuoCfg {
     static_assert(NSLOT == OP_STAGES, "K block i uses operand stage and scale slot i % OP_STAGES alike");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 __device__ __forceinline__ void tc_mma_pair_nvf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                  uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
@@ -478,8 +493,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 p.stats[blockIdx.x * 4 + 1] = (unsigned long long)c_wait;
                 p.stats[blockIdx.x * 4 + 2] = (unsigned long long)n_miss;
                 p.stats[blockIdx.x * 4 + 3] = (unsigned long long)c_acc;
-                p.stats[600 + blockIdx.x * 2] = (unsigned long long)s_commit;
-                p.stats[600 + blockIdx.x * 2 + 1] = (unsigned long long)s_obs;
+                p.stats[1024 + blockIdx.x * 2] = (unsigned long long)s_commit;
+                p.stats[1024 + blockIdx.x * 2 + 1] = (unsigned long long)s_obs;
             }
         } else {
             // -------------------------------------------------------- relay (peer CTA)
