@@ -53,6 +53,7 @@ def parse():
                     help="mlp workload on several ranks: type of the partial outputs that are all-reduced")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-mlp", action="store_true", help="skip the SwiGLU-block measurement added to the line")
     ap.add_argument("--ablate", action="store_true",
                     help="time the GEMM with parts of the kernel switched off through the library's test hooks and print a table")
     ap.add_argument("--plain-launch", action="store_true",
@@ -166,31 +167,40 @@ def cpu_baseline(args, sample_rows: int = 8192, budget_s: float = 10.0):
 
 
 def run_reference(args):
-    """--impl reference: the reference's own CPU emulation of the path on all host threads
-    (oracle port: the reference's torch code cannot travel to the GPU box); each step is a
-    bounded slab of activation rows of the same layer."""
+    """--impl reference: the reference's own CPU emulation of the path on all host threads (oracle port: the
+    reference's torch code cannot travel to the GPU box).  Runs exactly --steps timed and --warmup untimed steps
+    on all --M activation rows; only when that would take more than about four minutes (a calibration step on
+    1024 rows decides) does a step shrink to a slab of the rows, and the line says so."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import oracle as orc
     threads = orc.host_threads()
-    M = min(args.M, 1024)
-    steps, warm = max(1, min(args.steps, 10)), max(1, min(args.warmup, 2))
+    steps, warm = max(1, args.steps), max(0, args.warmup)
     lin = CpuLinear(args.N, args.K, threads)
-    x = lin.make_input(M)
-    for _ in range(warm):
-        lin.step(x)
+    probe = lin.make_input(min(args.M, 1024))
+    lin.step(probe[:64])
     t0 = time.perf_counter()
-    for _ in range(steps):
-        lin.step(x)
+    lin.step(probe)
+    per_row = (time.perf_counter() - t0) / probe.shape[0]
+    budget_rows = int(240.0 / ((steps + warm) * per_row))
+    M = args.M if budget_rows >= args.M else max(128, budget_rows // 128 * 128)
+    n_in = n_inputs(args) if M == args.M else 2
+    xs = [lin.make_input(M) for _ in range(n_in)]      # the same rotation over inputs as the GPU arm
+    for i in range(warm):
+        lin.step(xs[i % n_in])
+    t0 = time.perf_counter()
+    for i in range(steps):
+        lin.step(xs[i % n_in])
     dt = (time.perf_counter() - t0) / steps
     val = 2.0 * M * args.N * args.K / dt / 1e12
-    sample = f"{M} of {args.M} activation rows per step, oracle port, weight quantized once"
+    sample = (f"{M} of {args.M} activation rows per step, oracle port (C quantize + dequantize, numpy FP32 matmul), "
+              f"weight quantized once outside the timed steps")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus,
         "steps": steps, "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
-        "config": {"workload": workload_name(args)},
+        "config": config_dict(args, args.gpus),
         "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -466,6 +476,159 @@ def run_mlp(args):
         dist.destroy_process_group()
 
 
+def profile_traffic(name: str):
+    """DRAM bytes per launch of a kernel, as recorded in its committed ncu summary under profiles/ (the line
+    'dram_bytes_per_launch: <bytes> (<shape>)'); None when the summary or the line is missing."""
+    import re
+    f = ROOT / "profiles" / name
+    if not f.exists():
+        return None
+    m = re.search(r"^dram_bytes_per_launch:\s*([0-9.eE+]+)", f.read_text(), re.M)
+    return float(m.group(1)) if m else None
+
+
+def same_box_gpu(xs, w, M, N, K, steps):
+    """The reference's own GPU path for the same step on this GPU, outside the product's timed region: its two-kernel
+    activation quantizer and its cuBLASLt NVFP4 GEMM (csrc/thor_fp4_core.cu:555-578,697-757 of the reference project,
+    compiled unmodified for sm_100a into oracle/_ref by oracle/build_ref.sh), on the same activations and the same
+    quantized weight.  A comparison figure only; nothing of it is on the product path."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_refgpu", ROOT / "tests" / "refgpu.py")
+    refgpu = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(refgpu)
+    try:
+        L = refgpu.lib()
+    except OSError as e:
+        return {"unavailable": f"unavailable on this box: {e}"}
+    if L is None:
+        return {"unavailable": "unavailable on this box: oracle/_ref/libthorfp4_ref_core.so was not shipped"}
+    rc = L.tfp4_init(32 << 20)
+    if rc != 0:
+        return {"unavailable": f"unavailable on this box: reference tfp4_init rc={rc}"}
+    dev = xs[0].device
+    packed = torch.zeros(L.tfp4_packed_bytes(M, K), dtype=torch.uint8, device=dev)
+    sblk = torch.zeros(L.tfp4_scale_bytes(M, K), dtype=torch.uint8, device=dev)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    st = lambda: torch.cuda.current_stream().cuda_stream
+
+    def step(i, ev=None):
+        x = xs[i % len(xs)]
+        if ev:
+            ev[0].record()
+        r1 = L.tfp4_quant(x.data_ptr(), M, K, 2, 1.0, packed.data_ptr(), sblk.data_ptr(), st())
+        if ev:
+            ev[1].record()
+        r2 = L.tfp4_gemm(packed.data_ptr(), sblk.data_ptr(), 1.0, w.packed.data_ptr(), w.sblk.data_ptr(),
+                         float(w.tensor_scale), out.data_ptr(), M, N, K, 1, st())
+        if ev:
+            ev[2].record()
+        return r1, r2
+    r1, r2 = step(0)
+    if r1 != 0 or r2 != 0:
+        return {"unavailable": f"unavailable on this box: reference tfp4_quant rc={r1}, tfp4_gemm rc={r2}"}
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for i in range(steps):
+        step(i, evs[i])
+    torch.cuda.synchronize()
+    q_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in evs]))
+    g_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in evs]))
+    t_ms = evs[0][0].elapsed_time(evs[-1][2]) / steps
+    return {"source": "the reference's csrc/thor_fp4_core.cu compiled for sm_100a (oracle/_ref): tfp4_quant (two kernels) + "
+                      "tfp4_gemm (cuBLASLt NVFP4), same activations and quantized weight, same GPU, after the timed region",
+            "steps": steps, "ms_per_step": t_ms, "step_tflops": 2.0 * M * N * K / (t_ms * 1e-3) / 1e12,
+            "gemm_ms": g_ms, "gemm_tflops": 2.0 * M * N * K / (g_ms * 1e-3) / 1e12,
+            "quant_ms": q_ms, "quant_gbs": M * K * (2 + 0.5 + 1.0 / 16) / (q_ms * 1e-3) / 1e9}
+
+
+def measure_mlp_block(args, dev, rank, world, steps):
+    """BASELINE configuration 5 on the ranks of this run: the NVFP4 SwiGLU block (hidden 8192, intermediate 28672,
+    16384 tokens, weights ~N(0, 0.02)), gate/up split by rows and down by columns over the ranks, one exchange of
+    the partial outputs per block.  Every rank builds the same full weights from one seed and keeps its shard, so
+    rank 0 can compare the sharded result with the unsharded block on the same input.  Device-timed, max over ranks."""
+    import torch.distributed as dist
+    from thor_fp4 import _ext
+    from thor_fp4.fused import NVFP4GatedMLP
+    from thor_fp4.parallel import TensorParallelGatedMLP
+    M, H, I = 16384, 8192, args.inter
+    g = torch.Generator(device=dev).manual_seed(4321)
+    wg = torch.randn(I, H, device=dev, generator=g) * 0.02
+    wu = torch.randn(I, H, device=dev, generator=g) * 0.02
+    wd = torch.randn(H, I, device=dev, generator=g) * 0.02
+    xs = [torch.randn(M, H, device=dev, generator=g).bfloat16() for _ in range(2)]
+    reduce_dtype = args.reduce_dtype if world > 1 else "bf16"
+    tp = TensorParallelGatedMLP(H, I, device=dev, reduce_dtype=reduce_dtype, weight_std=0.02)
+    tp.load_full_weights(wg, wu, wd)
+    tp.local.refresh_weight()
+    err = None
+    if rank == 0:
+        full = NVFP4GatedMLP(H, I, device=dev, out_dtype="f32", weight_std=0.02)
+        with torch.no_grad():
+            full.w_gate.copy_(wg); full.w_up.copy_(wu); full.w_down.copy_(wd)
+        ref = full(xs[0][:1024]).clone()
+        del full
+    del wg, wu, wd
+    torch.cuda.empty_cache()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        for i in range(3):
+            fn(i)
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            fn(i)
+        b.record()
+        barrier()
+        t = torch.tensor([a.elapsed_time(b) / n], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+    y = tp(xs[0])
+    torch.cuda.synchronize()
+    if rank == 0:
+        got = y[:1024].float()
+        err = float((got - ref).norm() / ref.norm())
+    ms = timed(lambda i: tp(xs[i % 2]), steps)
+    ms_local = timed(lambda i: tp.local(xs[i % 2]), steps)          # the rank's GEMMs alone, nothing exchanged
+    ms_xchg = None
+    if world > 1:
+        buf = torch.zeros(M, H, dtype=torch.float32 if reduce_dtype == "f32" else torch.bfloat16, device=dev)
+        ms_xchg = timed(lambda i: dist.all_reduce(buf), steps)          # the exchange alone (NCCL all-reduce of the partials)
+    if _ext.status() != 0:
+        raise RuntimeError(f"device status word {_ext.status()}")
+    flop = 6.0 * M * H * I
+    res = {"workload": f"NVFP4 SwiGLU block, hidden {H}, intermediate {I}, {M} tokens bf16, weights ~N(0,0.02); gate/up "
+                       f"rows and down columns split over {world} rank(s)",
+           "tensor_parallel": world, "scaling": "strong", "steps": steps, "ms_per_block": ms,
+           "tflops": flop / (ms * 1e-3) / 1e12, "ms_local_gemms_only": ms_local,
+           "exchange": tp.exchange_name() if world > 1 else None, "reduce_dtype": reduce_dtype if world > 1 else None,
+           "ms_exchange_alone": ms_xchg,
+           "exchange_share": (None if world == 1 else max(0.0, 1.0 - ms_local / ms)),
+           "rel_error_vs_unsharded_block": err,
+           "fused_epilogue": bool(getattr(tp.local, "fuse_epilogue", False))}
+    del tp, xs
+    torch.cuda.empty_cache()
+    return res
+
+
+def n_inputs(args):
+    """Input buffers a run rotates over so that together they exceed the 126 MB L2 (> 256 MB of bf16 activations)."""
+    return max(2, int(np.ceil(300e6 / (args.M * args.K * 2))))
+
+
+def config_dict(args, world):
+    return {"workload": workload_name(args), "replicas": world,
+            "l2": f"inputs rotate over {n_inputs(args)} buffers of {args.M * args.K * 2 / 1e6:.0f} MB (> 126 MB L2)"}
+
+
 def workload_name(args):
     return (f"thor_fp4.Linear({args.K},{args.N},bias=False,out_dtype=bf16), activation bf16 [{args.M},{args.K}] ~N(0,1), "
             "weight Kaiming-uniform fp32 quantized once (two-level NVFP4); step = activation quantize + block-scaled GEMM")
@@ -497,7 +660,7 @@ def run_ours(args):
     lin.refresh_weight()
     w = lin._weight_fp4
     # inputs larger than L2 (126 MB): rotate over buffers totalling > 256 MB
-    n_in = max(2, int(np.ceil(300e6 / (M * K * 2))))
+    n_in = n_inputs(args)
     xs = [torch.randn(M, K, device=dev).bfloat16() for _ in range(n_in)]
     packed = torch.zeros(ops.packed_bytes(M, K), dtype=torch.uint8, device=dev)
     sblk = torch.zeros(ops.scale_bytes(M, K), dtype=torch.uint8, device=dev)
@@ -623,6 +786,18 @@ def run_ours(args):
     else:
         e2e_ms = None
 
+    # ---------------- the reference's own GPU kernels on this GPU, same operands (rank 0, outside every timed region)
+    same_box = None
+    if rank == 0 and not args.profile:
+        same_box = same_box_gpu(xs, w, M, N, K, max(5, min(args.steps, 20)))
+    barrier()
+    # ---------------- the sharded configuration (SwiGLU block over the ranks of this run)
+    mlp = None
+    if not args.profile and not args.no_mlp:
+        del xs, packed, sblk, out
+        torch.cuda.empty_cache()
+        mlp = measure_mlp_block(args, dev, rank, world, max(3, min(args.steps, 10)))
+
     t = torch.tensor([total_ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -642,21 +817,20 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
-        "config": {"workload": workload_name(args), "replicas": world,
-                   "l2": f"inputs rotate over {n_in} buffers of {M * K * 2 / 1e6:.0f} MB (> 126 MB L2)"},
+        "config": config_dict(args, world),
         "roofline": {"bound": "tensor", "kernel": "gemm_duo_kernel (tcgen05 cta_group::2 NVFP4 block-scaled GEMM, 256x256 tiles)",
                      "achieved": gemm_tflops, "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp4_peak,
                      "peak_note": f"4 x {pk['src']} bf16 burst ({pk['bf16']}); no FP4 peak is measured on this pool",
                      "frac_of_nominal_9000": gemm_tflops / 9000.0,
-                     # dram__bytes_read + dram__bytes_write of one launch at 8192^3 (ncu capture summarised under profiles/)
-                     "traffic": 208.0e6 if (M, N, K) == (8192, 8192, 8192) else None,
+                     # dram__bytes_read + dram__bytes_write of one launch at 8192^3, read from the committed ncu summary
+                     "traffic": profile_traffic("gemm_duo_kernel_8192.md") if (M, N, K) == (8192, 8192, 8192) else None,
                      "avg_launch_ms": g_ms},
         "roofline_quantizer": {"bound": "hbm", "kernel": "quant_nvfp4_kernel", "achieved": q_gbs,
                                "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": q_gbs / pk["hbm_gbs"],
                                "peak_note": f"{pk['src']} copy bandwidth",
-                               # one ncu capture of this kernel on [8192, 8192] bf16: 134.2 MB read + 20.1 MB written
-                               # (the rest of the 37.7 MB of output is still in L2 when the kernel ends)
-                               "traffic": 154.3e6 if (args.M, args.K) == (8192, 8192) else None, "avg_launch_ms": q_ms,
+                               # one ncu capture of this kernel on [8192, 8192] bf16, read from the committed summary
+                               "traffic": profile_traffic("quant_nvfp4_kernel.md") if (args.M, args.K) == (8192, 8192) else None,
+                               "avg_launch_ms": q_ms,
                                "algorithmic_bytes_per_launch": q_bytes,
                                "note": "inside the step, on [8192, 8192]; 'alone_large' is the same kernel timed alone on [16384, 8192]",
                                "alone_large": (dict(q_large, frac=q_large["achieved"] / pk["hbm_gbs"]) if q_large else None)},
@@ -668,6 +842,11 @@ def run_ours(args):
                        "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                        "ms_per_step": e2e_max,
                        "api": "thor_fp4.Linear.forward, pinned host buffers; upload, layer and download of neighbouring steps overlap on three streams"}
+    if same_box is not None:
+        same_box["ours_gemm_ms"], same_box["ours_quant_ms"], same_box["ours_ms_per_step"] = g_ms, q_ms, ms_step
+        line["same_box_gpu"] = same_box
+    if mlp is not None:
+        line["tp_mlp"] = mlp
     if not args.no_cpu and world == 1:      # the CPU baseline is a single-GPU-run item
         line["cpu_baseline"] = cpu_baseline(args)
     print(json.dumps(line))

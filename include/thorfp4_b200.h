@@ -89,7 +89,9 @@ int tfp4_linear(const void* x, int64_t M, int64_t K, int in_dtype, float act_ts,
  * activation, elementwise product, re-quantization of the hidden tensor; csrc K14 mx8_mul for the MX form)
  * for the NVFP4 block: gu is the [R, 2*I] f16/bf16 output of the stacked gate/up GEMM (I gate values,
  * then I up values per row); writes the NVFP4 codes and scale tiles of h = silu(gate) * up (FP32 math,
- * h rounded to the input type, per-tensor scale 1) exactly as tfp4_quant would from h.  in_dtype 1 f16, 2 bf16. */
+ * h rounded to the input type, per-tensor scale 1) exactly as tfp4_quant would from h.  in_dtype 1 f16, 2 bf16.
+ * The unfused form of tfp4_swiglu_gemm below (stacked halves instead of alternating blocks; gate, up and h each
+ * rounded to the 16-bit type). */
 int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype,
                       uint8_t* packed, uint8_t* sblk, void* stream);
 
@@ -151,6 +153,36 @@ const char* tfc4_variant_name(int i);
 int tfc4_variant_index(const char* name);
 int tfc4_gemm(int variant, const void* A, const void* SA, const void* B, const void* SB,
               void* D, int64_t M, int64_t N, int64_t K, float alpha, void* stream);
+
+/* Addition over tfc4_gemm: the same variants with bias[n] (N floats or NULL) fused into the epilogue and any output type
+ * (0 f16, 1 bf16, 2 f32) - the MXFP8 x MXFP4 path with its FP32 accumulator observable, which the parity tests of the
+ * fused epilogues below start from. */
+int tfc4_gemm_ex(int variant, const void* A, const void* SA, const void* B, const void* SB, const float* bias,
+                 void* D, int64_t M, int64_t N, int64_t K, float alpha, int out_dtype, void* stream);
+
+/* Replaces the fused-epilogue library of the reference (csrc/fused_kernels.cu:379-447, bound at src/thor_fp4/_ext.py:82-94):
+ * MXFP8 activations A (M,K) x MXFP4 weights B (N,K) with the inter-layer work in the GEMM's epilogue -
+ * D = e4m3 codes (M*N bytes, row-major) and SFD = UE8M0 scale tiles (tfc4f_sfd_bytes, the 128x4 layout) of
+ * act(alpha * A @ B^T + bias[n]); the variant name picks the activation (gelu | silu | ident; its tile numbers pick
+ * nothing here), the block scale is the power of two at or above amax / 448 (csrc/fused_kernels.cu:74-123).  Same
+ * argument checks and codes as the reference: -1 bad variant, -3 K % 128, -4 N % 32, -5 null bias.  gelu and silu are
+ * computed from correctly rounded FP32 operations only, so the bytes are reproducible on a CPU. */
+int tfc4f_n_variants(void);
+const char* tfc4f_variant_name(int i);
+int tfc4f_variant_index(const char* name);
+int64_t tfc4f_sfd_bytes(int64_t M, int64_t N);
+int tfc4f_gemm(int variant, const void* A, const void* SA, const void* B, const void* SB, const float* bias,
+               void* D, void* SFD, int64_t M, int64_t N, int64_t K, float alpha, void* stream);
+
+/* The NVFP4 counterpart of that fused layer for the SwiGLU block (the reference's gated block is the MXFP8 chain of
+ * src/thor_fp4/fused.py:199-232: two fused GEMMs, tfp4_mx8_mul, a third GEMM): ONE gate/up GEMM whose epilogue computes
+ * h = silu(alpha * x Wg^T) * (alpha * x Wu^T) in FP32 and quantizes it to NVFP4 (the arithmetic of tfp4_quant with
+ * per-tensor scale 1), alpha = tsA * tsW.  packedW / sblkW: the stacked weight (N = 2 * intermediate rows, K) whose rows
+ * alternate in blocks of 16 - gate rows j..j+15, then up rows j..j+15.  h_packed / h_sblk: codes (pad128(M),
+ * intermediate / 2) and scale tiles of h, ready as the A operand of the down projection; rows M..pad128(M) are written
+ * as zeros.  N % 128 == 0, K % 64 == 0.  No (M, 2 * intermediate) tensor is written to memory. */
+int tfp4_swiglu_gemm(const void* packedA, const void* sblkA, float tsA, const void* packedW, const void* sblkW, float tsW,
+                     void* h_packed, void* h_sblk, int64_t M, int64_t N, int64_t K, void* stream);
 
 /* Additions: status word of the current device (0 = healthy; otherwise the role
  * whose bounded wait expired: 1 producer, 2 accumulator hand-back, 3 operands,

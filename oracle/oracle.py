@@ -70,6 +70,11 @@ def lib():
         L.orc_scales_gemv.argtypes = [_u8p, _i64, _i64, _u8p]; L.orc_scales_gemv.restype = None
         L.orc_gemm_f64acc_rows.argtypes = [_f32p, _f32p, _f32p, ctypes.c_float, _i64, _i64, _i64, _i64, _f32p]
         L.orc_gemm_f64acc_rows.restype = None
+        for name in ("orc_det_exp2", "orc_det_rcp", "orc_det_silu", "orc_det_gelu"):
+            getattr(L, name).argtypes = [ctypes.c_float]; getattr(L, name).restype = ctypes.c_float
+        L.orc_silu_mul.argtypes = [_f32p, _f32p, _i64, _f32p]; L.orc_silu_mul.restype = None
+        L.orc_bias_act_rows.argtypes = [_f32p, _f32p, ctypes.c_int, _i64, _i64, _i64, _f32p]
+        L.orc_bias_act_rows.restype = None
         _lib = L
     return _lib
 
@@ -218,6 +223,39 @@ def mx_fake_quant(x: np.ndarray, kind="mxfp4") -> np.ndarray:
     R, K = x.shape
     p, s = quantize_mx(x, kind)
     return dequantize_mx(p, s, kind, R, K)
+
+
+# --------------------------------------------------------------------------- activations of the fused epilogues
+_ACT = {"ident": 0, "gelu": 1, "silu": 2, 0: 0, 1: 1, 2: 2}
+
+
+def silu_mul(g: np.ndarray, u: np.ndarray) -> np.ndarray:
+    """silu(g) * u in float32 with the library's reproducible silu (the hidden value of the SwiGLU block)."""
+    g = np.ascontiguousarray(g, np.float32)
+    u = np.ascontiguousarray(u, np.float32)
+    out = np.empty_like(g)
+    lib().orc_silu_mul(_f32(g), _f32(u), g.size, _f32(out))
+    return out
+
+
+def bias_act(x: np.ndarray, bias, act, threads: int = 1) -> np.ndarray:
+    """act(x + bias[col]) in float32; act 'ident' | 'gelu' | 'silu' (the library's reproducible forms)."""
+    x = np.ascontiguousarray(x, np.float32)
+    R, N = x.shape
+    out = np.empty_like(x)
+    b = np.ascontiguousarray(bias, np.float32) if bias is not None else None
+    L = lib()
+    _run(lambda r0, r1: L.orc_bias_act_rows(_f32(x), _f32(b) if b is not None else None, _ACT[act], r0, r1, N, _f32(out)),
+         _ranges(R, threads), threads)
+    return out
+
+
+def deinterleave16(gu: np.ndarray):
+    """Columns of the stacked gate/up GEMM whose weight rows alternate in blocks of 16 (16 gate features, the 16
+    matching up features, ...) -> (gate, up), each (R, N/2)."""
+    R, N = gu.shape
+    v = gu.reshape(R, N // 32, 2, 16)
+    return np.ascontiguousarray(v[:, :, 0, :]).reshape(R, N // 2), np.ascontiguousarray(v[:, :, 1, :]).reshape(R, N // 2)
 
 
 # --------------------------------------------------------------------------- GEMM emulation

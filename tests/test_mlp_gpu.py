@@ -4,9 +4,10 @@ block against a CPU emulation (fake-quantize, double-accumulate matmuls, bf16 in
 and the fused activation path against the unfused one.
 
 The reference pins the fused-epilogue outputs of its gated block only by loose tolerances
-(tests/test_fused.py:73-76 of the reference project); here h is defined as the unfused block
-holds it - FP32 silu(gate)*up rounded to bf16, per-tensor scale 1 - so the only freedom left is
-the last ulp of expf, which moves a few values across a bf16 rounding boundary."""
+(tests/test_fused.py:73-76 of the reference project); here h of the three-kernel form is defined as
+that block holds it - FP32 silu(gate)*up rounded to bf16, per-tensor scale 1 - with silu built from
+correctly rounded operations that the oracle repeats, so the codes are compared byte for byte.
+(The one-kernel form, silu and quantization in the GEMM epilogue, is in test_fused_epilogue_gpu.py.)"""
 import numpy as np
 import pytest
 import torch
@@ -21,8 +22,7 @@ def _bf16_round(a: np.ndarray) -> np.ndarray:
 
 
 def _silu_mul(g: np.ndarray, u: np.ndarray) -> np.ndarray:
-    g = g.astype(np.float32)
-    return (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u.astype(np.float32)
+    return orc.silu_mul(g, u)
 
 
 @gpu
@@ -37,12 +37,8 @@ def test_swiglu_quant_matches_oracle_on_same_h(R, I):
     h = _bf16_round(_silu_mul(guf[:, :I], guf[:, I:]))
     p_ref, s_ref = orc.quantize_nvfp4(h, 1.0, threads=orc.host_threads())
     got_p, got_s = packed.cpu().numpy(), sblk.cpu().numpy()
-    # an expf that differs in its last bit moves a value across a bf16 boundary now and then: a handful of bytes
-    assert (got_s != s_ref).mean() < 2e-4
-    assert (got_p != p_ref).mean() < 5e-4
-    d_got = orc.dequantize_nvfp4(got_p, got_s, 1.0, R, I)
-    d_ref = orc.dequantize_nvfp4(p_ref, s_ref, 1.0, R, I)
-    assert np.linalg.norm(d_got - d_ref) / np.linalg.norm(d_ref) < 1e-3
+    assert np.array_equal(got_s, s_ref)
+    assert np.array_equal(got_p, p_ref)
     # rows past R of the last 128-row tile are written as zeros
     pad = ops.pad_rows(R)
     assert not got_p[R * I // 2: pad * I // 2].any()
@@ -70,6 +66,7 @@ def test_nvfp4_gated_mlp_matches_cpu_emulation(M):
     torch.manual_seed(3)
     mlp = NVFP4GatedMLP(H, I, device="cuda", out_dtype="f32", weight_std=0.05)
     x = torch.randn(M, H, device="cuda").bfloat16()
+    mlp.fuse_epilogue = False          # the three-kernel form, which holds gate, up and h in bf16 as the emulation below does
     y = mlp(x).float().cpu().numpy()
     y_unfused = None
     mlp.fuse_activation = False
@@ -88,7 +85,7 @@ def test_nvfp4_gated_mlp_matches_cpu_emulation(M):
     ref = orc.gemm_f64acc(orc.nvfp4_fake_quant(h, 1.0), wdq, None, 1.0, threads=thr)
     err = np.linalg.norm(y - ref) / np.linalg.norm(ref)
     assert err < 1e-3, err
-    assert np.linalg.norm(y - y_unfused) / np.linalg.norm(y_unfused) < 1e-3
+    assert np.linalg.norm(y - y_unfused) / np.linalg.norm(y_unfused) < 2e-3    # torch's silu differs in the last bit now and then
 
 
 @gpu

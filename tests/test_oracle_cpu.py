@@ -169,3 +169,30 @@ def test_mx8_ceil_scale_quantizer_against_torch_float8():
     # within half an e4m3 step (2^-4 relative) of the input wherever the input is not tiny next to its block's amax
     big = np.abs(blocks) > amax[..., None] * 2.0 ** -6
     assert np.max(np.abs(dblocks - blocks)[big] / np.abs(blocks)[big]) <= 2.0 ** -4 + 1e-7
+
+
+def test_reproducible_activations_are_silu_and_gelu():
+    """The activations of the fused epilogues are defined by this build (the reference's live in un-vendored CUTLASS
+    and are pinned only by tolerances): built from correctly rounded FP32 operations so that CPU and GPU agree bit for
+    bit.  Here: they are silu and gelu to FP32 working accuracy, and well behaved at the edges."""
+    import math
+    L = orc.lib()
+    xs = np.concatenate([np.linspace(-30, 30, 4001), np.array([0.0, -0.0, 1e-30, -1e-30, 88.0, -88.0, 1e4, -1e4])]).astype(np.float32)
+    for x in xs:
+        x = float(x)
+        s_ref = x / (1.0 + math.exp(-x)) if x > -700 else 0.0
+        g_ref = 0.5 * x * (1.0 + math.erf(x / math.sqrt(2.0)))
+        s, g = L.orc_det_silu(x), L.orc_det_gelu(x)
+        assert abs(s - s_ref) <= 3e-6 * abs(s_ref) + 1e-30, (x, s, s_ref)
+        assert abs(g - g_ref) <= 5e-7 * max(1.0, abs(x)), (x, g, g_ref)
+    assert L.orc_det_exp2(0.0) == 1.0 and L.orc_det_exp2(3.0) == 8.0 and L.orc_det_exp2(-2.0) == 0.25
+    assert abs(L.orc_det_rcp(3.0) - 1.0 / 3.0) < 1e-7
+    assert math.isnan(L.orc_det_silu(float("nan"))) and L.orc_det_silu(float("inf")) == float("inf")
+    g = np.array([[1.0, -2.0, 0.5, 30.0]], np.float32)
+    u = np.array([[2.0, 3.0, -4.0, 0.1]], np.float32)
+    h = orc.silu_mul(g, u)
+    assert np.allclose(h, (g / (1 + np.exp(-g))) * u, rtol=2e-6)
+    gu = np.arange(2 * 64, dtype=np.float32).reshape(2, 64)
+    gate, up = orc.deinterleave16(gu)
+    assert gate[0, :16].tolist() == list(range(16)) and up[0, :16].tolist() == list(range(16, 32))
+    assert gate[0, 16:].tolist() == list(range(32, 48)) and up[1, 16:].tolist() == list(range(64 + 48, 128))

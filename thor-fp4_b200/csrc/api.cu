@@ -24,6 +24,10 @@ void quant_set_tile_rows(int);
 int act_quant_mx8(const void*, const float*, int64_t, int64_t, int, int, uint8_t*, uint8_t*, cudaStream_t);
 int fake_quant_nvfp4(const void*, int64_t, int, float, void*, int, cudaStream_t);
 int swiglu_quant_nvfp4(const void*, int64_t, int64_t, int, uint8_t*, uint8_t*, cudaStream_t);
+int gemm_swiglu_nvfp4(const void*, const void*, const void*, const void*, float, void*, void*, int64_t, int64_t, int64_t,
+                      cudaStream_t);
+int gemm_mx8_out(const void*, const void*, const void*, const void*, float, const float*, int, void*, void*, int64_t,
+                 int64_t, int64_t, cudaStream_t);
 int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
                  int64_t, int, cudaStream_t);
 int gemm_noalloc_status(int);
@@ -47,6 +51,15 @@ const Variant kVariants[] = {
     {"mxfp8xfp4_256x128x256_c2x1", 1},
 };
 constexpr int kNVariants = (int)(sizeof(kVariants) / sizeof(kVariants[0]));
+// names of csrc/fused_kernels.cu:224-247 in the reference project: activation of the epilogue; the tile numbers of a
+// name select nothing here (one two-CTA kernel serves them all)
+struct FusedVariant { const char* name; int act; };      // act: 0 identity, 1 gelu, 2 silu
+const FusedVariant kFusedVariants[] = {
+    {"mx8out_gelu_128x128x256_c1", 1},  {"mx8out_gelu_128x128x256_c2x1", 1}, {"mx8out_gelu_128x256x256_c2x1", 1},
+    {"mx8out_gelu_128x128x128_c2x1", 1}, {"mx8out_silu_128x128x256_c1", 2},  {"mx8out_silu_128x256x256_c2x1", 2},
+    {"mx8out_ident_128x128x256_c1", 0}, {"mx8out_ident_128x256x256_c2x1", 0},
+};
+constexpr int kNFusedVariants = (int)(sizeof(kFusedVariants) / sizeof(kFusedVariants[0]));
 inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
 }  // namespace
 
@@ -123,6 +136,51 @@ int tfc4_gemm(int variant, const void* A, const void* SA, const void* B, const v
     }
     return tfp4::gemm_block_scaled(kVariants[variant].kind, A, SA, B, SB, alpha, nullptr, D, M, N, K,
                                    tfp4::OUT_BF16, S(stream));
+}
+
+int tfc4_gemm_ex(int variant, const void* A, const void* SA, const void* B, const void* SB, const float* bias, void* D,
+                 int64_t M, int64_t N, int64_t K, float alpha, int out_dtype, void* stream) {
+    if (variant < 0 || variant >= kNVariants) {
+        fprintf(stderr, "thor_fp4: bad variant %d (0..%d)\n", variant, kNVariants - 1);
+        return TFP4_ERR_CUDA;
+    }
+    return tfp4::gemm_block_scaled(kVariants[variant].kind, A, SA, B, SB, alpha, bias, D, M, N, K, out_dtype, S(stream));
+}
+
+int tfc4f_n_variants(void) { return kNFusedVariants; }
+const char* tfc4f_variant_name(int i) { return (i >= 0 && i < kNFusedVariants) ? kFusedVariants[i].name : nullptr; }
+int tfc4f_variant_index(const char* name) {
+    if (!name) return -1;
+    for (int i = 0; i < kNFusedVariants; ++i)
+        if (strcmp(name, kFusedVariants[i].name) == 0) return i;
+    return -1;
+}
+int64_t tfc4f_sfd_bytes(int64_t M, int64_t N) { return tfp4::pad128(M) * ((N / 32 + 3) / 4 * 4); }
+int tfc4f_gemm(int variant, const void* A, const void* SA, const void* B, const void* SB, const float* bias, void* D,
+               void* SFD, int64_t M, int64_t N, int64_t K, float alpha, void* stream) {
+    // argument checks and their codes as in the reference (csrc/fused_kernels.cu:423-445)
+    if (variant < 0 || variant >= kNFusedVariants) {
+        fprintf(stderr, "thor_fp4 fused: bad variant %d (0..%d)\n", variant, kNFusedVariants - 1);
+        return -1;
+    }
+    if (K % 128 != 0) {
+        fprintf(stderr, "thor_fp4 fused: K must be a multiple of 128 (got %ld)\n", (long)K);
+        return -3;
+    }
+    if (N % 32 != 0) {
+        fprintf(stderr, "thor_fp4 fused: N must be a multiple of 32 (got %ld)\n", (long)N);
+        return -4;
+    }
+    if (!bias) {
+        fprintf(stderr, "thor_fp4 fused: bias pointer is required (pass zeros)\n");
+        return -5;
+    }
+    return tfp4::gemm_mx8_out(A, SA, B, SB, alpha, bias, kFusedVariants[variant].act, D, SFD, M, N, K, S(stream));
+}
+
+int tfp4_swiglu_gemm(const void* pA, const void* sA, float tsA, const void* pW, const void* sW, float tsW, void* h_packed,
+                     void* h_sblk, int64_t M, int64_t N, int64_t K, void* stream) {
+    return tfp4::gemm_swiglu_nvfp4(pA, sA, pW, sW, tsA * tsW, h_packed, h_sblk, M, N, K, S(stream));
 }
 
 int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype, uint8_t* packed, uint8_t* sblk, void* stream) {

@@ -39,6 +39,8 @@
 #include <tuple>
 
 #include "common.cuh"
+#include "det_math.cuh"
+#include "quant_block.cuh"
 
 namespace tfp4 {
 
@@ -56,6 +58,8 @@ struct GemmParams {
     const uint8_t* sfW;      // weight scales (tile layout)
     const uint8_t* sfA;      // activation scales (tile layout)
     void* out;
+    void* out2;              // quantizing epilogues: the scale-tile buffer (out then holds the codes)
+    int32_t epi_act;         // MXFP8 epilogue: 0 identity, 1 gelu, 2 silu
     const float* bias;       // may be null
     float alpha;
     int64_t M, N, K;
@@ -1008,18 +1012,29 @@ int out_map(const CUtensorMap** map, void* out, int64_t M, int64_t N, int esize,
     return TFP4_OK;
 }
 
-int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int dev, cudaStream_t stream) {
-    const CUtensorMap* tm_out = nullptr;
-    int rc = out_map(&tm_out, p.out, p.M, p.N, p.out_dtype == OUT_F32 ? 4 : 2, dev);
-    if (rc) return rc;
+template <int KIND, int EPI>
+cudaError_t launch_duo_inst(const cudaLaunchConfig_t& cfg, const Plan& plan, const CUtensorMap& tm_out, const GemmParams& p) {
+    // the instantiation with the test hooks runs only while a debug mask is set
+    return p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<KIND, true, EPI>, plan.tmW, plan.tmA, tm_out, p)
+                   : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<KIND, false, EPI>, plan.tmW, plan.tmA, tm_out, p);
+}
+
+// epi 0: plain output (any kind); 1: SwiGLU + NVFP4 (kind 0); 2: bias + activation + MXFP8 (kind 1)
+int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int epi, int dev, cudaStream_t stream) {
+    const CUtensorMap* tm_out = &plan.tmA;      // the quantizing epilogues store with plain instructions: no output map
+    if (epi == 0) {
+        int rc = out_map(&tm_out, p.out, p.M, p.N, p.out_dtype == OUT_F32 ? 4 : 2, dev);
+        if (rc) return rc;
+    }
     const size_t smem = DuoCfg::SMEM_BYTES;
     if ((int)smem > st->max_smem) return TFP4_ERR_NO_PLAN;
     p.stages = DuoCfg::OP_STAGES;
     if (!st->duo_attr_set) {
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
-        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+#define TFP4_DUO_ATTR(K_, E_)                                                                                                   \
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<K_, false, E_>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem)); \
+        TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<K_, true, E_>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
+        TFP4_DUO_ATTR(0, 0) TFP4_DUO_ATTR(1, 0) TFP4_DUO_ATTR(0, 1) TFP4_DUO_ATTR(1, 2)
+#undef TFP4_DUO_ATTR
         st->duo_attr_set = true;
     }
     const int64_t tiles = ((p.M + DuoCfg::TILE_M - 1) / DuoCfg::TILE_M) * ((p.N + DuoCfg::TILE_N - 1) / DuoCfg::TILE_N);
@@ -1038,14 +1053,11 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int d
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl ? 2 : 1;
-    // the instantiation with the test hooks runs only while a debug mask is set
     cudaError_t e;
-    if (kind == 0)
-        e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<0, true>, plan.tmW, plan.tmA, *tm_out, p)
-                    : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<0, false>, plan.tmW, plan.tmA, *tm_out, p);
-    else
-        e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<1, true>, plan.tmW, plan.tmA, *tm_out, p)
-                    : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<1, false>, plan.tmW, plan.tmA, *tm_out, p);
+    if (epi == 1) e = launch_duo_inst<0, 1>(cfg, plan, *tm_out, p);
+    else if (epi == 2) e = launch_duo_inst<1, 2>(cfg, plan, *tm_out, p);
+    else if (kind == 0) e = launch_duo_inst<0, 0>(cfg, plan, *tm_out, p);
+    else e = launch_duo_inst<1, 0>(cfg, plan, *tm_out, p);
     if (e != cudaSuccess) {
         fprintf(stderr, "thor_fp4_b200: two-CTA GEMM launch failed: %s\n", cudaGetErrorString(e));
         return TFP4_ERR_LAUNCH;
@@ -1098,6 +1110,14 @@ int workspace_for(DeviceState* st, cudaStream_t stream, size_t need, float** out
     return TFP4_OK;
 }
 
+// what the GEMM's epilogue makes of the accumulator (see gemm_duo.cuh): 0 plain output, 1 SwiGLU + NVFP4, 2 bias +
+// activation + MXFP8; out2 = scale-tile buffer of the quantized output, act = activation of mode 2
+struct EpilogueSpec {
+    int epi = 0;
+    void* out2 = nullptr;
+    int act = 0;
+};
+
 int g_force_bn = 0;
 int g_force_splits = 0;    // 0 automatic, 1 never split K, n split into (about) n ranges
 int g_pair_mode = -1;   // -1: automatic (256x256 two-CTA kernel for batches above 128 tokens with enough tiles); 0: single-CTA
@@ -1109,7 +1129,9 @@ int g_debug = 0;
 // kind 0: NVFP4 x NVFP4 ; kind 1: MXFP8 activations x MXFP4 weights
 int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const void* packedB,
                          const void* sblkB, float alpha, const float* bias, void* out, int64_t M, int64_t N,
-                         int64_t K, int out_dtype, cudaStream_t stream, const ExtScratch* ext) {
+                         int64_t K, int out_dtype, cudaStream_t stream, const ExtScratch* ext,
+                         const EpilogueSpec* es = nullptr) {
+    const int epi = es ? es->epi : 0;
     if (M < 1 || N < 8 || (N % 8) != 0) {
         fprintf(stderr, "thor_fp4: gemm needs M >= 1, N >= 8, N %% 8 == 0 (got M=%ld N=%ld)\n", (long)M, (long)N);
         return TFP4_ERR_BAD_M;
@@ -1153,8 +1175,11 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     const bool duo_ok = M > 128 && N >= 64 && g_force_bn == 0 && g_force_splits <= 1 && st->sm_count >= 2;
     // measured: from 192 tokens on the two-CTA kernel is level with or ahead of the single-CTA one even when its
     // 256x256 tiles fill only part of the GPU (8192 x 8192 at 256 tokens: 18.6 against 20.7 us)
-    const bool duo = duo_ok && (g_pair_mode >= 1 ||
-                                (g_pair_mode == -1 && (M >= 192 || duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5)));
+    // the quantizing epilogues exist in the two-CTA kernel only (any batch size: rows past M are zero-filled tiles)
+    if (epi != 0 && st->sm_count < 2) return TFP4_ERR_NO_PLAN;
+    const bool duo = epi != 0 || (duo_ok && (g_pair_mode >= 1 ||
+                                (g_pair_mode == -1 && (M >= 192 || duo_tiles * 8 >= (int64_t)(st->sm_count / 2) * 5))));
+    if (duo) bn = 256;
     const uint32_t box_a = duo ? 128u : (uint32_t)bn;
     PlanKey key{packedA, packedB, M, N, K, kind, duo ? 1256 : bn, dev};
     auto it = g_plans.find(key);
@@ -1183,6 +1208,8 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.sfW = static_cast<const uint8_t*>(sblkB);
     p.sfA = static_cast<const uint8_t*>(sblkA);
     p.out = out;
+    p.out2 = es ? es->out2 : nullptr;
+    p.epi_act = es ? es->act : 0;
     p.bias = bias;
     p.alpha = alpha;
     p.M = M; p.N = N; p.K = K;
@@ -1280,7 +1307,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.status = ext ? ext->status : st->status_dev;
     p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
-    if (duo) return launch_duo(st, pl, p, kind, dev, stream);
+    if (duo) return launch_duo(st, pl, p, kind, epi, dev, stream);
 #define TFP4_GO(KINDV)                                                          \
     switch (bn) {                                                               \
         case 32: return launch<KINDV, 32>(st, pl, p, 0, stream);                \
@@ -1298,6 +1325,47 @@ int gemm_block_scaled(int kind, const void* packedA, const void* sblkA, const vo
                       int64_t K, int out_dtype, cudaStream_t stream) {
     return gemm_block_scaled_ws(kind, packedA, sblkA, packedB, sblkB, alpha, bias, out, M, N, K, out_dtype, stream,
                                 nullptr);
+}
+
+// Gate/up GEMM of a SwiGLU block with the activation, the product and the NVFP4 quantization of the hidden tensor in the
+// epilogue.  packedB / sblkB: the stacked weight [2I, K] whose rows alternate in blocks of 16 (gate rows j..j+15, up
+// rows j..j+15, ...), N = 2I.  h_packed / h_sblk: codes [pad128(M), I/2] and UE4M3 scale tiles of
+// h = silu(alpha * x Wg^T) * (alpha * x Wu^T), quantized with per-tensor scale 1; rows M..pad128(M) are written as zeros.
+int gemm_swiglu_nvfp4(const void* packedA, const void* sblkA, const void* packedB, const void* sblkB, float alpha,
+                      void* h_packed, void* h_sblk, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    if (N <= 0 || (N % 128) != 0) {
+        fprintf(stderr, "thor_fp4: the SwiGLU epilogue needs 2 * intermediate %% 128 == 0 (got N=%ld)\n", (long)N);
+        return TFP4_ERR_BAD_M;
+    }
+    if (!h_sblk || (reinterpret_cast<uintptr_t>(h_sblk) & 15)) {
+        fprintf(stderr, "thor_fp4: the SwiGLU epilogue needs a 16-byte aligned scale buffer\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    EpilogueSpec es;
+    es.epi = 1;
+    es.out2 = h_sblk;
+    return gemm_block_scaled_ws(0, packedA, sblkA, packedB, sblkB, alpha, nullptr, h_packed, M, N, K, OUT_BF16, stream,
+                                nullptr, &es);
+}
+
+// MXFP8 x MXFP4 GEMM whose epilogue adds bias[n], applies the activation (0 identity, 1 gelu, 2 silu) and re-quantizes
+// to MXFP8: D = e4m3 codes [M, N] (one byte each, rows past M untouched), SFD = UE8M0 scale tiles (power of two at or
+// above amax / 448 per 32 features).  N % 32 == 0, K % 128 == 0.
+int gemm_mx8_out(const void* packedA, const void* sblkA, const void* packedB, const void* sblkB, float alpha,
+                 const float* bias, int act, void* D, void* SFD, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    if (!SFD || (reinterpret_cast<uintptr_t>(SFD) & 15) || act < 0 || act > 2 || (bias && (reinterpret_cast<uintptr_t>(bias) & 15))) {
+        fprintf(stderr, "thor_fp4: the MXFP8 epilogue needs 16-byte aligned scale and bias buffers and act in 0..2\n");
+        return TFP4_ERR_BAD_ARG;
+    }
+    if (N <= 0 || (N % 32) != 0) {
+        fprintf(stderr, "thor_fp4: the MXFP8 epilogue needs N %% 32 == 0 (got %ld)\n", (long)N);
+        return TFP4_ERR_NO_PLAN;
+    }
+    EpilogueSpec es;
+    es.epi = 2;
+    es.out2 = SFD;
+    es.act = act;
+    return gemm_block_scaled_ws(1, packedA, sblkA, packedB, sblkB, alpha, bias, D, M, N, K, OUT_BF16, stream, nullptr, &es);
 }
 
 // ---------------------------------------------------------------------------------------------

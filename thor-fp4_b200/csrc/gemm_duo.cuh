@@ -317,10 +317,86 @@ __device__ __forceinline__ uint32_t duo_kblock_mx(uint32_t on, uint32_t accumula
     return ready;
 }
 
+template <int V> struct IntTag { static constexpr int value = V; };
+
+// One 32-column chunk of the SwiGLU epilogue: columns 0-15 are gate features j..j+15, columns 16-31 the matching up
+// features.  h = silu(alpha * gate) * (alpha * up) in FP32 (reproducible silu, det_math.cuh), then the activation
+// quantizer's block arithmetic with per-tensor scale 1: sc = ue4m3(amax * (1/6)), codes = e2m1_ties_up(h / dec(sc))
+// through the bracketed reciprocal path of quant_block.cuh.  lo / hi: the codes of h[0..7] / h[8..15].
+__device__ __forceinline__ void swiglu_block16(const uint32_t (&v)[32], float alpha, uint32_t& lo, uint32_t& hi, uint32_t& sc) {
+    float h0[8], h1[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        h0[i] = __fmul_rn(det_silu(__fmul_rn(alpha, __uint_as_float(v[i]))), __fmul_rn(alpha, __uint_as_float(v[16 + i])));
+        h1[i] = __fmul_rn(det_silu(__fmul_rn(alpha, __uint_as_float(v[8 + i]))), __fmul_rn(alpha, __uint_as_float(v[24 + i])));
+        amax = fmaxf(amax, fmaxf(fabsf(h0[i]), fabsf(h1[i])));
+    }
+    sc = f32x2_to_e4m3x2(__fmul_rn(amax, 1.0f / 6.0f), 0.f) & 0x7fu;
+    const float ds = e4m3_to_f32(sc);
+    lo = block_codes8<1>(h0, ds);
+    hi = block_codes8<1>(h1, ds);
+}
+
+// One 32-column chunk of the MXFP8 epilogue = one MX block: y = act(alpha * acc + bias[n]) (act 0 identity, 1 gelu,
+// 2 silu; reproducible forms), block scale byte = the power of two at or above amax * (1/448), codes = e4m3(y / 2^e)
+// (an exact scaling).  bias: this chunk's 32 floats or null.  w: 32 code bytes.
+__device__ __forceinline__ void act_mx8_block32(const uint32_t (&v)[32], float alpha, const float* bias, int act,
+                                                uint32_t (&w)[8], uint32_t& scb) {
+    float y[32];
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias != nullptr) b = __ldg(reinterpret_cast<const float4*>(bias + i));
+        const float bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float t = __fmul_rn(alpha, __uint_as_float(v[i + j]));
+            if (bias != nullptr) t = __fadd_rn(t, bb[j]);
+            y[i + j] = t;
+        }
+    }
+    if (act == 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = det_gelu(y[i]);
+    } else if (act == 2) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = det_silu(y[i]);
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(y[i]));
+    // power of two at or above amax / 448 (csrc/thor_fp4_core.cu:612-619 of the reference project)
+    const float a = __fmul_rn(amax, 1.0f / 448.0f);
+    uint32_t sb = 0u;
+    if (a > 0.f) {
+        const uint32_t u = __float_as_uint(a);
+        if ((u >> 23) == 0u) sb = (u > 0x00400000u) ? 1u : 0u;
+        else sb = (u >> 23) + ((u & 0x007fffffu) ? 1u : 0u);
+        if (sb > 254u) sb = 254u;
+    }
+    scb = sb;
+    const int e = 127 - (int)sb;
+    const float inv = e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(0x00400000u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        w[i] = f32x4_to_e4m3x4(__fmul_rn(y[4 * i], inv), __fmul_rn(y[4 * i + 1], inv), __fmul_rn(y[4 * i + 2], inv),
+                               __fmul_rn(y[4 * i + 3], inv));
+}
+
 // KIND 0: NVFP4 x NVFP4 (256 elements of K per K block, four scale atoms per 128 rows and K block);
 // KIND 1: MXFP8 tokens x MXFP4 weights (128 elements per K block, one atom; the 4-bit weights are expanded by TMA
 // to one byte per code in shared memory, and that copy credits its packed size to the barrier).
-template <int KIND, bool DBG>
+//
+// EPI selects what the epilogue makes of the FP32 accumulator (a thread holds 32 consecutive features of one token):
+//   0  out = cast(alpha * acc + bias) through shared memory and TMA stores;
+//   1  SwiGLU + NVFP4: the weight rows alternate in blocks of 16 (16 gate features, the 16 matching up features), so a
+//      32-column chunk is one 16-element quantization block of h = silu(alpha * gate) * (alpha * up); the thread
+//      quantizes it with the activation quantizer's arithmetic (per-tensor scale 1) and stores the e2m1 codes and
+//      UE4M3 scale bytes straight into the A-operand buffers of the next GEMM - no [M, 2I] tensor reaches memory;
+//   2  bias + activation + MXFP8: a 32-column chunk is one MX block of act(alpha * acc + bias[n]); e4m3 codes and
+//      UE8M0 scale bytes (power of two at or above amax / 448) go to the next layer's A-operand buffers.
+template <int KIND, bool DBG, int EPI>
 __global__ void __launch_bounds__(DUO_THREADS, 1)
 gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                 const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
@@ -522,54 +598,124 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const bool out16 = p.out_dtype != OUT_F32, bf16 = p.out_dtype == OUT_BF16;
         const int esize = out16 ? 2 : 4;
         const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)(half * 4 + q) * C::EPI_BUF;
-        for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
-            const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
-            if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
-            tc_fence_after();
-            const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
-            const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
-            // One 32-column chunk: alpha, bias, cast, swizzled shared memory, TMA store.
-            auto emit = [&](const uint32_t (&v)[32], int c) {
-                const int64_t nn = n0 + c;
-                // 16-bit outputs alternate between two 2 KB blocks; f32 outputs have one 4 KB block
-                const uint32_t buf = my_buf + (out16 ? (nstore & 1u) * (C::EPI_BUF / 2) : 0u);
-                if (lane == 0) {
-                    if (out16) bulk_wait_read_1();       // the store issued from this block two chunks ago has read it
-                    else bulk_wait_read_0();
-                }
+        if constexpr (EPI == 0) {
+            for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
+                const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+                if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
+                tc_fence_after();
+                const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
+                const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
+                // One 32-column chunk: alpha, bias, cast, swizzled shared memory, TMA store.
+                auto emit = [&](const uint32_t (&v)[32], int c) {
+                    const int64_t nn = n0 + c;
+                    // 16-bit outputs alternate between two 2 KB blocks; f32 outputs have one 4 KB block
+                    const uint32_t buf = my_buf + (out16 ? (nstore & 1u) * (C::EPI_BUF / 2) : 0u);
+                    if (lane == 0) {
+                        if (out16) bulk_wait_read_1();       // the store issued from this block two chunks ago has read it
+                        else bulk_wait_read_0();
+                    }
+                    __syncwarp();
+                    float f[32];
+                    duo_scale(v, f, nn, p.N, p.alpha, p.bias);
+                    if (out16) duo_put16_64(f, buf, lane, bf16);
+                    else duo_put32(f, buf + (uint32_t)lane * 128u, lane);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
+                        // lies outside altogether still closes an (empty) group, so that the group counts above hold
+                        if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
+                        bulk_commit_group();
+                    }
+                    ++nstore;
+                };
+                // The warp's 128 columns are four chunks.  Two are read at once; the third is read while the second is
+                // emitted and the fourth right after, so the accumulator goes back to the MMA issuer after two chunks'
+                // worth of arithmetic instead of three.
+                uint32_t va[32], vb[32];
+                tc_ld32(t_lane, va);
+                tc_ld32(t_lane + 32u, vb);
+                tc_wait_ld();
+                emit(va, 0);
+                tc_ld32(t_lane + 64u, va);
+                emit(vb, 32);
+                tc_wait_ld();
+                tc_ld32(t_lane + 96u, vb);
+                tc_wait_ld();
+                tc_fence_before();
                 __syncwarp();
-                float f[32];
-                duo_scale(v, f, nn, p.N, p.alpha, p.bias);
-                if (out16) duo_put16_64(f, buf, lane, bf16);
-                else duo_put32(f, buf + (uint32_t)lane * 128u, lane);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);      // this warp's columns are all in registers
+                emit(va, 64);
+                emit(vb, 96);
+            }
+        } else {
+            // quantizing epilogues: nothing goes through shared memory; every thread owns one token row
+            uint8_t* const q_codes = reinterpret_cast<uint8_t*>(p.out);
+            uint8_t* const q_scales = reinterpret_cast<uint8_t*>(p.out2);
+            const int64_t Mpad = pad128(p.M);
+            // EPI 1: h has N/2 features, N/4 code bytes and N/32 scale columns per row; EPI 2: N code bytes, N/32 scale columns
+            const int64_t code_ld = (EPI == 1) ? (p.N >> 2) : p.N;
+            const int64_t atoms_per_tile = ((p.N >> 5) + 3) >> 2;
+            for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
+                const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+                if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
+                tc_fence_after();
+                const int64_t row = mt * C::TILE_M + rank * 128 + q * 32 + lane;      // this thread's token
+                const int64_t n0 = nt * C::TILE_N + half * 128;                       // first of this warp's 128 columns
+                uint32_t cw[8];
+                uint32_t scw = 0;
+                auto emit = [&](const uint32_t (&v)[32], auto ci_tag) {
+                    constexpr int ci = decltype(ci_tag)::value;      // compile-time: cw[] stays in registers
+                    const int64_t nn = n0 + 32 * ci;
+                    if constexpr (EPI == 1) {
+                        uint32_t lo, hi, sc;
+                        swiglu_block16(v, p.alpha, lo, hi, sc);
+                        if (row >= p.M || nn >= p.N) { lo = hi = sc = 0u; }            // padding rows are written as zeros
+                        cw[2 * ci] = lo;
+                        cw[2 * ci + 1] = hi;
+                        scw |= sc << (8 * ci);
+                    } else {
+                        uint32_t w[8], sc = 0u;
+                        if (nn < p.N) {
+                            act_mx8_block32(v, p.alpha, p.bias != nullptr ? p.bias + nn : nullptr, p.epi_act, w, sc);
+                            if (row < p.M && !(dbg & 1)) {
+                                uint4* dst = reinterpret_cast<uint4*>(q_codes + row * code_ld + nn);
+                                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                            }
+                        }
+                        scw |= sc << (8 * ci);
+                    }
+                };
+                uint32_t va[32], vb[32];
+                tc_ld32(t_lane, va);
+                tc_ld32(t_lane + 32u, vb);
+                tc_wait_ld();
+                emit(va, IntTag<0>{});
+                tc_ld32(t_lane + 64u, va);
+                emit(vb, IntTag<1>{});
+                tc_wait_ld();
+                tc_ld32(t_lane + 96u, vb);
+                tc_wait_ld();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
-                    // lies outside altogether still closes an (empty) group, so that the group counts above hold
-                    if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
-                    bulk_commit_group();
+                if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);      // this warp's columns are all in registers
+                emit(va, IntTag<2>{});
+                emit(vb, IntTag<3>{});
+                if (n0 < p.N && !(dbg & 1)) {
+                    const int64_t atom = (row >> 7) * atoms_per_tile + (n0 >> 7);     // 128 columns = 4 scale columns = one atom
+                    if (EPI == 1) {
+                        if (row < Mpad) {
+                            uint4* dst = reinterpret_cast<uint4*>(q_codes + row * code_ld + (n0 >> 2));
+                            dst[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+                            dst[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
+                            *reinterpret_cast<uint32_t*>(q_scales + atom * 512 + 16 * lane + 4 * q) = scw;
+                        }
+                    } else if (row < p.M) {
+                        *reinterpret_cast<uint32_t*>(q_scales + atom * 512 + 16 * lane + 4 * q) = scw;
+                    }
                 }
-                ++nstore;
-            };
-            // The warp's 128 columns are four chunks.  Two are read at once; the third is read while the second is
-            // emitted and the fourth right after, so the accumulator goes back to the MMA issuer after two chunks'
-            // worth of arithmetic instead of three.
-            uint32_t va[32], vb[32];
-            tc_ld32(t_lane, va);
-            tc_ld32(t_lane + 32u, vb);
-            tc_wait_ld();
-            emit(va, 0);
-            tc_ld32(t_lane + 64u, va);
-            emit(vb, 32);
-            tc_wait_ld();
-            tc_ld32(t_lane + 96u, vb);
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);      // this warp's columns are all in registers
-            emit(va, 64);
-            emit(vb, 96);
+            }
         }
         if (lane == 0) bulk_wait_all();
     } else if (warp < 10) {

@@ -54,6 +54,13 @@ SIGNATURES = {
     "tfc4_variant_name": (ctypes.c_char_p, [c_int]),
     "tfc4_variant_index": (c_int, [ctypes.c_char_p]),
     "tfc4_gemm": (c_int, [c_int, c_void, c_void, c_void, c_void, c_void, i64, i64, i64, c_float, c_void]),
+    "tfc4_gemm_ex": (c_int, [c_int, c_void, c_void, c_void, c_void, c_void, c_void, i64, i64, i64, c_float, c_int, c_void]),
+    "tfc4f_n_variants": (c_int, []),
+    "tfc4f_variant_name": (ctypes.c_char_p, [c_int]),
+    "tfc4f_variant_index": (c_int, [ctypes.c_char_p]),
+    "tfc4f_sfd_bytes": (i64, [i64, i64]),
+    "tfc4f_gemm": (c_int, [c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void, i64, i64, i64, c_float, c_void]),
+    "tfp4_swiglu_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void, i64, i64, i64, c_void]),
     "tfp4_status": (c_int, []),
     "tfp4_clear_status": (None, []),
     "tfp4_plan_stats": (None, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
@@ -64,10 +71,6 @@ SIGNATURES = {
     "tfp4_set_debug": (None, [c_int]),
     "tfp4_set_quant_tile_rows": (None, [c_int]),
     "tfp4_debug_stats": (c_int, [ctypes.POINTER(ctypes.c_uint64), c_int]),
-}
-OPTIONAL_SIGNATURES = {
-    "tfp4_swiglu_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void,
-                                 i64, i64, i64, c_void]),
 }
 
 _lib = None
@@ -96,10 +99,6 @@ def core():
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(L, name)
             fn.restype, fn.argtypes = res, args
-        for name, (res, args) in OPTIONAL_SIGNATURES.items():
-            if hasattr(L, name):
-                fn = getattr(L, name)
-                fn.restype, fn.argtypes = res, args
         _lib = L
     return _lib
 
@@ -125,9 +124,9 @@ def cutlass():
 
 
 def fused():
-    """Library handle if the fused-epilogue entry points are present, else None."""
-    L = core()
-    return L if hasattr(L, "tfc4f_gemm") else None
+    """The reference keeps its fused-epilogue GEMMs (tfc4f_*) in a third, optional library; here they live in the
+    one library, so this never returns None."""
+    return core()
 
 
 def cublaslt_version() -> int:

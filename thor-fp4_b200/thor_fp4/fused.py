@@ -71,10 +71,16 @@ class FusedLinear(nn.Module):
             raise ValueError(f"out_features={out_features}: the SF store needs N % 32 == 0")
         if act not in _ACTS:
             raise ValueError(f"act={act!r}: pick 'gelu' | 'silu' | 'ident'")
-        self.variant = variant or resolve_mx8_variant(in_features)
-        self.variant_idx = _ext.cutlass().tfc4_variant_index(self.variant.encode())
+        L = _ext.fused()
+        if variant is None:      # the reference's default pick: the first registered variant of this activation
+            names = [bytes(L.tfc4f_variant_name(i)).decode() for i in range(L.tfc4f_n_variants())]
+            variant = next((n for n in names if n.startswith(f"mx8out_{act}_128x128x256")), names[0])
+        self.variant_idx = L.tfc4f_variant_index(variant.encode())
         if self.variant_idx < 0:
             raise ValueError(f"unknown fused variant {variant!r}")
+        self.variant = variant
+        # the plain GEMM variant of the unfused (checker) path
+        self._plain_idx = _ext.cutlass().tfc4_variant_index(resolve_mx8_variant(in_features).encode())
         self.act = act
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features, device=device))
@@ -86,7 +92,7 @@ class FusedLinear(nn.Module):
         self._w: ops.MXTensor | None = None
         self._bufs: dict = {}
         self.max_chunk = max_chunk
-        self.fuse_epilogue = True     # False: torch elementwise ops + separate quantizer (the checker's path)
+        self.fuse_epilogue = True     # False: GEMM, then bias + activation + quantizer as separate passes (the checker's path)
 
     def _apply(self, fn, recurse=True):
         self._w, self._bufs = None, {}
@@ -115,7 +121,6 @@ class FusedLinear(nn.Module):
                 bufs = {
                     "in": MX8Act(torch.zeros(ops.mx_packed_bytes(M, K, "mxfp8"), dtype=torch.uint8, device=dev),
                                  torch.zeros(ops.mx_scale_bytes(M, K), dtype=torch.uint8, device=dev), (M, K)),
-                    "acc": torch.empty(M, N, dtype=torch.bfloat16, device=dev),
                     "out": MX8Act(torch.zeros(ops.mx_packed_bytes(M, N, "mxfp8"), dtype=torch.uint8, device=dev),
                                   torch.zeros(ops.mx_scale_bytes(M, N), dtype=torch.uint8, device=dev), (M, N)),
                 }
@@ -123,25 +128,29 @@ class FusedLinear(nn.Module):
             if not isinstance(x, MX8Act):
                 act_in = bufs["in"]
                 ops.quantize_mx(xc, "mxfp8", act_in.packed, act_in.sblk)
-            acc, out = bufs["acc"], bufs["out"]
-            ops.gemm_mx(self.variant_idx, act_in.packed, act_in.sblk, self._w.packed, self._w.sblk,
-                        acc, M, N, K, 1.0)
+            out = bufs["out"]
             if self.fuse_epilogue:
-                # bias, activation and MXFP8 re-quantization in one pass over the GEMM output
-                b = self.bias.detach().float().contiguous() if self.bias is not None else None
-                rc = _ext.device_lib().tfp4_act_quant_mx8(
-                    acc.data_ptr(), b.data_ptr() if b is not None else None, M, N, _ext.IN_DTYPE[acc.dtype],
-                    _ACT_CODE[self.act], out.packed.data_ptr(), out.sblk.data_ptr(), _ext.stream())
-                assert rc == 0, f"tfp4_act_quant_mx8 rc={rc}"
+                # bias, activation and MXFP8 re-quantization in the GEMM's epilogue: one kernel, no (M, N) tensor
+                b = self.bias.detach().float().contiguous() if self.bias is not None else self._zero_bias(dev)
+                ops.gemm_mx8_out(self.variant_idx, act_in.packed, act_in.sblk, self._w.packed, self._w.sblk, b,
+                                 out.packed, out.sblk, M, N, K, 1.0)
                 return out
-            y = acc.float()
-            if self.bias is not None:
-                y = y + self.bias.float()
-            y = _ACTS[self.act](y).contiguous()
-            rc = _ext.device_lib().tfp4_act_quant_mx8(y.data_ptr(), None, M, N, _ext.IN_DTYPE[y.dtype], 0,
-                                                      out.packed.data_ptr(), out.sblk.data_ptr(), _ext.stream())
+            acc = bufs.get("acc")
+            if acc is None:
+                acc = bufs["acc"] = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            ops.gemm_mx(self._plain_idx, act_in.packed, act_in.sblk, self._w.packed, self._w.sblk, acc, M, N, K, 1.0)
+            b = self.bias.detach().float().contiguous() if self.bias is not None else None
+            rc = _ext.device_lib().tfp4_act_quant_mx8(
+                acc.data_ptr(), b.data_ptr() if b is not None else None, M, N, _ext.IN_DTYPE[acc.dtype],
+                _ACT_CODE[self.act], out.packed.data_ptr(), out.sblk.data_ptr(), _ext.stream())
             assert rc == 0, f"tfp4_act_quant_mx8 rc={rc}"
             return out
+
+    def _zero_bias(self, dev):
+        z = self._bufs.get("zero_bias")
+        if z is None:
+            z = self._bufs["zero_bias"] = torch.zeros(self.out_features, dtype=torch.float32, device=dev)
+        return z
 
     def extra_repr(self) -> str:
         return (f"in={self.in_features}, out={self.out_features}, bias={self.bias is not None}, "
@@ -190,10 +199,15 @@ def mx8_chain(*dims: int, variant: str | None = None, device=None) -> nn.Sequent
 class NVFP4GatedMLP(nn.Module):
     """NVFP4 SwiGLU block: y = down( nvfp4( silu(x Wg^T) * (x Wu^T) ) ), no biases.
 
-    x is quantized once; gate and up run as one GEMM over the stacked weight
-    [Wg; Wu]; h is re-quantized with act_tensor_scale 1 (dynamic block scales only,
-    so shards of the intermediate dimension quantize independently).  Buffers are
-    cached per batch size; the warmed block is capturable."""
+    x is quantized once; gate and up run as ONE GEMM over the stacked weight whose epilogue computes
+    silu(gate) * up in FP32 and quantizes h to NVFP4 straight into the down projection's operand
+    buffers (tfp4_swiglu_gemm: no (M, 2I) tensor is written).  h is quantized with act_tensor_scale 1
+    (dynamic block scales only, so shards of the intermediate dimension quantize independently).
+    Buffers are cached per batch size; the warmed block is capturable.
+
+    fuse_epilogue = False selects the three-kernel form (gate/up GEMM to bf16, one-pass silu*up +
+    quantize kernel, down GEMM; with fuse_activation = False the middle step is torch elementwise ops
+    + the plain quantizer): the path the tests check the fused one against."""
 
     def __init__(self, hidden: int, intermediate: int, device=None, out_dtype: str = "bf16",
                  weight_std: float | None = None):
@@ -210,8 +224,10 @@ class NVFP4GatedMLP(nn.Module):
             else:
                 nn.init.normal_(w, std=weight_std)
         self.tensor_scales: tuple | None = None   # optional (ts_gate_up, ts_down) override
-        self.fuse_activation = True               # False: torch elementwise + separate quantizer (the checker's path)
+        self.fuse_epilogue = True                 # False: separate kernels between the GEMMs (the checker's path)
+        self.fuse_activation = True               # unfused path only: False = torch elementwise + plain quantizer
         self._q = None
+        self._q_layout = None
         self._bufs: dict = {}
 
     def _apply(self, fn, recurse=True):
@@ -219,15 +235,19 @@ class NVFP4GatedMLP(nn.Module):
         return super()._apply(fn, recurse)
 
     def refresh_weight(self):
-        wgu = torch.cat([self.w_gate.detach().float(), self.w_up.detach().float()], dim=0).contiguous()
+        """Quantize the weights: the gate/up stack in the row order of the selected path (blocks of 16 alternating
+        for the fused epilogue, gate half then up half otherwise); the per-tensor scale covers the whole stack."""
+        wg, wu = self.w_gate.detach().float(), self.w_up.detach().float()
+        wgu = ops.interleave16(wg, wu) if self.fuse_epilogue else torch.cat([wg, wu], dim=0).contiguous()
         ts = self.tensor_scales or (None, None)
         self._q = (NVFP4Tensor.from_float(wgu, ts[0]),
                    NVFP4Tensor.from_float(self.w_down.detach().float().contiguous(), ts[1]))
+        self._q_layout = self.fuse_epilogue
         return self
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         with torch.no_grad():
-            if self._q is None:
+            if self._q is None or self._q_layout != self.fuse_epilogue:
                 self.refresh_weight()
             wgu, wd = self._q
             H, I = self.hidden, self.intermediate
@@ -244,20 +264,25 @@ class NVFP4GatedMLP(nn.Module):
                 b = {
                     "xp": torch.zeros(ops.packed_bytes(M, H), dtype=torch.uint8, device=dev),
                     "xs": torch.zeros(ops.scale_bytes(M, H), dtype=torch.uint8, device=dev),
-                    "gu": torch.empty(M, 2 * I, dtype=torch.bfloat16, device=dev),
                     "hp": torch.zeros(ops.packed_bytes(M, I), dtype=torch.uint8, device=dev),
                     "hs": torch.zeros(ops.scale_bytes(M, I), dtype=torch.uint8, device=dev),
                     "y": torch.empty(M, H, dtype=_ext.OUT_TORCH[self.out_dtype], device=dev),
                 }
                 self._bufs[key] = b
             ops.quantize_nvfp4(x, 1.0, b["xp"], b["xs"])
-            ops.gemm(b["xp"], b["xs"], 1.0, wgu.packed, wgu.sblk, wgu.tensor_scale, b["gu"], M, 2 * I, H, "bf16")
-            if self.fuse_activation:
-                # silu(gate) * up and the re-quantization of h in one pass over the GEMM output
-                ops.swiglu_quantize_nvfp4(b["gu"], b["hp"], b["hs"])
+            if self.fuse_epilogue:
+                ops.swiglu_gemm(b["xp"], b["xs"], 1.0, wgu, M, b["hp"], b["hs"])
             else:
-                h = (F.silu(b["gu"][:, :I].float()) * b["gu"][:, I:].float()).to(torch.bfloat16)
-                ops.quantize_nvfp4(h, 1.0, b["hp"], b["hs"])
+                gu = b.get("gu")
+                if gu is None:
+                    gu = b["gu"] = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=x.device)
+                ops.gemm(b["xp"], b["xs"], 1.0, wgu.packed, wgu.sblk, wgu.tensor_scale, gu, M, 2 * I, H, "bf16")
+                if self.fuse_activation:
+                    # silu(gate) * up and the re-quantization of h in one pass over the GEMM output
+                    ops.swiglu_quantize_nvfp4(gu, b["hp"], b["hs"])
+                else:
+                    h = (F.silu(gu[:, :I].float()) * gu[:, I:].float()).to(torch.bfloat16)
+                    ops.quantize_nvfp4(h, 1.0, b["hp"], b["hs"])
             y = out if out is not None else b["y"]
             ops.gemm(b["hp"], b["hs"], 1.0, wd.packed, wd.sblk, wd.tensor_scale, y, M, H, I, self.out_dtype)
             return y

@@ -16,7 +16,7 @@ from . import _ext
 __all__ = [
     "pad_rows", "packed_bytes", "scale_bytes", "mx_packed_bytes", "mx_scale_bytes",
     "quantize_nvfp4", "fake_quantize_nvfp4", "quantize_mx", "mx8_mul", "dequantize_nvfp4", "block_scales",
-    "gemm", "gemm_mx", "gemv", "NVFP4Tensor", "MXTensor",
+    "gemm", "gemm_mx", "gemv", "NVFP4Tensor", "MXTensor", "interleave16", "swiglu_gemm", "gemm_mx8_out",
 ]
 
 
@@ -80,6 +80,46 @@ def swiglu_quantize_nvfp4(gu: torch.Tensor, packed: torch.Tensor | None = None,
                              _ext.stream())
     assert rc == 0, f"tfp4_swiglu_quant rc={rc}"
     return packed, sblk
+
+
+def interleave16(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """Stack two (I, K) weights as (2I, K) with rows alternating in blocks of 16: gate rows j..j+15, up rows j..j+15,
+    gate rows j+16.., ...  This is the row order swiglu_gemm wants: a 32-column chunk of the gate/up GEMM's output then
+    holds one 16-element quantization block of gate values and the matching block of up values."""
+    I, K = w_gate.shape
+    assert w_up.shape == (I, K) and I % 16 == 0, "intermediate size must be a multiple of 16"
+    return torch.stack([w_gate.reshape(I // 16, 16, K), w_up.reshape(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def swiglu_gemm(packedA: torch.Tensor, sblkA: torch.Tensor, tsA: float, w: "NVFP4Tensor", M: int,
+                h_packed: torch.Tensor | None = None, h_sblk: torch.Tensor | None = None):
+    """Gate/up GEMM with silu(gate) * up and the NVFP4 quantization of h in its epilogue (tfp4_swiglu_gemm).
+    w: the NVFP4 stack interleave16(Wg, Wu) of shape (2I, K).  Returns (codes, scale tiles) of h (M, I), quantized with
+    per-tensor scale 1: the A operand of the down projection.  No (M, 2I) tensor is written."""
+    L = _ext.device_lib()
+    N, K = w.shape
+    I = N // 2
+    assert N % 128 == 0, f"intermediate size {I} must be a multiple of 64"
+    if h_packed is None:
+        h_packed = torch.zeros(packed_bytes(M, I), dtype=torch.uint8, device=packedA.device)
+    if h_sblk is None:
+        h_sblk = torch.zeros(scale_bytes(M, I), dtype=torch.uint8, device=packedA.device)
+    rc = L.tfp4_swiglu_gemm(packedA.data_ptr(), sblkA.data_ptr(), float(tsA), w.packed.data_ptr(), w.sblk.data_ptr(),
+                            float(w.tensor_scale), h_packed.data_ptr(), h_sblk.data_ptr(), M, N, K, _ext.stream())
+    assert rc == 0, f"tfp4_swiglu_gemm rc={rc}"
+    return h_packed, h_sblk
+
+
+def gemm_mx8_out(variant: int, packedA: torch.Tensor, sblkA: torch.Tensor, packedB: torch.Tensor, sblkB: torch.Tensor,
+                 bias: torch.Tensor, d_packed: torch.Tensor, d_sblk: torch.Tensor, M: int, N: int, K: int,
+                 alpha: float = 1.0) -> None:
+    """tfc4f_gemm: MXFP8 (M, K) x MXFP4 (N, K) with bias[n], the variant's activation and the MXFP8 re-quantization of
+    the output in the epilogue; d_packed (>= M*N bytes) and d_sblk (tfc4f_sfd_bytes) receive codes and scale tiles."""
+    L = _ext.device_lib()
+    assert bias.dtype == torch.float32 and bias.numel() == N and bias.is_contiguous()
+    rc = L.tfc4f_gemm(variant, packedA.data_ptr(), sblkA.data_ptr(), packedB.data_ptr(), sblkB.data_ptr(), bias.data_ptr(),
+                      d_packed.data_ptr(), d_sblk.data_ptr(), M, N, K, float(alpha), _ext.stream())
+    assert rc == 0, f"tfc4f_gemm rc={rc}"
 
 
 _FQ_OUT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}

@@ -80,6 +80,9 @@ class TensorParallelGatedMLP(nn.Module):
         m._q = None
         return self
 
+    def exchange_name(self) -> str:
+        return f"NCCL all-reduce of the partial outputs, {self.chunks} token chunks overlapped with the next chunk's GEMMs"
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return self.local(x)
