@@ -564,10 +564,10 @@ def measure_mlp_block(args, dev, rank, world, steps):
     tp.local.refresh_weight()
     err = None
     if rank == 0:
-        full = NVFP4GatedMLP(H, I, device=dev, out_dtype="f32", weight_std=0.02)
+        full = NVFP4GatedMLP(H, I, device=dev, out_dtype="f32" if world > 1 else "bf16", weight_std=0.02)
         with torch.no_grad():
             full.w_gate.copy_(wg); full.w_up.copy_(wu); full.w_down.copy_(wd)
-        ref = full(xs[0][:1024]).clone()
+        ref = full(xs[0][:1024]).float().clone()
         del full
     del wg, wu, wd
     torch.cuda.empty_cache()
@@ -599,9 +599,26 @@ def measure_mlp_block(args, dev, rank, world, steps):
     ms = timed(lambda i: tp(xs[i % 2]), steps)
     ms_local = timed(lambda i: tp.local(xs[i % 2]), steps)          # the rank's GEMMs alone, nothing exchanged
     ms_xchg = None
+    scatter = None
     if world > 1:
         buf = torch.zeros(M, H, dtype=torch.float32 if reduce_dtype == "f32" else torch.bfloat16, device=dev)
         ms_xchg = timed(lambda i: dist.all_reduce(buf), steps)          # the exchange alone (NCCL all-reduce of the partials)
+        del buf
+        # the same block with the partial outputs reduce-scattered by token rows (each rank keeps M/P summed rows)
+        name_ar = tp.exchange_name()
+        tp.exchange = "reduce_scatter"
+        ys = tp(xs[0])
+        torch.cuda.synchronize()
+        err_rs = None
+        if rank == 0:
+            rows = tp.owned_rows(M)
+            rows = rows[rows < 1024].to(dev)
+            err_rs = float((ys[: rows.numel()].float() - ref[rows]).norm() / ref[rows].norm()) if rows.numel() else None
+        ms_rs = timed(lambda i: tp(xs[i % 2]), steps)
+        scatter = {"exchange": tp.exchange_name(), "ms_per_block": ms_rs, "tflops": 6.0 * M * H * I / (ms_rs * 1e-3) / 1e12,
+                   "rel_error_vs_unsharded_block": err_rs,
+                   "note": "every rank ends with its M/P token rows of the output, fully summed"}
+        tp.exchange = "all_reduce"
     if _ext.status() != 0:
         raise RuntimeError(f"device status word {_ext.status()}")
     flop = 6.0 * M * H * I
@@ -609,10 +626,11 @@ def measure_mlp_block(args, dev, rank, world, steps):
                        f"rows and down columns split over {world} rank(s)",
            "tensor_parallel": world, "scaling": "strong", "steps": steps, "ms_per_block": ms,
            "tflops": flop / (ms * 1e-3) / 1e12, "ms_local_gemms_only": ms_local,
-           "exchange": tp.exchange_name() if world > 1 else None, "reduce_dtype": reduce_dtype if world > 1 else None,
+           "exchange": name_ar if world > 1 else None, "reduce_dtype": reduce_dtype if world > 1 else None,
            "ms_exchange_alone": ms_xchg,
            "exchange_share": (None if world == 1 else max(0.0, 1.0 - ms_local / ms)),
            "rel_error_vs_unsharded_block": err,
+           "reduce_scatter": scatter,
            "fused_epilogue": bool(getattr(tp.local, "fuse_epilogue", False))}
     del tp, xs
     torch.cuda.empty_cache()

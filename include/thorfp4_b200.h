@@ -208,6 +208,10 @@ void tfp4_set_dependent_launch(int on);
  * -1 automatic with every tile cut alike, 1 never, n = about n K ranges for every tile (test hook). */
 void tfp4_set_splits(int n);
 void tfp4_set_debug(int bits);
+/* tile order of the two-CTA kernel: 0 = automatic (bands of token tiles sized to stay resident in L2 while the weights
+ * stream, once the activation no longer fits), -1 = token tiles fastest, gm > 0 = bands of gm token tiles with the
+ * feature tiles fastest inside a band (A/B timing) */
+void tfp4_set_raster(int gm);
 /* test hook: force the NVFP4 quantizer's tile height (64 or 128 rows; 0 = automatic) */
 void tfp4_set_quant_tile_rows(int rows);
 int tfp4_debug_stats(unsigned long long* out, int n_ctas);

@@ -193,6 +193,13 @@ full.tensor_scales = full_tensor_scales(wg, wu, wd)
 ref = full(x)
 err = ((y - ref).norm() / ref.norm()).item()
 assert err < 1e-5, err
+# the same block with the partial outputs reduce-scattered by token rows: each rank holds its rows, fully summed
+ts = TensorParallelGatedMLP(H, I, local=EmuMLP(H, I // world), exchange="reduce_scatter").load_full_weights(wg, wu, wd)
+ys = ts(x)
+rows = ts.owned_rows(M, on_device=False)
+assert ys.shape == (M // world, H) and rows.numel() == M // world
+assert ((ys - ref[rows]).norm() / ref[rows].norm()).item() < 1e-5
+assert torch.equal(ts.gather(ys, M), y)
 if rank == 0:
     print("TP_OK", err)
 dist.destroy_process_group()

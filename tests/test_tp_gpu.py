@@ -35,6 +35,17 @@ WORKER = textwrap.dedent('''
         ref = full(x).float()
         err = ((y - ref).norm() / ref.norm()).item()
         print("TP_ERR", err, "REPEAT_EQUAL", bool(torch.equal(y, y2)))
+    # the partial outputs reduce-scattered by token rows: each rank's rows equal the all-reduced ones
+    ts = TensorParallelGatedMLP(H, I, device="cuda", reduce_dtype="f32", chunks=3, exchange="reduce_scatter")
+    ts.load_full_weights(wg.cuda(), wu.cuda(), wd.cuda())
+    ys = ts(x).clone()
+    rows = ts.owned_rows(M).cuda()
+    same = bool(((ys - y[rows]).norm() / y[rows].norm()).item() < 1e-6)
+    back = ts.gather(ys, M)
+    ok = torch.tensor([int(same and ((back - y).norm() / y.norm()).item() < 1e-6)], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("RS_OK", int(ok.item()))
     dist.destroy_process_group()
 ''')
 
@@ -54,3 +65,4 @@ def test_tensor_parallel_mlp_two_gpus(tmp_path):
     # the sharded down projection sums two f32 partials instead of one accumulation: same codes, same products
     assert float(line[1]) < 1e-3
     assert line[3] == "True"
+    assert "RS_OK 1" in out.stdout

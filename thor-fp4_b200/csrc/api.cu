@@ -16,6 +16,7 @@ int gemm_block_scaled(int, const void*, const void*, const void*, const void*, f
                       int64_t, int64_t, int64_t, int, cudaStream_t);
 void gemm_set_token_tile(int);
 void gemm_set_debug(int);
+void gemm_set_raster(int);
 void gemm_set_pair_mode(int);
 void gemm_set_pdl(int);
 void quant_set_pdl(int);
@@ -213,6 +214,7 @@ void tfp4_clear_status(void) { tfp4::gemm_clear_status(); }
 void tfp4_plan_stats(uint64_t* hits, uint64_t* misses) { tfp4::gemm_plan_stats(hits, misses); }
 void tfp4_set_token_tile(int bn) { tfp4::gemm_set_token_tile(bn); }
 void tfp4_set_debug(int bits) { tfp4::gemm_set_debug(bits); }
+void tfp4_set_raster(int gm) { tfp4::gemm_set_raster(gm); }
 void tfp4_set_pair_mode(int mode) { tfp4::gemm_set_pair_mode(mode); }
 void tfp4_set_dependent_launch(int on) {
     tfp4::gemm_set_pdl(on);

@@ -60,6 +60,7 @@ struct GemmParams {
     void* out;
     void* out2;              // quantizing epilogues: the scale-tile buffer (out then holds the codes)
     int32_t epi_act;         // MXFP8 epilogue: 0 identity, 1 gelu, 2 silu
+    int32_t raster_gm;       // two-CTA kernel: tile order (see duo_tile_coords)
     const float* bias;       // may be null
     float alpha;
     int64_t M, N, K;
@@ -1118,6 +1119,7 @@ struct EpilogueSpec {
     int act = 0;
 };
 
+int g_raster_gm = 0;    // 0 automatic, -1 token tiles fastest, n > 0 bands of n token tiles
 int g_force_bn = 0;
 int g_force_splits = 0;    // 0 automatic, 1 never split K, n split into (about) n ranges
 int g_pair_mode = -1;   // -1: automatic (256x256 two-CTA kernel for batches above 128 tokens with enough tiles); 0: single-CTA
@@ -1210,6 +1212,20 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.out = out;
     p.out2 = es ? es->out2 : nullptr;
     p.epi_act = es ? es->act : 0;
+    // Tile order of the two-CTA kernel.  Each of the two dies keeps its own copy of what its SMs read in its half of
+    // the L2, so about 60 MB of operands stay resident per die.  With the token tiles fastest a wave of CTA pairs
+    // touches every token tile: fine while all of the activation codes fit, a re-fetch per wave when they do not
+    // (16384 x 8192 at K = 8192: 510 -> 469 us; the SwiGLU block's down projection, K = 28672: 2035 -> 1727 us).
+    // Bands of gm token tiles whose codes and scales take about 34 MB keep the band resident while the weights stream.
+    p.raster_gm = 0;
+    if (g_raster_gm > 0) {
+        p.raster_gm = g_raster_gm;
+    } else if (g_raster_gm == 0) {
+        const int64_t tile_bytes = 256 * (kind == 0 ? (K / 2 + K / 16) : (K + K / 32));
+        const int64_t tiles_m256 = (M + 255) / 256;
+        const int64_t gm = (int64_t)34000000 / tile_bytes;
+        if (gm < tiles_m256) p.raster_gm = (int32_t)(gm < 1 ? 1 : gm);
+    }
     p.bias = bias;
     p.alpha = alpha;
     p.M = M; p.N = N; p.K = K;
@@ -1449,6 +1465,7 @@ int gemm_warm() {
 }
 
 void gemm_set_debug(int d) { g_debug = d; }
+void gemm_set_raster(int gm) { g_raster_gm = gm; }
 void gemm_set_pair_mode(int m) { g_pair_mode = m; }
 void gemm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 

@@ -317,6 +317,23 @@ __device__ __forceinline__ uint32_t duo_kblock_mx(uint32_t on, uint32_t accumula
     return ready;
 }
 
+// Tile index -> (token tile mt, feature tile nt).  gm <= 0: token tiles fastest (a wave of CTA pairs shares few weight
+// tiles and spreads over many token tiles).  gm > 0: bands of gm token tiles, feature tiles fastest inside a band, so a
+// wave covers about gm x (pairs / gm) tiles and every operand tile in flight is shared by several pairs.
+__device__ __forceinline__ void duo_tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int gm, int64_t& mt, int64_t& nt) {
+    if (gm <= 0) {
+        nt = tile / tiles_m;
+        mt = tile - nt * tiles_m;
+    } else {
+        const int64_t band = (int64_t)gm * tiles_n;
+        const int64_t g = tile / band, r = tile - g * band;
+        const int64_t m0 = g * gm;
+        const int64_t rows = (tiles_m - m0 < gm) ? (tiles_m - m0) : gm;
+        nt = r / rows;
+        mt = m0 + (r - nt * rows);
+    }
+}
+
 template <int V> struct IntTag { static constexpr int value = V; };
 
 // One 32-column chunk of the SwiGLU epilogue: columns 0-15 are gate features j..j+15, columns 16-31 the matching up
@@ -480,7 +497,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const CUtensorMap* my_map = (lane == 0) ? &tmX : &tmW;
         const uint32_t my_dst = (lane == 0) ? smem_u32(sX) : smem_u32(sWh);
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
-            const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+            int64_t nt, mt;
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
             const int my_y = (lane == 0) ? (int)(mt * C::TILE_M + rank * 128) : (int)(nt * C::TILE_N + rank * 128);
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const uint32_t ph = (pmask >> s) & 1u;
@@ -600,7 +618,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)(half * 4 + q) * C::EPI_BUF;
         if constexpr (EPI == 0) {
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
-                const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+                int64_t nt, mt;
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
                 if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
                 tc_fence_after();
                 const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
@@ -657,7 +676,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const int64_t code_ld = (EPI == 1) ? (p.N >> 2) : p.N;
             const int64_t atoms_per_tile = ((p.N >> 5) + 3) >> 2;
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
-                const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+                int64_t nt, mt;
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
                 if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
                 tc_fence_after();
                 const int64_t row = mt * C::TILE_M + rank * 128 + q * 32 + lane;      // this thread's token
@@ -804,7 +824,8 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         bool ok = true;
         const uint32_t sf_base = smem_u32(sSF);
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
-            const int64_t nt = tile / tiles_m, mt = tile - nt * tiles_m;
+            int64_t nt, mt;
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
             const int64_t ta = 2 * mt + rank, tw = 2 * nt;
             const bool a_ok = ta < p.rows_a_tiles, w1_ok = tw + 1 < p.rows_w_tiles;
             const uint8_t* my_src = (lane == 0) ? p.sfA + ta * p.sf_tile_stride

@@ -69,6 +69,7 @@ SIGNATURES = {
     "tfp4_set_dependent_launch": (None, [c_int]),
     "tfp4_set_splits": (None, [c_int]),
     "tfp4_set_debug": (None, [c_int]),
+    "tfp4_set_raster": (None, [c_int]),
     "tfp4_set_quant_tile_rows": (None, [c_int]),
     "tfp4_debug_stats": (c_int, [ctypes.POINTER(ctypes.c_uint64), c_int]),
 }

@@ -48,19 +48,32 @@ def full_tensor_scales(w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.T
 
 
 class TensorParallelGatedMLP(nn.Module):
-    """y = all_reduce_sum_p( down_p( nvfp4( silu(x Wg_p^T) * (x Wu_p^T) ) ) ).
+    """y = sum_p( down_p( nvfp4( silu(x Wg_p^T) * (x Wu_p^T) ) ) ), the sum taken over the ranks.
 
     `local` computes the rank's partial product; by default it is an NVFP4GatedMLP on
     this rank's GPU (partials in `reduce_dtype`, f32 unless told otherwise, because
     rounding each partial to bf16 before the sum costs ~1.6e-3 relative error).
-    `group` defaults to the world group."""
+    `group` defaults to the world group.
+
+    exchange:
+      "all_reduce"      every rank ends with all M rows of y (what a replicated consumer wants); each rank moves
+                        2 (P-1)/P of the partial tensor;
+      "reduce_scatter"  every rank ends with M/P rows of y, fully summed - the tokens stay sharded for a consumer
+                        that works per token (residual add, norm, the next block's quantizer) and an all-gather is
+                        paid only where a replicated tensor is really needed; half the bytes of the all-reduce.
+                        forward() then returns the (M/P, hidden) rows `owned_rows(M)` of this rank.
+    The tokens are cut into `chunks` pieces: the exchange of one piece runs on the collective's own stream while
+    this rank's GEMMs of the next piece run."""
 
     def __init__(self, hidden: int, intermediate: int, group=None, device=None,
                  reduce_dtype: str = "f32", weight_std: float | None = 0.02, local: nn.Module | None = None,
-                 chunks: int = 4):
+                 chunks: int = 4, exchange: str = "all_reduce"):
         super().__init__()
+        if exchange not in ("all_reduce", "reduce_scatter"):
+            raise ValueError(f"exchange={exchange!r}: pick 'all_reduce' | 'reduce_scatter'")
         self.group = group
-        self.chunks = max(1, int(chunks))     # token chunks: the all-reduce of one overlaps the GEMMs of the next
+        self.exchange = exchange
+        self.chunks = max(1, int(chunks))     # token chunks: the exchange of one overlaps the GEMMs of the next
         self._y: dict = {}
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -81,34 +94,84 @@ class TensorParallelGatedMLP(nn.Module):
         return self
 
     def exchange_name(self) -> str:
-        return f"NCCL all-reduce of the partial outputs, {self.chunks} token chunks overlapped with the next chunk's GEMMs"
+        kind = "all-reduce" if self.exchange == "all_reduce" else "reduce-scatter by token rows"
+        return f"NCCL {kind} of the partial outputs, {self.chunks} token chunks overlapped with the next chunk's GEMMs"
+
+    # ------------------------------------------------------------------ token chunks
+    def _chunk_bounds(self, M: int, on_device: bool) -> list[tuple[int, int]]:
+        """Token chunks [r0, r1): multiples of 256 rows (whole GEMM tiles) whose sizes divide by the world size."""
+        n = self.chunks if (M >= 256 * self.chunks and on_device) else 1
+        step = -(-M // n)
+        step = -(-step // 256) * 256
+        if self.exchange == "reduce_scatter" and M % self.world != 0:
+            raise ValueError(f"reduce_scatter needs the token count ({M}) to divide by the world size ({self.world})")
+        return [(r0, min(M, r0 + step)) for r0 in range(0, M, step)]
+
+    def owned_rows(self, M: int, on_device: bool = True) -> torch.Tensor:
+        """Global token indices of the rows forward() returns on this rank under exchange='reduce_scatter'
+        (chunk by chunk, this rank's 1/P of each chunk)."""
+        idx = []
+        for r0, r1 in self._chunk_bounds(M, on_device):
+            n = (r1 - r0) // self.world
+            idx.append(torch.arange(r0 + self.rank * n, r0 + (self.rank + 1) * n))
+        return torch.cat(idx)
+
+    def gather(self, y_local: torch.Tensor, M: int) -> torch.Tensor:
+        """All-gather the reduce-scattered rows back into the replicated (M, hidden) tensor in token order."""
+        parts = [torch.empty_like(y_local) for _ in range(self.world)]
+        dist.all_gather(parts, y_local.contiguous(), group=self.group)
+        out = torch.empty(M, y_local.shape[1], dtype=y_local.dtype, device=y_local.device)
+        on_device = y_local.is_cuda
+        pos = 0
+        for r0, r1 in self._chunk_bounds(M, on_device):
+            n = (r1 - r0) // self.world
+            for p in range(self.world):
+                out[r0 + p * n: r0 + (p + 1) * n] = parts[p][pos: pos + n]
+            pos += n
+        return out
+
+    def _reduce_scatter(self, dst: torch.Tensor, src: torch.Tensor, async_op: bool):
+        if dist.get_backend(self.group) == "gloo":      # gloo has no reduce-scatter: same result through an all-reduce
+            dist.all_reduce(src, op=dist.ReduceOp.SUM, group=self.group)
+            n = src.shape[0] // self.world
+            dst.copy_(src[self.rank * n:(self.rank + 1) * n])
+            return None
+        return dist.reduce_scatter_tensor(dst, src, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return self.local(x)
         M = x.shape[0]
-        n = self.chunks if (M >= 256 * self.chunks and x.is_cuda) else 1
-        if n == 1:
+        bounds = self._chunk_bounds(M, x.is_cuda)
+        scatter = self.exchange == "reduce_scatter"
+        if len(bounds) == 1 and not scatter:
             y = self.local(x)
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
             return y
-        # The partial outputs are summed chunk by chunk: NCCL runs on its own stream, ordered after
+        # The partial outputs are exchanged chunk by chunk: NCCL runs on its own stream, ordered after
         # the chunk's GEMMs, while this stream goes on with the next chunk.
-        step = -(-M // n)
-        step = -(-step // 256) * 256
-        first = self.local(x[:step])
-        y = self._y.get((M, first.dtype))
-        if y is None:
+        r0, r1 = bounds[0]
+        first = self.local(x[r0:r1])
+        key = (M, first.dtype, scatter)
+        bufs = self._y.get(key)
+        if bufs is None:
             y = torch.empty(M, first.shape[1], dtype=first.dtype, device=first.device)
-            self._y[(M, first.dtype)] = y
-        works = []
-        for r0 in range(0, M, step):
-            r1 = min(M, r0 + step)
-            if r0 == 0:
-                y[:r1].copy_(first)
+            ys = torch.empty(M // self.world, first.shape[1], dtype=first.dtype, device=first.device) if scatter else None
+            bufs = self._y[key] = (y, ys)
+        y, ys = bufs
+        works, pos = [], 0
+        for i, (r0, r1) in enumerate(bounds):
+            if i == 0:
+                y[r0:r1].copy_(first)
             else:
-                self.local(x[r0:r1], out=y[r0:r1])
-            works.append(dist.all_reduce(y[r0:r1], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                self.local(x[r0:r1], out=y[r0:r1]) if x.is_cuda else y[r0:r1].copy_(self.local(x[r0:r1]))
+            if scatter:
+                n = (r1 - r0) // self.world
+                works.append(self._reduce_scatter(ys[pos:pos + n], y[r0:r1], async_op=True))
+                pos += n
+            else:
+                works.append(dist.all_reduce(y[r0:r1], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
         for w in works:
-            w.wait()
-        return y
+            if w is not None:
+                w.wait()
+        return ys if scatter else y
