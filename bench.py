@@ -599,7 +599,7 @@ def measure_mlp_block(args, dev, rank, world, steps):
     ms = timed(lambda i: tp(xs[i % 2]), steps)
     ms_local = timed(lambda i: tp.local(xs[i % 2]), steps)          # the rank's GEMMs alone, nothing exchanged
     ms_xchg = None
-    scatter = None
+    scatter = push = None
     if world > 1:
         buf = torch.zeros(M, H, dtype=torch.float32 if reduce_dtype == "f32" else torch.bfloat16, device=dev)
         ms_xchg = timed(lambda i: dist.all_reduce(buf), steps)          # the exchange alone (NCCL all-reduce of the partials)
@@ -618,6 +618,18 @@ def measure_mlp_block(args, dev, rank, world, steps):
         scatter = {"exchange": tp.exchange_name(), "ms_per_block": ms_rs, "tflops": 6.0 * M * H * I / (ms_rs * 1e-3) / 1e12,
                    "rel_error_vs_unsharded_block": err_rs,
                    "note": "every rank ends with its M/P token rows of the output, fully summed"}
+        # and with the transfer inside the down projection (TMA stores into the owners' staging buffers, local sum)
+        tp.exchange = "push"
+        yp = tp(xs[0])
+        torch.cuda.synchronize()
+        err_p = None
+        if rank == 0:
+            err_p = float((yp[:1024].float() - ref).norm() / ref.norm())
+        ms_p = timed(lambda i: tp(xs[i % 2]), steps)
+        push = {"exchange": tp.exchange_name(), "ms_per_block": ms_p, "tflops": 6.0 * M * H * I / (ms_p * 1e-3) / 1e12,
+                "rel_error_vs_unsharded_block": err_p,
+                "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * (4 if reduce_dtype == "f32" else 2)}
+        tp.close()
         tp.exchange = "all_reduce"
     if _ext.status() != 0:
         raise RuntimeError(f"device status word {_ext.status()}")
@@ -630,7 +642,7 @@ def measure_mlp_block(args, dev, rank, world, steps):
            "ms_exchange_alone": ms_xchg,
            "exchange_share": (None if world == 1 else max(0.0, 1.0 - ms_local / ms)),
            "rel_error_vs_unsharded_block": err,
-           "reduce_scatter": scatter,
+           "reduce_scatter": scatter, "push": push,
            "fused_epilogue": bool(getattr(tp.local, "fuse_epilogue", False))}
     del tp, xs
     torch.cuda.empty_cache()

@@ -184,6 +184,28 @@ int tfc4f_gemm(int variant, const void* A, const void* SA, const void* B, const 
 int tfp4_swiglu_gemm(const void* packedA, const void* sblkA, float tsA, const void* packedW, const void* sblkW, float tsW,
                      void* h_packed, void* h_sblk, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* No counterpart in the reference (it is single-GPU): the exchange of a tensor-parallel block whose last layer is
+ * row-parallel, with the transfer inside the GEMM.
+ * tfp4_gemm_push: tfp4_gemm whose epilogue stores this rank's partial product (M, N), 32 token rows at a time, into the
+ *   staging buffer of the rank that owns those rows: dest[o] (host array of n_dest <= 8 device pointers) = where this
+ *   rank's rows for owner o go, a row-major (rows_per_dest, N) matrix of out_dtype (1 bf16 or 2 f32) in owner o's memory,
+ *   mapped into this process (tfp4_peer_open; dest[own rank] is local memory).  Owner o holds token rows
+ *   [o * rows_per_dest, (o + 1) * rows_per_dest); rows_per_dest % 32 == 0.  The stores are TMA stores issued by the
+ *   epilogue warps while the tensor cores work on the next tile, so the NVLink transfer overlaps the GEMM.
+ * tfp4_sum_slots: out (rows, N) = sum over the n staged partials stage[s] (s ascending: the same order on every rank),
+ *   in_dtype 0 f32 / 2 bf16, out_dtype 0 f16 / 1 bf16 / 2 f32.  Run it after every rank's push has completed (a barrier
+ *   on the host or a collective in stream order between the two calls).
+ * tfp4_peer_alloc / _open / _close / _free: a device buffer with a 64-byte CUDA IPC handle that the other processes of
+ *   the node open to obtain a pointer valid on their device. */
+int tfp4_gemm_push(const void* packedA, const void* sblkA, float tsA, const void* packedB, const void* sblkB, float tsB,
+                   void* const* dest, int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K,
+                   int out_dtype, void* stream);
+int tfp4_sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dtype, void* out, int out_dtype, void* stream);
+int tfp4_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int tfp4_peer_open(const unsigned char* handle64, void** ptr);
+int tfp4_peer_close(void* ptr);
+int tfp4_peer_free(void* ptr);
+
 /* Additions: status word of the current device (0 = healthy; otherwise the role
  * whose bounded wait expired: 1 producer, 2 accumulator hand-back, 3 operands,
  * 4 epilogue), its reset, plan-cache counters, and a test hook that pins the

@@ -46,6 +46,23 @@ WORKER = textwrap.dedent('''
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if rank == 0:
         print("RS_OK", int(ok.item()))
+    # the reduce-scatter with its transfer inside the down projection (TMA stores into the owners' staging buffers)
+    tpush = TensorParallelGatedMLP(H, I, device="cuda", reduce_dtype="f32", exchange="push")
+    tpush.load_full_weights(wg.cuda(), wu.cuda(), wd.cuda())
+    good = True
+    for it in range(3):                               # three blocks in a row: both staging sets get reused
+        xi = x if it != 1 else (x * 0.5).bfloat16()
+        yi = tp(xi).clone()
+        yp = tpush(xi).clone()
+        rows_p = tpush.owned_rows(M).cuda()
+        good = good and yp.shape == (M // 2, H) and ((yp - yi[rows_p]).norm() / yi[rows_p].norm()).item() < 1e-6
+        good = good and ((tpush.gather(yp, M) - yi).norm() / yi.norm()).item() < 1e-6
+    okp = torch.tensor([int(good)], device="cuda")
+    dist.all_reduce(okp, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    tpush.close()
+    if rank == 0:
+        print("PUSH_OK", int(okp.item()))
     dist.destroy_process_group()
 ''')
 
@@ -66,3 +83,4 @@ def test_tensor_parallel_mlp_two_gpus(tmp_path):
     assert float(line[1]) < 1e-3
     assert line[3] == "True"
     assert "RS_OK 1" in out.stdout
+    assert "PUSH_OK 1" in out.stdout

@@ -13,7 +13,7 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 OUT_DIR = ROOT / "build"
 LIB = OUT_DIR / "libthorfp4_b200.so"
-SOURCES = ["quant.cu", "misc.cu", "gemm.cu", "api.cu"]
+SOURCES = ["quant.cu", "misc.cu", "gemm.cu", "peer.cu", "api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

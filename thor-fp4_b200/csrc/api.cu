@@ -29,6 +29,13 @@ int gemm_swiglu_nvfp4(const void*, const void*, const void*, const void*, float,
                       cudaStream_t);
 int gemm_mx8_out(const void*, const void*, const void*, const void*, float, const float*, int, void*, void*, int64_t,
                  int64_t, int64_t, cudaStream_t);
+int gemm_push(const void*, const void*, const void*, const void*, float, void* const*, int, int64_t, int64_t, int64_t, int64_t,
+              int, cudaStream_t);
+int sum_slots(const void*, int, int64_t, int64_t, int, void*, int, cudaStream_t);
+int peer_alloc(size_t, void**, unsigned char*);
+int peer_open(const unsigned char*, void**);
+int peer_close(void*);
+int peer_free(void*);
 int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
                  int64_t, int, cudaStream_t);
 int gemm_noalloc_status(int);
@@ -183,6 +190,18 @@ int tfp4_swiglu_gemm(const void* pA, const void* sA, float tsA, const void* pW, 
                      void* h_sblk, int64_t M, int64_t N, int64_t K, void* stream) {
     return tfp4::gemm_swiglu_nvfp4(pA, sA, pW, sW, tsA * tsW, h_packed, h_sblk, M, N, K, S(stream));
 }
+
+int tfp4_gemm_push(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB, void* const* dest,
+                   int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K, int out_dtype, void* stream) {
+    return tfp4::gemm_push(pA, sA, pB, sB, tsA * tsB, dest, n_dest, rows_per_dest, M, N, K, out_dtype, S(stream));
+}
+int tfp4_sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dtype, void* out, int out_dtype, void* stream) {
+    return tfp4::sum_slots(stage, n, rows, N, in_dtype, out, out_dtype, S(stream));
+}
+int tfp4_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) { return tfp4::peer_alloc(bytes, ptr, handle64); }
+int tfp4_peer_open(const unsigned char* handle64, void** ptr) { return tfp4::peer_open(handle64, ptr); }
+int tfp4_peer_close(void* ptr) { return tfp4::peer_close(ptr); }
+int tfp4_peer_free(void* ptr) { return tfp4::peer_free(ptr); }
 
 int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype, uint8_t* packed, uint8_t* sblk, void* stream) {
     return tfp4::swiglu_quant_nvfp4(gu, R, I, in_dtype, packed, sblk, S(stream));

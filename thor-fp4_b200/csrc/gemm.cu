@@ -34,6 +34,7 @@
 // status word the host reads, drains and frees its tensor memory.
 #include <cuda.h>
 
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -61,6 +62,7 @@ struct GemmParams {
     void* out2;              // quantizing epilogues: the scale-tile buffer (out then holds the codes)
     int32_t epi_act;         // MXFP8 epilogue: 0 identity, 1 gelu, 2 silu
     int32_t raster_gm;       // two-CTA kernel: tile order (see duo_tile_coords)
+    int64_t push_rows;       // push epilogue: token rows per owning rank
     const float* bias;       // may be null
     float alpha;
     int64_t M, N, K;
@@ -1021,8 +1023,61 @@ cudaError_t launch_duo_inst(const cudaLaunchConfig_t& cfg, const Plan& plan, con
 }
 
 // epi 0: plain output (any kind); 1: SwiGLU + NVFP4 (kind 0); 2: bias + activation + MXFP8 (kind 1)
-int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int epi, int dev, cudaStream_t stream) {
+// what the GEMM's epilogue makes of the accumulator (see gemm_duo.cuh): 0 plain output, 1 SwiGLU + NVFP4, 2 bias +
+// activation + MXFP8; out2 = scale-tile buffer of the quantized output, act = activation of mode 2
+struct EpilogueSpec {
+    int epi = 0;
+    void* out2 = nullptr;
+    int act = 0;
+    void* const* push_dest = nullptr;   // mode 3: per owning rank, where this rank's partial rows for that owner go
+    int push_ranks = 0;
+    int64_t push_rows = 0;              // token rows per owner
+};
+
+// tensor maps of the push epilogue's destinations, cached like the output maps
+struct PushKey {
+    const void* d[PUSH_MAX_RANKS]; int n; int64_t rows, M, N; int esize; int dev;
+    bool operator<(const PushKey& o) const {
+        for (int i = 0; i < PUSH_MAX_RANKS; ++i)
+            if (d[i] != o.d[i]) return d[i] < o.d[i];
+        return std::tie(n, rows, M, N, esize, dev) < std::tie(o.n, o.rows, o.M, o.N, o.esize, o.dev);
+    }
+};
+std::map<PushKey, PushMaps> g_push_maps;
+
+int push_maps(const PushMaps** out, const EpilogueSpec& es, int64_t M, int64_t N, int esize, int dev) {
+    PushKey key{};
+    for (int i = 0; i < es.push_ranks; ++i) key.d[i] = es.push_dest[i];
+    key.n = es.push_ranks; key.rows = es.push_rows; key.M = M; key.N = N; key.esize = esize; key.dev = dev;
+    auto it = g_push_maps.find(key);
+    if (it == g_push_maps.end()) {
+        PushMaps pm;
+        memset(&pm, 0, sizeof(pm));
+        for (int o = 0; o < es.push_ranks; ++o) {
+            int64_t rows = M - (int64_t)o * es.push_rows;
+            if (rows > es.push_rows) rows = es.push_rows;
+            if (rows <= 0) { pm.m[o] = pm.m[0]; continue; }      // no token row of this owner exists: never selected
+            int rc = encode_map(&pm.m[o], CU_TENSOR_MAP_DATA_TYPE_UINT8, es.push_dest[o], (uint64_t)(N * esize), (uint64_t)rows,
+                                (uint64_t)(N * esize), esize == 2 ? 64 : 128, 32,
+                                esize == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc) return rc;
+        }
+        for (int o = es.push_ranks; o < PUSH_MAX_RANKS; ++o) pm.m[o] = pm.m[0];
+        if (g_push_maps.size() > 1024) g_push_maps.clear();
+        it = g_push_maps.emplace(key, pm).first;
+    }
+    *out = &it->second;
+    return TFP4_OK;
+}
+
+int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int epi, int dev, cudaStream_t stream,
+               const EpilogueSpec* es) {
     const CUtensorMap* tm_out = &plan.tmA;      // the quantizing epilogues store with plain instructions: no output map
+    const PushMaps* pm = nullptr;
+    if (epi == 3) {
+        int rc = push_maps(&pm, *es, p.M, p.N, p.out_dtype == OUT_F32 ? 4 : 2, dev);
+        if (rc) return rc;
+    }
     if (epi == 0) {
         int rc = out_map(&tm_out, p.out, p.M, p.N, p.out_dtype == OUT_F32 ? 4 : 2, dev);
         if (rc) return rc;
@@ -1034,7 +1089,7 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int e
 #define TFP4_DUO_ATTR(K_, E_)                                                                                                   \
         TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<K_, false, E_>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem)); \
         TFP4_CK(cudaFuncSetAttribute(gemm_duo_kernel<K_, true, E_>, cudaFuncAttributeMaxDynamicSharedMemorySize, st->max_smem));
-        TFP4_DUO_ATTR(0, 0) TFP4_DUO_ATTR(1, 0) TFP4_DUO_ATTR(0, 1) TFP4_DUO_ATTR(1, 2)
+        TFP4_DUO_ATTR(0, 0) TFP4_DUO_ATTR(1, 0) TFP4_DUO_ATTR(0, 1) TFP4_DUO_ATTR(1, 2) TFP4_DUO_ATTR(0, 3)
 #undef TFP4_DUO_ATTR
         st->duo_attr_set = true;
     }
@@ -1055,7 +1110,10 @@ int launch_duo(DeviceState* st, const Plan& plan, GemmParams& p, int kind, int e
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl ? 2 : 1;
     cudaError_t e;
-    if (epi == 1) e = launch_duo_inst<0, 1>(cfg, plan, *tm_out, p);
+    if (epi == 3)
+        e = p.debug ? cudaLaunchKernelEx(&cfg, gemm_duo_kernel<0, true, 3>, plan.tmW, plan.tmA, *pm, p)
+                    : cudaLaunchKernelEx(&cfg, gemm_duo_kernel<0, false, 3>, plan.tmW, plan.tmA, *pm, p);
+    else if (epi == 1) e = launch_duo_inst<0, 1>(cfg, plan, *tm_out, p);
     else if (epi == 2) e = launch_duo_inst<1, 2>(cfg, plan, *tm_out, p);
     else if (kind == 0) e = launch_duo_inst<0, 0>(cfg, plan, *tm_out, p);
     else e = launch_duo_inst<1, 0>(cfg, plan, *tm_out, p);
@@ -1110,14 +1168,6 @@ int workspace_for(DeviceState* st, cudaStream_t stream, size_t need, float** out
     *out = blk.ptr;
     return TFP4_OK;
 }
-
-// what the GEMM's epilogue makes of the accumulator (see gemm_duo.cuh): 0 plain output, 1 SwiGLU + NVFP4, 2 bias +
-// activation + MXFP8; out2 = scale-tile buffer of the quantized output, act = activation of mode 2
-struct EpilogueSpec {
-    int epi = 0;
-    void* out2 = nullptr;
-    int act = 0;
-};
 
 int g_raster_gm = 0;    // 0 automatic, -1 token tiles fastest, n > 0 bands of n token tiles
 int g_force_bn = 0;
@@ -1217,6 +1267,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // touches every token tile: fine while all of the activation codes fit, a re-fetch per wave when they do not
     // (16384 x 8192 at K = 8192: 510 -> 469 us; the SwiGLU block's down projection, K = 28672: 2035 -> 1727 us).
     // Bands of gm token tiles whose codes and scales take about 34 MB keep the band resident while the weights stream.
+    p.push_rows = es ? es->push_rows : 0;
     p.raster_gm = 0;
     if (g_raster_gm > 0) {
         p.raster_gm = g_raster_gm;
@@ -1323,7 +1374,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     p.status = ext ? ext->status : st->status_dev;
     p.stats = ext ? ext->stats : st->stats_dev;
     const Plan& pl = it->second;
-    if (duo) return launch_duo(st, pl, p, kind, epi, dev, stream);
+    if (duo) return launch_duo(st, pl, p, kind, epi, dev, stream, es);
 #define TFP4_GO(KINDV)                                                          \
     switch (bn) {                                                               \
         case 32: return launch<KINDV, 32>(st, pl, p, 0, stream);                \
@@ -1382,6 +1433,32 @@ int gemm_mx8_out(const void* packedA, const void* sblkA, const void* packedB, co
     es.out2 = SFD;
     es.act = act;
     return gemm_block_scaled_ws(1, packedA, sblkA, packedB, sblkB, alpha, bias, D, M, N, K, OUT_BF16, stream, nullptr, &es);
+}
+
+// Row-parallel GEMM of a tensor-parallel block with the first half of the reduce-scatter in its epilogue: this rank's
+// partial product (M, N) is stored, 32-row block by 32-row block, into the staging buffers of the ranks that own the
+// token rows - dest[o] = where this rank's rows for owner o go, a row-major (rows_per_dest, N) matrix of out_dtype
+// (f32 or bf16) in owner o's memory (peer-mapped; dest[own rank] is local).  The stores are TMA stores issued by the
+// epilogue warps while the main loop runs; sum_slots on the owner completes the reduction.
+int gemm_push(const void* packedA, const void* sblkA, const void* packedB, const void* sblkB, float alpha, void* const* dest,
+              int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K, int out_dtype, cudaStream_t stream) {
+    if (n_dest < 1 || n_dest > PUSH_MAX_RANKS || rows_per_dest <= 0 || (rows_per_dest % 32) != 0 || (int64_t)n_dest * rows_per_dest < M ||
+        dest == nullptr || (out_dtype != OUT_F32 && out_dtype != OUT_BF16)) {
+        fprintf(stderr, "thor_fp4: gemm_push needs 1..%d destinations, rows per destination a multiple of 32 covering M, f32 or bf16 partials\n",
+                PUSH_MAX_RANKS);
+        return TFP4_ERR_BAD_ARG;
+    }
+    for (int i = 0; i < n_dest; ++i)
+        if (dest[i] == nullptr || (reinterpret_cast<uintptr_t>(dest[i]) & 15)) {
+            fprintf(stderr, "thor_fp4: gemm_push destination %d is null or not 16-byte aligned\n", i);
+            return TFP4_ERR_BAD_ARG;
+        }
+    EpilogueSpec es;
+    es.epi = 3;
+    es.push_dest = dest;
+    es.push_ranks = n_dest;
+    es.push_rows = rows_per_dest;
+    return gemm_block_scaled_ws(0, packedA, sblkA, packedB, sblkB, alpha, nullptr, dest[0], M, N, K, out_dtype, stream, nullptr, &es);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -413,10 +413,19 @@ __device__ __forceinline__ void act_mx8_block32(const uint32_t (&v)[32], float a
 //      UE4M3 scale bytes straight into the A-operand buffers of the next GEMM - no [M, 2I] tensor reaches memory;
 //   2  bias + activation + MXFP8: a 32-column chunk is one MX block of act(alpha * acc + bias[n]); e4m3 codes and
 //      UE8M0 scale bytes (power of two at or above amax / 448) go to the next layer's A-operand buffers.
+//   3  tensor-parallel push: the plain output of mode 0, but every 32-row block of the tile is stored (TMA, over
+//      NVLink for a peer) into the staging buffer of the rank that owns those token rows - one tensor map per owner -
+//      so the partial products of a row-parallel layer reach their owners while the main loop is still running;
+//      a sum over the staged partials completes the reduce-scatter.
+constexpr int PUSH_MAX_RANKS = 8;
+struct PushMaps { CUtensorMap m[PUSH_MAX_RANKS]; };
+template <int EPI> struct DuoOutMaps { using type = CUtensorMap; };
+template <> struct DuoOutMaps<3> { using type = PushMaps; };
+
 template <int KIND, bool DBG, int EPI>
 __global__ void __launch_bounds__(DUO_THREADS, 1)
 gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
+                const __grid_constant__ typename DuoOutMaps<EPI>::type tmO, const GemmParams p) {
     using C = DuoCfg;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -616,7 +625,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const bool out16 = p.out_dtype != OUT_F32, bf16 = p.out_dtype == OUT_BF16;
         const int esize = out16 ? 2 : 4;
         const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)(half * 4 + q) * C::EPI_BUF;
-        if constexpr (EPI == 0) {
+        if constexpr (EPI == 0 || EPI == 3) {
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 int64_t nt, mt;
             duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
@@ -643,7 +652,15 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     if (lane == 0) {
                         // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
                         // lies outside altogether still closes an (empty) group, so that the group counts above hold
-                        if (row0 < p.M && nn < p.N && !(dbg & 1)) tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
+                        if (row0 < p.M && nn < p.N && !(dbg & 1)) {
+                            if constexpr (EPI == 3) {
+                                // the owner of these 32 token rows (push_rows is a multiple of 32: a block has one owner)
+                                const int64_t o = row0 / p.push_rows;
+                                tma_store_2d(&tmO.m[o], (int)(nn * esize), (int)(row0 - o * p.push_rows), buf);
+                            } else {
+                                tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
+                            }
+                        }
                         bulk_commit_group();
                     }
                     ++nstore;

@@ -245,7 +245,9 @@ class NVFP4GatedMLP(nn.Module):
         self._q_layout = self.fuse_epilogue
         return self
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, down: bool = True):
+        """down=False stops after the hidden tensor and returns its buffers (codes, scale tiles), for callers that run
+        the down projection themselves (the tensor-parallel block's push exchange)."""
         with torch.no_grad():
             if self._q is None or self._q_layout != self.fuse_epilogue:
                 self.refresh_weight()
@@ -283,6 +285,8 @@ class NVFP4GatedMLP(nn.Module):
                 else:
                     h = (F.silu(gu[:, :I].float()) * gu[:, I:].float()).to(torch.bfloat16)
                     ops.quantize_nvfp4(h, 1.0, b["hp"], b["hs"])
+            if not down:
+                return b["hp"], b["hs"]
             y = out if out is not None else b["y"]
             ops.gemm(b["hp"], b["hs"], 1.0, wd.packed, wd.sblk, wd.tensor_scale, y, M, H, I, self.out_dtype)
             return y

@@ -12,10 +12,13 @@ quantization.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from . import _ext
 from .fused import NVFP4GatedMLP
 
 __all__ = ["TensorParallelGatedMLP", "shard_rows", "shard_cols"]
@@ -47,6 +50,52 @@ def full_tensor_scales(w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.T
     return (max(gu / (6.0 * 448.0), 1e-30), max(w_down.abs().amax().item() / (6.0 * 448.0), 1e-30))
 
 
+class _PushStaging:
+    """Staging memory of the push exchange on one rank: two sets (used alternately, so that a rank may start pushing
+    the next block while a slower rank still sums the previous one) of `world` slots of (rows, hidden) partial
+    products - slot s receives rank s's partials for this rank's token rows.  The buffer is exported over CUDA IPC;
+    every rank opens every other rank's buffer and keeps, per set and owner, the address of its own slot there."""
+
+    def __init__(self, group, world: int, rank: int, rows: int, hidden: int, dtype: torch.dtype, device):
+        L = _ext.device_lib()
+        self.L, self.world, self.rank, self.rows, self.hidden = L, world, rank, rows, hidden
+        self.esize = 4 if dtype == torch.float32 else 2
+        self.set_bytes = world * rows * hidden * self.esize
+        base = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        rc = L.tfp4_peer_alloc(2 * self.set_bytes, ctypes.byref(base), handle)
+        if rc != 0:
+            raise RuntimeError(f"tfp4_peer_alloc rc={rc}")
+        self.base = base.value
+        mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=device)
+        allh = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine, group=group)
+        self.peer_base, self._opened = [], []
+        for p in range(world):
+            if p == rank:
+                self.peer_base.append(self.base)
+                continue
+            ptr = ctypes.c_void_p()
+            rc = L.tfp4_peer_open(bytes(allh[p].cpu().tolist()), ctypes.byref(ptr))
+            if rc != 0:
+                raise RuntimeError(f"tfp4_peer_open of rank {p}'s staging buffer rc={rc}")
+            self.peer_base.append(ptr.value)
+            self._opened.append(ptr.value)
+        slot = rank * rows * hidden * self.esize
+        self.dest = [(ctypes.c_void_p * world)(*[self.peer_base[o] + k * self.set_bytes + slot for o in range(world)])
+                     for k in range(2)]
+        self.local_set = [self.base + k * self.set_bytes for k in range(2)]
+        self.turn = 0
+
+    def close(self):
+        for ptr in self._opened:
+            self.L.tfp4_peer_close(ptr)
+        self._opened = []
+        if self.base:
+            self.L.tfp4_peer_free(self.base)
+            self.base = None
+
+
 class TensorParallelGatedMLP(nn.Module):
     """y = sum_p( down_p( nvfp4( silu(x Wg_p^T) * (x Wu_p^T) ) ) ), the sum taken over the ranks.
 
@@ -62,6 +111,12 @@ class TensorParallelGatedMLP(nn.Module):
                         that works per token (residual add, norm, the next block's quantizer) and an all-gather is
                         paid only where a replicated tensor is really needed; half the bytes of the all-reduce.
                         forward() then returns the (M/P, hidden) rows `owned_rows(M)` of this rank.
+      "push"            the reduce-scatter with its transfer inside the down projection: the GEMM's epilogue stores
+                        each 32-row block of this rank's partial product into the staging buffer of the rank that owns
+                        those token rows (TMA stores over NVLink into peer memory, issued while the tensor cores work
+                        on the next tile), then one small collective orders the ranks and a local kernel sums the
+                        staged partials.  No collective kernel competes with the GEMM for SMs.  Rank r ends with rows
+                        [r M/P, (r+1) M/P); M must divide by 32 P.
     The tokens are cut into `chunks` pieces: the exchange of one piece runs on the collective's own stream while
     this rank's GEMMs of the next piece run."""
 
@@ -69,8 +124,9 @@ class TensorParallelGatedMLP(nn.Module):
                  reduce_dtype: str = "f32", weight_std: float | None = 0.02, local: nn.Module | None = None,
                  chunks: int = 4, exchange: str = "all_reduce"):
         super().__init__()
-        if exchange not in ("all_reduce", "reduce_scatter"):
-            raise ValueError(f"exchange={exchange!r}: pick 'all_reduce' | 'reduce_scatter'")
+        if exchange not in ("all_reduce", "reduce_scatter", "push"):
+            raise ValueError(f"exchange={exchange!r}: pick 'all_reduce' | 'reduce_scatter' | 'push'")
+        self._push: dict = {}
         self.group = group
         self.exchange = exchange
         self.chunks = max(1, int(chunks))     # token chunks: the exchange of one overlaps the GEMMs of the next
@@ -94,6 +150,9 @@ class TensorParallelGatedMLP(nn.Module):
         return self
 
     def exchange_name(self) -> str:
+        if self.exchange == "push":
+            return ("reduce-scatter by token rows inside the down projection: TMA stores of the partial tiles into the "
+                    "owners' staging buffers over NVLink from the GEMM epilogue, one 4-byte all-reduce as the barrier, local sum")
         kind = "all-reduce" if self.exchange == "all_reduce" else "reduce-scatter by token rows"
         return f"NCCL {kind} of the partial outputs, {self.chunks} token chunks overlapped with the next chunk's GEMMs"
 
@@ -110,6 +169,9 @@ class TensorParallelGatedMLP(nn.Module):
     def owned_rows(self, M: int, on_device: bool = True) -> torch.Tensor:
         """Global token indices of the rows forward() returns on this rank under exchange='reduce_scatter'
         (chunk by chunk, this rank's 1/P of each chunk)."""
+        if self.exchange == "push":
+            n = M // self.world
+            return torch.arange(self.rank * n, (self.rank + 1) * n)
         idx = []
         for r0, r1 in self._chunk_bounds(M, on_device):
             n = (r1 - r0) // self.world
@@ -120,6 +182,8 @@ class TensorParallelGatedMLP(nn.Module):
         """All-gather the reduce-scattered rows back into the replicated (M, hidden) tensor in token order."""
         parts = [torch.empty_like(y_local) for _ in range(self.world)]
         dist.all_gather(parts, y_local.contiguous(), group=self.group)
+        if self.exchange == "push":
+            return torch.cat(parts, dim=0)
         out = torch.empty(M, y_local.shape[1], dtype=y_local.dtype, device=y_local.device)
         on_device = y_local.is_cuda
         pos = 0
@@ -138,9 +202,47 @@ class TensorParallelGatedMLP(nn.Module):
             return None
         return dist.reduce_scatter_tensor(dst, src, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
 
+    def _forward_push(self, x: torch.Tensor) -> torch.Tensor:
+        m, L = self.local, _ext.device_lib()
+        M, H = x.shape[0], self.hidden
+        if M % (32 * self.world) != 0:
+            raise ValueError(f"exchange='push' needs the token count ({M}) to divide by 32 x world size ({32 * self.world})")
+        rows = M // self.world
+        dt = _ext.OUT_TORCH[m.out_dtype]
+        if dt not in (torch.float32, torch.bfloat16):
+            raise ValueError("exchange='push' stages f32 or bf16 partials")
+        st = self._push.get((M, dt))
+        if st is None:
+            stg = _PushStaging(self.group, self.world, self.rank, rows, H, dt, x.device)
+            st = self._push[(M, dt)] = (stg, torch.empty(rows, H, dtype=dt, device=x.device),
+                                        torch.zeros(1, dtype=torch.int32, device=x.device))
+        stg, ys, flag = st
+        hp, hs = m(x, down=False)
+        wd = m._q[1]
+        k = stg.turn
+        stg.turn ^= 1
+        rc = L.tfp4_gemm_push(hp.data_ptr(), hs.data_ptr(), 1.0, wd.packed.data_ptr(), wd.sblk.data_ptr(), float(wd.tensor_scale),
+                              stg.dest[k], self.world, rows, M, H, self.local_intermediate, _ext.OUT_DTYPE[m.out_dtype], _ext.stream())
+        assert rc == 0, f"tfp4_gemm_push rc={rc}"
+        # every rank's stores have landed once every rank's GEMM has completed: a 4-byte collective in stream order
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        rc = L.tfp4_sum_slots(stg.local_set[k], self.world, rows, H, _ext.IN_DTYPE[dt], ys.data_ptr(),
+                              _ext.OUT_DTYPE[m.out_dtype], _ext.stream())
+        assert rc == 0, f"tfp4_sum_slots rc={rc}"
+        return ys
+
+    def close(self):
+        """Release the IPC mappings and staging buffers of the push exchange (call on every rank before the process
+        group goes away; nothing to do for the other exchanges)."""
+        for stg, _, _ in self._push.values():
+            stg.close()
+        self._push = {}
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return self.local(x)
+        if self.exchange == "push":
+            return self._forward_push(x)
         M = x.shape[0]
         bounds = self._chunk_bounds(M, x.is_cuda)
         scatter = self.exchange == "reduce_scatter"
