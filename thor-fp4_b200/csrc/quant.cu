@@ -43,9 +43,64 @@ namespace {
 template <bool B> struct BoolTag { static constexpr bool value = B; };
 
 constexpr int QT_ROWS = 128;   // rows per CTA tile = one scale-atom height
-constexpr int QT_COLS = 256;   // columns per CTA tile = 8 elements x 32 lanes
+constexpr int QT_COLS = 256;   // columns per CTA tile = 16 elements x 16 lanes (NVFP4 quantizer), 8 x 32 (MX kernels)
 constexpr int QT_THREADS = 256;
 constexpr int QT_UNROLL = 4;   // rows in flight per warp
+
+// 16 consecutive elements of one row = one quantization block, held by ONE lane: raw bits as loaded
+// (two 16-byte loads for 16-bit inputs, four for f32) and their widening to float.
+template <typename T> struct Raw16 { uint4 v[sizeof(T) == 2 ? 2 : 4]; };
+
+template <typename T>
+__device__ __forceinline__ Raw16<T> fetch16(const T* p) {
+    Raw16<T> r;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(T) == 2 ? 2 : 4); ++i) r.v[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ Raw16<T> zero16() {
+    Raw16<T> r;
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(T) == 2 ? 2 : 4); ++i) r.v[i] = make_uint4(0u, 0u, 0u, 0u);
+    return r;
+}
+__device__ __forceinline__ void widen16(const Raw16<float>& r, float (&lo)[8], float (&hi)[8]) {
+    const uint4 q[4] = {r.v[0], r.v[1], r.v[2], r.v[3]};
+    lo[0] = __uint_as_float(q[0].x); lo[1] = __uint_as_float(q[0].y); lo[2] = __uint_as_float(q[0].z); lo[3] = __uint_as_float(q[0].w);
+    lo[4] = __uint_as_float(q[1].x); lo[5] = __uint_as_float(q[1].y); lo[6] = __uint_as_float(q[1].z); lo[7] = __uint_as_float(q[1].w);
+    hi[0] = __uint_as_float(q[2].x); hi[1] = __uint_as_float(q[2].y); hi[2] = __uint_as_float(q[2].z); hi[3] = __uint_as_float(q[2].w);
+    hi[4] = __uint_as_float(q[3].x); hi[5] = __uint_as_float(q[3].y); hi[6] = __uint_as_float(q[3].z); hi[7] = __uint_as_float(q[3].w);
+}
+template <typename T>
+__device__ __forceinline__ void widen16(const Raw16<T>& r, float (&lo)[8], float (&hi)[8]) {
+    Raw8<T> a, b;
+    a.a = r.v[0];
+    b.a = r.v[1];
+    widen8(a, lo);
+    widen8(b, hi);
+}
+
+// The scale byte of a 16-element block held by one lane (f = its two halves) and the decode scale ds = dec(sc) * ts.
+// Same arithmetic as block_scale8 (quant_block.cuh) without the shuffle between the two lanes of a pair.
+template <int MODE>
+__device__ __forceinline__ float block_scale16(const float (&lo)[8], const float (&hi)[8], float ts, float rts_lo, float rts_hi,
+                                               uint32_t& sc) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(lo[i]), fabsf(hi[i])));
+    float pre = amax * (1.0f / 6.0f);
+    if (MODE == 1 || MODE == 3) {
+        const uint32_t both = f32x2_to_e4m3x2(pre * rts_lo, pre * rts_hi);
+        sc = both & 0x7fu;
+        if (sc != ((both >> 8) & 0x7fu)) sc = f32x2_to_e4m3x2(__fdiv_rn(pre, ts), 0.f) & 0x7fu;
+    } else {
+        if (MODE != 0) pre = __fdiv_rn(pre, ts);   // (amax * (1/6)) / ts, the reference's operand order
+        sc = f32x2_to_e4m3x2(pre, 0.f) & 0x7fu;
+    }
+    const float sf = e4m3_to_f32(sc);
+    return (MODE != 0) ? sf * ts : sf;
+}
 
 // MODE 0: EXACT16 (16-bit input, ts == 1); 1: BRACKET; 2: LITERAL (always divide);
 // 3: BRACKET without the tiny-input check (16-bit input and ts <= 128: the smallest non-zero
@@ -55,6 +110,12 @@ constexpr int QT_UNROLL = 4;   // rows in flight per warp
 // the quantized tensor is h = round_to_T(silu(gate) * up), computed in FP32, held in T like the
 // unfused block holds it, and quantized with the same code path (one pass instead of an elementwise
 // kernel with FP32 temporaries followed by the quantizer).
+//
+// Work split.  A lane owns one whole 16-element block (32 contiguous bytes of a 16-bit row): the block's amax,
+// scale byte and multiplier are computed once, by the lane that needs them, with no exchange between lanes.
+// A half-warp covers the tile's 256 columns of one row (512 contiguous bytes), so a warp works on two rows at a
+// time: warp w, half h handles tile rows 16 * it + 2 * w + h.  Codes leave as 8 bytes per lane (128 contiguous
+// bytes per half-warp); scale bytes are staged in shared memory and leave as whole 512-byte atoms.
 template <typename T, int MODE, int ROWS, bool GATED = false>
 __global__ void __launch_bounds__(QT_THREADS, sizeof(T) == 2 ? 4 : 3)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
@@ -67,12 +128,16 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     griddep_wait();
     griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = lane >> 4, l16 = lane & 15;
     const int64_t r0 = (int64_t)blockIdx.y * ROWS;
     const int ra = (ROWS == 128) ? 0 : (int)(r0 & 127);   // first row of this CTA inside its scale atom
-    constexpr int UNROLL = (MODE == 0 && !GATED) ? 4 : 2;   // rows in flight per warp
+    constexpr int STEPS = ROWS / 16;                   // 16 rows per step and CTA (8 warps x 2 half-warps)
+    // steps (= rows per lane) per buffer set; two sets alternate.  The variants with more arithmetic per block keep one
+    // row per set: with two they spill
+    constexpr int UNROLL = (MODE == 0 && !GATED) ? 2 : 1;
     const int64_t ld = GATED ? 2 * K : K;              // input row stride in elements
     const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
-    const int64_t col = c0 + lane * 8;
+    const int64_t col = c0 + l16 * 16;
     const bool col_ok = col < K;
     const int64_t Rpad = pad128(R);
 
@@ -82,96 +147,77 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
 
     reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
     // MODE 0: the multiplier of a block depends only on its scale byte (127 values): RN(1 / dec(sc)) * (1 + 2^-21),
-    // computed once per CTA with the arithmetic the per-row code used, then one shared-memory read per row
+    // computed once per CTA with the arithmetic the per-row code used, then one shared-memory read per block
     __shared__ float s_rb[128];
     if (MODE == 0 && threadIdx.x < 128)
         s_rb[threadIdx.x] = __frcp_rn(e4m3_to_f32(threadIdx.x)) * 1.000000476837158203125f;
     __syncthreads();
 
-    // warp w handles tile rows w, w+8, ..., w+120, UNROLL rows per step; the raw loads of
-    // the next step are issued before the current step is processed (loads always in flight)
     constexpr int NSRC = GATED ? 2 : 1;
     // the tile loop, instantiated twice: tiles wholly inside the tensor (no row or column checks) and edge tiles
     auto run_tile = [&](auto full_tag) {
         constexpr bool FULL = decltype(full_tag)::value;
-        auto fetch_rows = [&](int it, Raw8<T> (&dst)[NSRC][UNROLL]) {
+        auto fetch_rows = [&](int it, Raw16<T> (&dst)[NSRC][UNROLL]) {
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int64_t r = r0 + warp + 8 * (it + u);
+                const int64_t r = r0 + 16 * (it + u) + 2 * warp + half;
 #pragma unroll
                 for (int g = 0; g < NSRC; ++g)
-                    dst[g][u] = (FULL || (col_ok && r < R)) ? fetch8<T>(x + r * ld + g * K + col) : zero8<T>();
+                    dst[g][u] = (FULL || (col_ok && r < R)) ? fetch16<T>(x + r * ld + g * K + col) : zero16<T>();
             }
         };
-        // two row buffers used alternately (the loads of one step are in flight while the other is processed),
-        // without register copies between them
-        auto process = [&](int it, Raw8<T> (&cur)[NSRC][UNROLL]) {
-
-            float f[UNROLL][8];
+        auto process = [&](int it, Raw16<T> (&cur)[NSRC][UNROLL]) {
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                widen8(cur[0][u], f[u]);
+                float lo[8], hi[8];
+                widen16(cur[0][u], lo, hi);
                 if constexpr (GATED) {
-                    float up[8];
-                    widen8(cur[NSRC - 1][u], up);
+                    float ulo[8], uhi[8];
+                    widen16(cur[NSRC - 1][u], ulo, uhi);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         // silu from correctly rounded operations only (det_math.cuh): the CPU oracle repeats them
-                        // bit for bit, so the codes of h can be checked byte by byte
-                        const float hv = __fmul_rn(det_silu(f[u][i]), up[i]);
-                        f[u][i] = static_cast<float>(static_cast<T>(hv));     // h is held in T
+                        // bit for bit, so the codes of h can be checked byte by byte; h is held in T
+                        lo[i] = static_cast<float>(static_cast<T>(__fmul_rn(det_silu(lo[i]), ulo[i])));
+                        hi[i] = static_cast<float>(static_cast<T>(__fmul_rn(det_silu(hi[i]), uhi[i])));
                     }
                 }
-            }
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int rl = warp + 8 * (it + u);
+                const int rl = 16 * (it + u) + 2 * warp + half;
                 const int64_t r = r0 + rl;
-                uint32_t codes = 0;
-                if (FULL || r < R) {   // warp-uniform: every lane takes part in the shuffles
+                uint32_t c_lo = 0, c_hi = 0;
+                if (FULL || r < R) {
                     uint32_t sc;
-                    const float ds = block_scale8<MODE>(f[u], ts, rts_lo, rts_hi, sc);
-                    if ((lane & 1) == 0 && (FULL || col_ok)) {
-                        const int sl = lane >> 1;   // scale column inside the tile, 0..15
-                        s_sf[(sl >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (sl & 3)] = (uint8_t)sc;
-                    }
+                    const float ds = block_scale16<MODE>(lo, hi, ts, rts_lo, rts_hi, sc);
+                    if (FULL || col_ok)      // scale column l16 of the tile: atom l16 / 4, byte 16 * (row % 32) + 4 * (row / 32) + l16 % 4
+                        s_sf[(l16 >> 2) * 512 + 16 * ((ra + rl) & 31) + 4 * ((ra + rl) >> 5) + (l16 & 3)] = (uint8_t)sc;
                     if constexpr (MODE == 0) {
                         const float rb = s_rb[sc];
-                        float y[8];
+                        float ya[8], yb[8];
 #pragma unroll
-                        for (int i = 0; i < 8; i += 2) mul2_pz(y[i], y[i + 1], f[u][i], f[u][i + 1], rb);
-                        codes = pack_codes_rne(y);
+                        for (int i = 0; i < 8; i += 2) {
+                            mul2_pz(ya[i], ya[i + 1], lo[i], lo[i + 1], rb);
+                            mul2_pz(yb[i], yb[i + 1], hi[i], hi[i + 1], rb);
+                        }
+                        c_lo = pack_codes_rne(ya);
+                        c_hi = pack_codes_rne(yb);
                     } else {
-                        codes = block_codes8<MODE>(f[u], ds);
+                        c_lo = block_codes8<MODE>(lo, ds);
+                        c_hi = block_codes8<MODE>(hi, ds);
                     }
                 }
                 if (FULL || (col_ok && r < Rpad))
-                    *reinterpret_cast<uint32_t*>(packed + r * (K >> 1) + (col >> 1)) = codes;
+                    *reinterpret_cast<uint2*>(packed + r * (K >> 1) + (col >> 1)) = make_uint2(c_lo, c_hi);
             }
         };
-        Raw8<T> buf_a[NSRC][UNROLL], buf_b[NSRC][UNROLL];
+        // two sets of row buffers used alternately: the loads of one are in flight while the other is processed
+        Raw16<T> buf_a[NSRC][UNROLL], buf_b[NSRC][UNROLL];
         fetch_rows(0, buf_a);
-        if constexpr (GATED || MODE == 0) {
-            // (four rows per step, or twice the loads plus the activation arithmetic: these variants spill with
-            // the loop body instantiated twice and gain nothing from it; they copy the prefetched rows instead)
 #pragma unroll 1
-            for (int it = 0; it < ROWS / 8; it += UNROLL) {
-                if (it + UNROLL < ROWS / 8) fetch_rows(it + UNROLL, buf_b);
-                process(it, buf_a);
-#pragma unroll
-                for (int u = 0; u < UNROLL; ++u) {
-#pragma unroll
-                    for (int g = 0; g < NSRC; ++g) buf_a[g][u] = buf_b[g][u];
-                }
-            }
-        } else {
-#pragma unroll 1
-            for (int it = 0; it < ROWS / 8; it += 2 * UNROLL) {
-                fetch_rows(it + UNROLL, buf_b);
-                process(it, buf_a);
-                if (it + 2 * UNROLL < ROWS / 8) fetch_rows(it + 2 * UNROLL, buf_a);
-                process(it + UNROLL, buf_b);
-            }
+        for (int it = 0; it < STEPS; it += 2 * UNROLL) {
+            if (it + UNROLL < STEPS) fetch_rows(it + UNROLL, buf_b);
+            process(it, buf_a);
+            if (it + 2 * UNROLL < STEPS) fetch_rows(it + 2 * UNROLL, buf_a);
+            if (it + UNROLL < STEPS) process(it + UNROLL, buf_b);
         }
     };
     if (r0 + ROWS <= R && c0 + QT_COLS <= K) run_tile(BoolTag<true>{});
