@@ -119,7 +119,7 @@ __device__ __forceinline__ float block_scale16(const float (&lo)[8], const float
 template <typename T, int MODE, int ROWS, bool GATED = false>
 __global__ void __launch_bounds__(QT_THREADS, sizeof(T) == 2 ? 4 : 3)
 quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
-                   uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk) {
+                   uint8_t* __restrict__ packed, uint8_t* __restrict__ sblk, int64_t tiles_x, int64_t n_tiles) {
     __shared__ __align__(16) uint8_t s_sf[4 * 512];
     // Programmatic dependent launch on both sides: this grid may have been made resident while the kernel
     // before it (the GEMM producing x, or the GEMM still reading the previous contents of packed / sblk) was
@@ -129,31 +129,38 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     griddep_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = lane >> 4, l16 = lane & 15;
-    const int64_t r0 = (int64_t)blockIdx.y * ROWS;
-    const int ra = (ROWS == 128) ? 0 : (int)(r0 & 127);   // first row of this CTA inside its scale atom
     constexpr int STEPS = ROWS / 16;                   // 16 rows per step and CTA (8 warps x 2 half-warps)
     // steps (= rows per lane) per buffer set; two sets alternate.  The variants with more arithmetic per block keep one
     // row per set: with two they spill
     constexpr int UNROLL = (MODE == 0 && !GATED) ? 2 : 1;
     const int64_t ld = GATED ? 2 * K : K;              // input row stride in elements
-    const int64_t c0 = (int64_t)blockIdx.x * QT_COLS;
-    const int64_t col = c0 + l16 * 16;
-    const bool col_ok = col < K;
     const int64_t Rpad = pad128(R);
 
     // reciprocals of the per-tensor scale biased by +-2^-20 (bracket modes only)
     const float rts = __frcp_rn(ts);
     const float rts_hi = rts * 1.00000095367431640625f, rts_lo = rts * 0.99999904632568359375f;
 
-    reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
     // MODE 0: the multiplier of a block depends only on its scale byte (127 values): RN(1 / dec(sc)) * (1 + 2^-21),
     // computed once per CTA with the arithmetic the per-row code used, then one shared-memory read per block
     __shared__ float s_rb[128];
     if (MODE == 0 && threadIdx.x < 128)
         s_rb[threadIdx.x] = __frcp_rn(e4m3_to_f32(threadIdx.x)) * 1.000000476837158203125f;
-    __syncthreads();
 
     constexpr int NSRC = GATED ? 2 : 1;
+    // Persistent over tiles: the grid is sized to the CTAs that are resident at once and every CTA walks the tiles
+    // tile = blockIdx.x, + gridDim.x, ...  With whole-wave launches a tile count such as 2048 on 592 resident CTAs
+    // runs 4 waves for 3.46 waves of work; here the CTAs differ by at most one (finer, 64-row) tile.
+#pragma unroll 1
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int64_t ty = tile / tiles_x;
+    const int64_t r0 = ty * ROWS;
+    const int ra = (ROWS == 128) ? 0 : (int)(r0 & 127);   // first row of this tile inside its scale atom
+    const int64_t c0 = (tile - ty * tiles_x) * QT_COLS;
+    const int64_t col = c0 + l16 * 16;
+    const bool col_ok = col < K;
+    reinterpret_cast<uint2*>(s_sf)[threadIdx.x] = make_uint2(0u, 0u);
+    __syncthreads();      // staging cleared (and, first time round, the multiplier table written)
+
     // the tile loop, instantiated twice: tiles wholly inside the tensor (no row or column checks) and edge tiles
     auto run_tile = [&](auto full_tag) {
         constexpr bool FULL = decltype(full_tag)::value;
@@ -227,16 +234,18 @@ quant_nvfp4_kernel(const T* __restrict__ x, int64_t R, int64_t K, float ts,
     const int64_t D = K >> 6;                          // atoms per 128-row tile
     const int64_t d0 = c0 >> 6;
     const int n_atoms = (int)((K - c0 >= QT_COLS) ? 4 : ((K - c0) >> 6));
-    uint8_t* tile = sblk + ((r0 >> 7) * D + d0) * 512;
+    uint8_t* dst = sblk + ((r0 >> 7) * D + d0) * 512;
     if (ROWS == 128) {
         const int atom = threadIdx.x >> 6;             // 64 threads x 8 bytes per atom
         if (atom < n_atoms)
-            *reinterpret_cast<uint2*>(tile + threadIdx.x * 8) = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
+            *reinterpret_cast<uint2*>(dst + threadIdx.x * 8) = reinterpret_cast<const uint2*>(s_sf)[threadIdx.x];
     } else if (threadIdx.x < 128) {
         // rows ra..ra+63 own bytes [8h, 8h+8) of every 16-byte lane row, h = ra / 64
         const int atom = threadIdx.x >> 5, off = atom * 512 + 16 * (threadIdx.x & 31) + (ra >> 3);
         if (atom < n_atoms)
-            *reinterpret_cast<uint2*>(tile + off) = *reinterpret_cast<const uint2*>(s_sf + off);
+            *reinterpret_cast<uint2*>(dst + off) = *reinterpret_cast<const uint2*>(s_sf + off);
+    }
+    __syncthreads();      // the staging bytes have been read before the next tile clears them
     }
 }
 
@@ -506,29 +515,38 @@ mx8_mul_kernel(const uint8_t* __restrict__ ap, const uint8_t* __restrict__ as,
 
 int g_quant_pdl = 1;   // 1: the NVFP4 quantizer is launched as a programmatic dependent of the kernel before it
 
+// resident CTAs of the quantizer on the current device (4 per SM for 16-bit inputs, 3 for f32: the launch bounds)
+int quant_slots(int elem_size) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms * (elem_size == 2 ? 4 : 3);
+}
+
 template <typename T, int ROWS>
 int launch_quant_nvfp4_rows(const T* xp, int64_t R, int64_t K, float ts, uint8_t* packed, uint8_t* sblk,
                             cudaStream_t stream) {
-    // the grid covers the padded rows so that the rows past R of the last 128-row tile get their zeros
-    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)(pad128(R) / ROWS));
+    // the tiles cover the padded rows so that the rows past R of the last 128-row tile get their zeros
+    const int64_t tiles_x = (K + QT_COLS - 1) / QT_COLS, n_tiles = tiles_x * (pad128(R) / ROWS);
+    const int64_t slots = quant_slots((int)sizeof(T));
     const bool ts_sane = (ts >= 0x1p-100f) && (ts <= 0x1p30f);   // false for NaN too
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
+    cfg.gridDim = dim3((unsigned)(n_tiles < slots ? n_tiles : slots));
     cfg.blockDim = dim3(QT_THREADS);
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = g_quant_pdl ? 1 : 0;
     if (!ts_sane) {
-        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 2, ROWS>, xp, R, K, ts, packed, sblk));
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 2, ROWS>, xp, R, K, ts, packed, sblk, tiles_x, n_tiles));
     } else if (sizeof(T) == 2 && ts == 1.0f) {
-        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 0, ROWS>, xp, R, K, ts, packed, sblk));
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 0, ROWS>, xp, R, K, ts, packed, sblk, tiles_x, n_tiles));
     } else if (sizeof(T) == 2 && ts <= 128.0f) {
-        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 3, ROWS>, xp, R, K, ts, packed, sblk));
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 3, ROWS>, xp, R, K, ts, packed, sblk, tiles_x, n_tiles));
     } else {
-        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 1, ROWS>, xp, R, K, ts, packed, sblk));
+        TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<T, 1, ROWS>, xp, R, K, ts, packed, sblk, tiles_x, n_tiles));
     }
     return TFP4_OK;
 }
@@ -538,13 +556,16 @@ int g_quant_rows = 0;   // test hook: 64 / 128 forces the tile height, 0 = autom
 template <typename T>
 int launch_quant_nvfp4(const void* x, int64_t R, int64_t K, float ts, uint8_t* packed,
                        uint8_t* sblk, cudaStream_t stream) {
-    // 128-row tiles (whole scale atoms) measured faster than 64-row ones at every benchmarked size;
-    // the half-atom variant is kept for grids that would otherwise leave most SMs idle
+    // 128-row tiles (whole scale atoms: 512-byte scale stores) when every resident CTA gets many of them; 64-row
+    // tiles (half atoms) when the count per CTA is small, where one tile more or less per CTA is a visible share
     const int64_t tiles128 = ((K + QT_COLS - 1) / QT_COLS) * (pad128(R) / 128);
     const T* xp = static_cast<const T*>(x);
     if (g_quant_rows == 64) return launch_quant_nvfp4_rows<T, 64>(xp, R, K, ts, packed, sblk, stream);
     if (g_quant_rows == 128) return launch_quant_nvfp4_rows<T, 128>(xp, R, K, ts, packed, sblk, stream);
-    if (tiles128 < 148) return launch_quant_nvfp4_rows<T, 64>(xp, R, K, ts, packed, sblk, stream);
+    const int64_t slots = quant_slots((int)sizeof(T));
+    const int64_t rounds = (tiles128 + slots - 1) / slots;      // tiles of the busiest CTA
+    // more than 4 % of the busiest CTA's time idle elsewhere (8192 x 8192: 2048 tiles on 592 CTAs = 4 rounds for 3.46)
+    if (rounds * slots * 100 > tiles128 * 104) return launch_quant_nvfp4_rows<T, 64>(xp, R, K, ts, packed, sblk, stream);
     return launch_quant_nvfp4_rows<T, 128>(xp, R, K, ts, packed, sblk, stream);
 }
 
@@ -640,7 +661,9 @@ int swiglu_quant_nvfp4(const void* gu, int64_t R, int64_t K, int in_dtype, uint8
         fprintf(stderr, "thor_fp4: tfp4_swiglu_quant needs a 16-byte aligned f16/bf16 input, packed 4-byte, sblk 8-byte aligned\n");
         return TFP4_ERR_BAD_ARG;
     }
-    dim3 grid((unsigned)((K + QT_COLS - 1) / QT_COLS), (unsigned)(pad128(R) / 128));
+    const int64_t tiles_x = (K + QT_COLS - 1) / QT_COLS, n_tiles = tiles_x * (pad128(R) / 128);
+    const int64_t slots = quant_slots(2);
+    dim3 grid((unsigned)(n_tiles < slots ? n_tiles : slots));
     cudaLaunchAttribute attr[1];       // dependent of the gate/up GEMM before it (waits for it before its first load)
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -652,10 +675,10 @@ int swiglu_quant_nvfp4(const void* gu, int64_t R, int64_t K, int in_dtype, uint8
     cfg.numAttrs = g_quant_pdl ? 1 : 0;
     if (in_dtype == IN_BF16)
         TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<__nv_bfloat16, 0, 128, true>,
-                                   static_cast<const __nv_bfloat16*>(gu), R, K, 1.0f, packed, sblk));
+                                   static_cast<const __nv_bfloat16*>(gu), R, K, 1.0f, packed, sblk, tiles_x, n_tiles));
     else
         TFP4_CK(cudaLaunchKernelEx(&cfg, quant_nvfp4_kernel<__half, 0, 128, true>, static_cast<const __half*>(gu), R, K, 1.0f,
-                                   packed, sblk));
+                                   packed, sblk, tiles_x, n_tiles));
     return TFP4_OK;
 }
 
