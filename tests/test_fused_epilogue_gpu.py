@@ -264,3 +264,66 @@ def test_act_quant_mx8_bias_reads_stay_inside_the_vector():
     torch.cuda.synchronize()
     dec = orc.dequantize_mx(packed.cpu().numpy(), sblk.cpu().numpy(), "mxfp8", R, N)
     assert np.isfinite(dec).all()
+
+
+# ------------------------------------------------------------------------------------------ push epilogue (one GPU)
+@gpu
+@pytest.mark.parametrize("od", ["f32", "bf16"])
+@pytest.mark.parametrize("M,N,K,owners", [(512, 384, 1024, 2), (1024, 1000, 512, 4), (768, 256, 256, 8), (300, 264, 512, 2)])
+def test_gemm_push_fills_every_owners_staging_rows(od, M, N, K, owners):
+    """tfp4_gemm_push on one GPU: the 'owners' are buffers of this process, so the destination logic (which 32-row
+    block goes to which owner, at which row of its slot) is checked without NVLink: owner o must hold exactly the rows
+    [o * rows, (o + 1) * rows) of the plain GEMM's output, bit for bit, and nothing outside its slot is touched."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    L = _ext.device_lib()
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = torch.randn(N, K, device="cuda", generator=g) * 0.05
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    dt = _ext.OUT_TORCH[od]
+    rows = -(-M // owners)
+    rows = -(-rows // 32) * 32                                   # rows per owner: a multiple of 32 covering M
+    stage = [torch.full((rows + 8, N), 7.0, dtype=dt, device="cuda") for _ in range(owners)]
+    dest = (ctypes.c_void_p * owners)(*[t.data_ptr() for t in stage])
+    L.tfp4_set_splits(1)
+    try:
+        rc = L.tfp4_gemm_push(a.packed.data_ptr(), a.sblk.data_ptr(), ctypes.c_float(1.0), b.packed.data_ptr(), b.sblk.data_ptr(),
+                              ctypes.c_float(b.tensor_scale), dest, owners, rows, M, N, K, _ext.OUT_DTYPE[od], _ext.stream())
+        assert rc == 0
+        ref = torch.empty(M, N, dtype=dt, device="cuda")
+        L.tfp4_set_pair_mode(2)                                  # the same kernel for the plain output
+        ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, ref, M, N, K, od)
+        torch.cuda.synchronize()
+    finally:
+        L.tfp4_set_splits(0)
+        L.tfp4_set_pair_mode(-1)
+    assert _ext.status() == 0
+    for o in range(owners):
+        have = max(0, min(rows, M - o * rows))
+        assert torch.equal(stage[o][:have], ref[o * rows: o * rows + have]), f"owner {o}"
+        assert (stage[o][have:] == 7.0).all(), f"owner {o}: rows beyond its share were written"
+    # and the owner-side sum over staged partials
+    slots = torch.stack([t[:rows] for t in stage[:2]]).contiguous()
+    for out_dt, code in ((torch.float32, 2), (torch.bfloat16, 1)):
+        out = torch.empty(rows, N, dtype=out_dt, device="cuda")
+        if (rows * N) % 8 == 0:
+            assert L.tfp4_sum_slots(slots.data_ptr(), 2, rows, N, _ext.IN_DTYPE[dt], out.data_ptr(), code, _ext.stream()) == 0
+            torch.cuda.synchronize()
+            want = (slots[0].float() + slots[1].float()).to(out_dt)
+            assert torch.equal(out, want)
+
+
+@gpu
+def test_gemm_push_argument_checks():
+    from thor_fp4 import _ext
+    L = _ext.device_lib()
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    dest = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
+    args = lambda n, rows, od: (buf.data_ptr(), buf.data_ptr(), ctypes.c_float(1.0), buf.data_ptr(), buf.data_ptr(), ctypes.c_float(1.0),
+                                dest, n, rows, 64, 64, 64, od, _ext.stream())
+    assert L.tfp4_gemm_push(*args(2, 48, 2)) == -7        # rows per owner not a multiple of 32
+    assert L.tfp4_gemm_push(*args(2, 16 * 2, 0)) == -7    # f16 partials are not offered
+    assert L.tfp4_gemm_push(*args(1, 32, 2)) == -7        # one owner of 32 rows does not cover 64 tokens
+    assert L.tfp4_gemm_push(*args(9, 32, 2)) == -7        # more owners than the kernel's map table holds
