@@ -54,6 +54,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-mlp", action="store_true", help="skip the SwiGLU-block measurement added to the line")
+    ap.add_argument("--graph", action="store_true",
+                    help="several ranks: also capture the SwiGLU block, with its NCCL reduce-scatter, in a CUDA graph and time the "
+                         "replay (on one rank the captured block is always timed)")
     ap.add_argument("--ablate", action="store_true",
                     help="time the GEMM with parts of the kernel switched off through the library's test hooks and print a table")
     ap.add_argument("--plain-launch", action="store_true",
@@ -620,16 +623,41 @@ def measure_mlp_block(args, dev, rank, world, steps):
                    "note": "every rank ends with its M/P token rows of the output, fully summed"}
         # and with the transfer inside the down projection (TMA stores into the owners' staging buffers, local sum)
         tp.exchange = "push"
-        yp = tp(xs[0])
-        torch.cuda.synchronize()
-        err_p = None
-        if rank == 0:
-            err_p = float((yp[:1024].float() - ref).norm() / ref.norm())
-        ms_p = timed(lambda i: tp(xs[i % 2]), steps)
-        push = {"exchange": tp.exchange_name(), "ms_per_block": ms_p, "tflops": 6.0 * M * H * I / (ms_p * 1e-3) / 1e12,
-                "rel_error_vs_unsharded_block": err_p,
-                "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * (4 if reduce_dtype == "f32" else 2)}
+        try:
+            yp = tp(xs[0])          # the set-up (CUDA IPC) succeeds or fails on all ranks together
+            torch.cuda.synchronize()
+            err_p = None
+            if rank == 0:
+                err_p = float((yp[:1024].float() - ref).norm() / ref.norm())
+            ms_p = timed(lambda i: tp(xs[i % 2]), steps)
+            push = {"exchange": tp.exchange_name(), "ms_per_block": ms_p, "tflops": 6.0 * M * H * I / (ms_p * 1e-3) / 1e12,
+                    "rel_error_vs_unsharded_block": err_p,
+                    "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * (4 if reduce_dtype == "f32" else 2)}
+        except RuntimeError as e:
+            push = {"unavailable": str(e)[:300]}
         tp.close()
+        tp.exchange = "all_reduce"
+    # the per-rank block captured in a CUDA graph and replayed (the form the benchmark configuration names): one rank
+    # -> the three kernels; several ranks -> the reduce-scatter exchange, whose NCCL collective is captured with them
+    # (the push exchange's staging set alternates from call to call, which a captured graph cannot do)
+    graph = None
+    if args.graph or world == 1:
+        try:
+            if world > 1:
+                tp.exchange = "reduce_scatter"
+            xg = xs[0].clone()
+            for _ in range(2):
+                tp(xg)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                yg = tp(xg)
+            ms_g = timed(lambda i: g.replay(), steps)
+            graph = {"exchange": tp.exchange_name() if world > 1 else None, "ms_per_block": ms_g,
+                     "tflops": 6.0 * M * H * I / (ms_g * 1e-3) / 1e12}
+            del g, yg
+        except Exception as e:  # noqa: BLE001
+            graph = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         tp.exchange = "all_reduce"
     if _ext.status() != 0:
         raise RuntimeError(f"device status word {_ext.status()}")
@@ -642,7 +670,7 @@ def measure_mlp_block(args, dev, rank, world, steps):
            "ms_exchange_alone": ms_xchg,
            "exchange_share": (None if world == 1 else max(0.0, 1.0 - ms_local / ms)),
            "rel_error_vs_unsharded_block": err,
-           "reduce_scatter": scatter, "push": push,
+           "reduce_scatter": scatter, "push": push, "cuda_graph": graph,
            "fused_epilogue": bool(getattr(tp.local, "fuse_epilogue", False))}
     del tp, xs
     torch.cuda.empty_cache()
@@ -676,7 +704,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=4))
 
     def barrier():
         if world > 1:

@@ -374,3 +374,33 @@ def test_gemm_bias_reads_stay_inside_the_vector(M, od):
         assert torch.isfinite(out.float()).all(), "NaN bait leaked in: out-of-bounds bias read"
         ref = _oracle_out(a, b, bias.cpu().numpy())
         assert _fro(out.float().cpu().numpy(), ref) < (TOL if od == "f32" else 3e-3)
+
+
+@gpu
+@pytest.mark.parametrize("shape", [(1300, 1104, 512), (2048, 768, 256), (700, 2600, 320)])
+def test_tile_order_does_not_change_a_bit(shape):
+    """The two-CTA kernel walks its output tiles either with the token tiles fastest or in bands of gm token tiles
+    (chosen by the host from the L2 footprint for large activations): every order must give the same bits, also when
+    the last band is short (6 or 9 token tiles in bands of 4 or 5) and when a band is wider than the matrix."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = shape
+    x, w = _operands(M, N, K, seed=N)
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    bias = torch.randn(N, device="cuda") * 0.01
+    L = _ext.core()
+    outs = {}
+    try:
+        for gm in (-1, 1, 2, 4, 5, 64):
+            L.tfp4_set_raster(gm)
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, "bf16", bias=bias)
+            torch.cuda.synchronize()
+            outs[gm] = out
+    finally:
+        L.tfp4_set_raster(0)
+    assert _ext.status() == 0
+    assert torch.isfinite(outs[-1].float()).all()
+    for gm, out in outs.items():
+        assert torch.equal(out, outs[-1]), f"gm={gm}"

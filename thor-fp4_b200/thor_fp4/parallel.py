@@ -64,23 +64,31 @@ class _PushStaging:
         base = ctypes.c_void_p()
         handle = ctypes.create_string_buffer(64)
         rc = L.tfp4_peer_alloc(2 * self.set_bytes, ctypes.byref(base), handle)
-        if rc != 0:
-            raise RuntimeError(f"tfp4_peer_alloc rc={rc}")
-        self.base = base.value
+        self.base = base.value if rc == 0 else None
+        self.peer_base, self._opened = [], []
+        # every rank takes part in every collective below whatever happened locally, and all ranks learn together
+        # whether the set-up worked: a rank that raised alone would leave the others waiting in a collective
         mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device=device)
         allh = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(allh, mine, group=group)
-        self.peer_base, self._opened = [], []
+        ok = rc == 0
         for p in range(world):
             if p == rank:
                 self.peer_base.append(self.base)
                 continue
             ptr = ctypes.c_void_p()
-            rc = L.tfp4_peer_open(bytes(allh[p].cpu().tolist()), ctypes.byref(ptr))
-            if rc != 0:
-                raise RuntimeError(f"tfp4_peer_open of rank {p}'s staging buffer rc={rc}")
-            self.peer_base.append(ptr.value)
-            self._opened.append(ptr.value)
+            if ok and L.tfp4_peer_open(bytes(allh[p].cpu().tolist()), ctypes.byref(ptr)) == 0:
+                self.peer_base.append(ptr.value)
+                self._opened.append(ptr.value)
+            else:
+                ok = False
+                self.peer_base.append(None)
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            self.close()
+            raise RuntimeError("push exchange: sharing the staging buffers over CUDA IPC failed on at least one rank "
+                               "(tfp4_peer_alloc / tfp4_peer_open; see the library's message on stderr)")
         slot = rank * rows * hidden * self.esize
         self.dest = [(ctypes.c_void_p * world)(*[self.peer_base[o] + k * self.set_bytes + slot for o in range(world)])
                      for k in range(2)]
