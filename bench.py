@@ -602,7 +602,7 @@ def measure_mlp_block(args, dev, rank, world, steps):
     ms = timed(lambda i: tp(xs[i % 2]), steps)
     ms_local = timed(lambda i: tp.local(xs[i % 2]), steps)          # the rank's GEMMs alone, nothing exchanged
     ms_xchg = None
-    scatter = push = None
+    scatter = push = copy = None
     if world > 1:
         buf = torch.zeros(M, H, dtype=torch.float32 if reduce_dtype == "f32" else torch.bfloat16, device=dev)
         ms_xchg = timed(lambda i: dist.all_reduce(buf), steps)          # the exchange alone (NCCL all-reduce of the partials)
@@ -635,6 +635,22 @@ def measure_mlp_block(args, dev, rank, world, steps):
                     "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * (4 if reduce_dtype == "f32" else 2)}
         except RuntimeError as e:
             push = {"unavailable": str(e)[:300]}
+        tp.close()
+        # and with the transfer on the copy engines beside the next token chunk's GEMMs
+        tp.exchange = "copy"
+        try:
+            yc = tp(xs[0])
+            torch.cuda.synchronize()
+            err_c = None
+            if rank == 0:
+                rows = tp.owned_rows(M)
+                rows = rows[rows < 1024].to(dev)
+                err_c = float((yc[: rows.numel()].float() - ref[rows]).norm() / ref[rows].norm()) if rows.numel() else None
+            ms_c = timed(lambda i: tp(xs[i % 2]), steps)
+            copy = {"exchange": tp.exchange_name(), "ms_per_block": ms_c, "tflops": 6.0 * M * H * I / (ms_c * 1e-3) / 1e12,
+                    "rel_error_vs_unsharded_block": err_c}
+        except RuntimeError as e:
+            copy = {"unavailable": str(e)[:300]}
         tp.close()
         tp.exchange = "all_reduce"
     # the per-rank block captured in a CUDA graph and replayed (the form the benchmark configuration names): one rank
@@ -670,7 +686,7 @@ def measure_mlp_block(args, dev, rank, world, steps):
            "ms_exchange_alone": ms_xchg,
            "exchange_share": (None if world == 1 else max(0.0, 1.0 - ms_local / ms)),
            "rel_error_vs_unsharded_block": err,
-           "reduce_scatter": scatter, "push": push, "cuda_graph": graph,
+           "reduce_scatter": scatter, "push": push, "copy": copy, "cuda_graph": graph,
            "fused_epilogue": bool(getattr(tp.local, "fuse_epilogue", False))}
     del tp, xs
     torch.cuda.empty_cache()

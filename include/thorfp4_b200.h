@@ -196,7 +196,10 @@ int tfp4_swiglu_gemm(const void* packedA, const void* sblkA, float tsA, const vo
  *   in_dtype 0 f32 / 2 bf16, out_dtype 0 f16 / 1 bf16 / 2 f32.  Run it after every rank's push has completed (a barrier
  *   on the host or a collective in stream order between the two calls).
  * tfp4_peer_alloc / _open / _close / _free: a device buffer with a 64-byte CUDA IPC handle that the other processes of
- *   the node open to obtain a pointer valid on their device. */
+ *   the node open to obtain a pointer valid on their device.
+ * tfp4_peer_copy: one device-to-device copy in stream order (cudaMemcpyAsync); towards a mapped peer buffer it goes over
+ *   NVLink through the copy engines and uses no SM - the transfer of the "copy" exchange, which runs beside the next
+ *   token chunk's GEMMs. */
 int tfp4_gemm_push(const void* packedA, const void* sblkA, float tsA, const void* packedB, const void* sblkB, float tsB,
                    void* const* dest, int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K,
                    int out_dtype, void* stream);
@@ -204,6 +207,7 @@ int tfp4_sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dty
 int tfp4_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 int tfp4_peer_open(const unsigned char* handle64, void** ptr);
 int tfp4_peer_close(void* ptr);
+int tfp4_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 int tfp4_peer_free(void* ptr);
 
 /* Additions: status word of the current device (0 = healthy; otherwise the role

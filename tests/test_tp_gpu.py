@@ -57,6 +57,18 @@ WORKER = textwrap.dedent('''
         rows_p = tpush.owned_rows(M).cuda()
         good = good and yp.shape == (M // 2, H) and ((yp - yi[rows_p]).norm() / yi[rows_p].norm()).item() < 1e-6
         good = good and ((tpush.gather(yp, M) - yi).norm() / yi.norm()).item() < 1e-6
+    # ... and with its transfer on the copy engines, chunk by chunk beside the next chunk's GEMMs
+    tcopy = TensorParallelGatedMLP(H, I, device="cuda", reduce_dtype="f32", chunks=3, exchange="copy")
+    tcopy.load_full_weights(wg.cuda(), wu.cuda(), wd.cuda())
+    for it in range(3):
+        xi = x if it != 1 else (x * 0.5).bfloat16()
+        yi = tp(xi).clone()
+        yc = tcopy(xi).clone()
+        rows_c = tcopy.owned_rows(M).cuda()
+        good = good and yc.shape == (M // 2, H) and ((yc - yi[rows_c]).norm() / yi[rows_c].norm()).item() < 1e-6
+        good = good and ((tcopy.gather(yc, M) - yi).norm() / yi.norm()).item() < 1e-6
+    torch.cuda.synchronize()
+    tcopy.close()
     okp = torch.tensor([int(good)], device="cuda")
     dist.all_reduce(okp, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()

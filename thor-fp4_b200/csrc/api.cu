@@ -35,6 +35,7 @@ int sum_slots(const void*, int, int64_t, int64_t, int, void*, int, cudaStream_t)
 int peer_alloc(size_t, void**, unsigned char*);
 int peer_open(const unsigned char*, void**);
 int peer_close(void*);
+int peer_copy(void*, const void*, size_t, cudaStream_t);
 int peer_free(void*);
 int gemm_noalloc(const void*, const void*, const void*, const void*, float, const float*, void*, int64_t, int64_t,
                  int64_t, int, cudaStream_t);
@@ -201,6 +202,7 @@ int tfp4_sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dty
 int tfp4_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64) { return tfp4::peer_alloc(bytes, ptr, handle64); }
 int tfp4_peer_open(const unsigned char* handle64, void** ptr) { return tfp4::peer_open(handle64, ptr); }
 int tfp4_peer_close(void* ptr) { return tfp4::peer_close(ptr); }
+int tfp4_peer_copy(void* dst, const void* src, size_t bytes, void* stream) { return tfp4::peer_copy(dst, src, bytes, S(stream)); }
 int tfp4_peer_free(void* ptr) { return tfp4::peer_free(ptr); }
 
 int tfp4_swiglu_quant(const void* gu, int64_t R, int64_t I, int in_dtype, uint8_t* packed, uint8_t* sblk, void* stream) {

@@ -118,6 +118,15 @@ int peer_open(const unsigned char* handle64, void** ptr) {
     return TFP4_OK;
 }
 
+// One device-to-device copy on the stream (a peer destination goes over NVLink through the copy engines: no SM is used,
+// so it runs beside a GEMM that occupies every SM).  One cudaMemcpyAsync per call.
+int peer_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream) {
+    if (!dst || !src) return TFP4_ERR_BAD_ARG;
+    if (bytes == 0) return TFP4_OK;
+    TFP4_CK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream));
+    return TFP4_OK;
+}
+
 int peer_close(void* ptr) {
     if (ptr) TFP4_CK(cudaIpcCloseMemHandle(ptr));
     return TFP4_OK;

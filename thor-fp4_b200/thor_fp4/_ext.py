@@ -67,6 +67,7 @@ SIGNATURES = {
     "tfp4_peer_alloc": (c_int, [ctypes.c_size_t, ctypes.POINTER(c_void), ctypes.c_char_p]),
     "tfp4_peer_open": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_void)]),
     "tfp4_peer_close": (c_int, [c_void]),
+    "tfp4_peer_copy": (c_int, [c_void, c_void, ctypes.c_size_t, c_void]),
     "tfp4_peer_free": (c_int, [c_void]),
     "tfp4_status": (c_int, []),
     "tfp4_clear_status": (None, []),

@@ -125,6 +125,13 @@ class TensorParallelGatedMLP(nn.Module):
                         on the next tile), then one small collective orders the ranks and a local kernel sums the
                         staged partials.  No collective kernel competes with the GEMM for SMs.  Rank r ends with rows
                         [r M/P, (r+1) M/P); M must divide by 32 P.
+      "copy"            the reduce-scatter with its transfer on the copy engines: the tokens are cut into chunks, each
+                        chunk's f32 partial product is written locally by the down projection and then copied, slice by
+                        slice (one cudaMemcpyAsync per owner, on a second stream), into the owners' staging buffers over
+                        NVLink while the tensor cores work on the next chunk; copy engines use no SM, so the transfer
+                        really runs beside the GEMMs and only the last chunk's copies are exposed.  Then the same
+                        4-byte collective and local sum as "push".  Row ownership as "reduce_scatter" (rank r owns the
+                        r-th 1/P of every chunk).
     The tokens are cut into `chunks` pieces: the exchange of one piece runs on the collective's own stream while
     this rank's GEMMs of the next piece run."""
 
@@ -132,8 +139,9 @@ class TensorParallelGatedMLP(nn.Module):
                  reduce_dtype: str = "f32", weight_std: float | None = 0.02, local: nn.Module | None = None,
                  chunks: int = 4, exchange: str = "all_reduce"):
         super().__init__()
-        if exchange not in ("all_reduce", "reduce_scatter", "push"):
-            raise ValueError(f"exchange={exchange!r}: pick 'all_reduce' | 'reduce_scatter' | 'push'")
+        if exchange not in ("all_reduce", "reduce_scatter", "push", "copy"):
+            raise ValueError(f"exchange={exchange!r}: pick 'all_reduce' | 'reduce_scatter' | 'push' | 'copy'")
+        self._side = None
         self._push: dict = {}
         self.group = group
         self.exchange = exchange
@@ -158,6 +166,10 @@ class TensorParallelGatedMLP(nn.Module):
         return self
 
     def exchange_name(self) -> str:
+        if self.exchange == "copy":
+            return (f"reduce-scatter by token rows on the copy engines: {self.chunks} token chunks, each chunk's partial rows "
+                    "copied into the owners' staging buffers over NVLink (cudaMemcpyAsync on a second stream) beside the next "
+                    "chunk's GEMMs, one 4-byte all-reduce as the barrier, local sum")
         if self.exchange == "push":
             return ("reduce-scatter by token rows inside the down projection: TMA stores of the partial tiles into the "
                     "owners' staging buffers over NVLink from the GEMM epilogue, one 4-byte all-reduce as the barrier, local sum")
@@ -170,7 +182,7 @@ class TensorParallelGatedMLP(nn.Module):
         n = self.chunks if (M >= 256 * self.chunks and on_device) else 1
         step = -(-M // n)
         step = -(-step // 256) * 256
-        if self.exchange == "reduce_scatter" and M % self.world != 0:
+        if self.exchange in ("reduce_scatter", "copy") and M % self.world != 0:
             raise ValueError(f"reduce_scatter needs the token count ({M}) to divide by the world size ({self.world})")
         return [(r0, min(M, r0 + step)) for r0 in range(0, M, step)]
 
@@ -239,11 +251,55 @@ class TensorParallelGatedMLP(nn.Module):
         assert rc == 0, f"tfp4_sum_slots rc={rc}"
         return ys
 
+    def _forward_copy(self, x: torch.Tensor) -> torch.Tensor:
+        m, L = self.local, _ext.device_lib()
+        M, H = x.shape[0], self.hidden
+        bounds = self._chunk_bounds(M, True)
+        if any((r1 - r0) % self.world for r0, r1 in bounds):
+            raise ValueError(f"exchange='copy' needs every token chunk to divide by the world size ({self.world})")
+        rows = M // self.world
+        dt = _ext.OUT_TORCH[m.out_dtype]
+        if dt not in (torch.float32, torch.bfloat16):
+            raise ValueError("exchange='copy' stages f32 or bf16 partials")
+        st = self._push.get((M, dt, "copy"))
+        if st is None:
+            stg = _PushStaging(self.group, self.world, self.rank, rows, H, dt, x.device)
+            st = self._push[(M, dt, "copy")] = (stg, torch.empty(rows, H, dtype=dt, device=x.device),
+                                                torch.zeros(1, dtype=torch.int32, device=x.device),
+                                                torch.empty(M, H, dtype=dt, device=x.device))
+        stg, ys, flag, y = st
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        side, main = self._side, torch.cuda.current_stream()
+        k = stg.turn
+        stg.turn ^= 1
+        row_bytes = H * stg.esize
+        pos = 0
+        for r0, r1 in bounds:
+            m(x[r0:r1], out=y[r0:r1])                                   # this chunk's partial product, local
+            ev = torch.cuda.Event()
+            ev.record(main)
+            side.wait_event(ev)
+            n = (r1 - r0) // self.world
+            for o in range(self.world):                                 # owner o takes the o-th 1/P of the chunk
+                dst = stg.dest[k][o] + pos * row_bytes
+                src = y.data_ptr() + (r0 + o * n) * row_bytes
+                rc = L.tfp4_peer_copy(dst, src, n * row_bytes, side.cuda_stream)
+                assert rc == 0, f"tfp4_peer_copy rc={rc}"
+            pos += n
+        main.wait_stream(side)
+        # every rank's copies have landed once every rank has got here: a 4-byte collective in stream order
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        rc = L.tfp4_sum_slots(stg.local_set[k], self.world, rows, H, _ext.IN_DTYPE[dt], ys.data_ptr(),
+                              _ext.OUT_DTYPE[m.out_dtype], _ext.stream())
+        assert rc == 0, f"tfp4_sum_slots rc={rc}"
+        return ys
+
     def close(self):
-        """Release the IPC mappings and staging buffers of the push exchange (call on every rank before the process
-        group goes away; nothing to do for the other exchanges)."""
-        for stg, _, _ in self._push.values():
-            stg.close()
+        """Release the IPC mappings and staging buffers of the push and copy exchanges (call on every rank before the
+        process group goes away; nothing to do for the other exchanges)."""
+        for entry in self._push.values():
+            entry[0].close()
         self._push = {}
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -251,6 +307,8 @@ class TensorParallelGatedMLP(nn.Module):
             return self.local(x)
         if self.exchange == "push":
             return self._forward_push(x)
+        if self.exchange == "copy":
+            return self._forward_copy(x)
         M = x.shape[0]
         bounds = self._chunk_bounds(M, x.is_cuda)
         scatter = self.exchange == "reduce_scatter"
