@@ -191,7 +191,9 @@ int tfp4_swiglu_gemm(const void* packedA, const void* sblkA, float tsA, const vo
  *   rank's rows for owner o go, a row-major (rows_per_dest, N) matrix of out_dtype (1 bf16 or 2 f32) in owner o's memory,
  *   mapped into this process (tfp4_peer_open; dest[own rank] is local memory).  Owner o holds token rows
  *   [o * rows_per_dest, (o + 1) * rows_per_dest); rows_per_dest % 32 == 0.  The stores are TMA stores issued by the
- *   epilogue warps while the tensor cores work on the next tile, so the NVLink transfer overlaps the GEMM.
+ *   epilogue warps while the tensor cores work on the next tile, so the NVLink transfer overlaps the GEMM.  first_dest:
+ *   the owner whose token tiles this rank computes first (pass own rank + 1): every rank then walks the owners in a
+ *   different rotation and no owner's links take every rank's stores at once.
  * tfp4_sum_slots: out (rows, N) = sum over the n staged partials stage[s] (s ascending: the same order on every rank),
  *   in_dtype 0 f32 / 2 bf16, out_dtype 0 f16 / 1 bf16 / 2 f32.  Run it after every rank's push has completed (a barrier
  *   on the host or a collective in stream order between the two calls).
@@ -201,7 +203,7 @@ int tfp4_swiglu_gemm(const void* packedA, const void* sblkA, float tsA, const vo
  *   NVLink through the copy engines and uses no SM - the transfer of the "copy" exchange, which runs beside the next
  *   token chunk's GEMMs. */
 int tfp4_gemm_push(const void* packedA, const void* sblkA, float tsA, const void* packedB, const void* sblkB, float tsB,
-                   void* const* dest, int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K,
+                   void* const* dest, int n_dest, int64_t rows_per_dest, int first_dest, int64_t M, int64_t N, int64_t K,
                    int out_dtype, void* stream);
 int tfp4_sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dtype, void* out, int out_dtype, void* stream);
 int tfp4_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);

@@ -290,7 +290,8 @@ def test_gemm_push_fills_every_owners_staging_rows(od, M, N, K, owners):
     L.tfp4_set_splits(1)
     try:
         rc = L.tfp4_gemm_push(a.packed.data_ptr(), a.sblk.data_ptr(), ctypes.c_float(1.0), b.packed.data_ptr(), b.sblk.data_ptr(),
-                              ctypes.c_float(b.tensor_scale), dest, owners, rows, M, N, K, _ext.OUT_DTYPE[od], _ext.stream())
+                              ctypes.c_float(b.tensor_scale), dest, owners, rows, (M + N) % owners, M, N, K, _ext.OUT_DTYPE[od],
+                              _ext.stream())
         assert rc == 0
         ref = torch.empty(M, N, dtype=dt, device="cuda")
         L.tfp4_set_pair_mode(2)                                  # the same kernel for the plain output
@@ -322,7 +323,7 @@ def test_gemm_push_argument_checks():
     buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     dest = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
     args = lambda n, rows, od: (buf.data_ptr(), buf.data_ptr(), ctypes.c_float(1.0), buf.data_ptr(), buf.data_ptr(), ctypes.c_float(1.0),
-                                dest, n, rows, 64, 64, 64, od, _ext.stream())
+                                dest, n, rows, 0, 64, 64, 64, od, _ext.stream())
     assert L.tfp4_gemm_push(*args(2, 48, 2)) == -7        # rows per owner not a multiple of 32
     assert L.tfp4_gemm_push(*args(2, 16 * 2, 0)) == -7    # f16 partials are not offered
     assert L.tfp4_gemm_push(*args(1, 32, 2)) == -7        # one owner of 32 rows does not cover 64 tokens

@@ -29,8 +29,8 @@ int gemm_swiglu_nvfp4(const void*, const void*, const void*, const void*, float,
                       cudaStream_t);
 int gemm_mx8_out(const void*, const void*, const void*, const void*, float, const float*, int, void*, void*, int64_t,
                  int64_t, int64_t, cudaStream_t);
-int gemm_push(const void*, const void*, const void*, const void*, float, void* const*, int, int64_t, int64_t, int64_t, int64_t,
-              int, cudaStream_t);
+int gemm_push(const void*, const void*, const void*, const void*, float, void* const*, int, int64_t, int, int64_t, int64_t,
+              int64_t, int, cudaStream_t);
 int sum_slots(const void*, int, int64_t, int64_t, int, void*, int, cudaStream_t);
 int peer_alloc(size_t, void**, unsigned char*);
 int peer_open(const unsigned char*, void**);
@@ -193,8 +193,9 @@ int tfp4_swiglu_gemm(const void* pA, const void* sA, float tsA, const void* pW, 
 }
 
 int tfp4_gemm_push(const void* pA, const void* sA, float tsA, const void* pB, const void* sB, float tsB, void* const* dest,
-                   int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K, int out_dtype, void* stream) {
-    return tfp4::gemm_push(pA, sA, pB, sB, tsA * tsB, dest, n_dest, rows_per_dest, M, N, K, out_dtype, S(stream));
+                   int n_dest, int64_t rows_per_dest, int first_dest, int64_t M, int64_t N, int64_t K, int out_dtype,
+                   void* stream) {
+    return tfp4::gemm_push(pA, sA, pB, sB, tsA * tsB, dest, n_dest, rows_per_dest, first_dest, M, N, K, out_dtype, S(stream));
 }
 int tfp4_sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dtype, void* out, int out_dtype, void* stream) {
     return tfp4::sum_slots(stage, n, rows, N, in_dtype, out, out_dtype, S(stream));

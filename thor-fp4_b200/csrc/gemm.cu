@@ -63,6 +63,7 @@ struct GemmParams {
     int32_t epi_act;         // MXFP8 epilogue: 0 identity, 1 gelu, 2 silu
     int32_t raster_gm;       // two-CTA kernel: tile order (see duo_tile_coords)
     int64_t push_rows;       // push epilogue: token rows per owning rank
+    int64_t m_shift;         // two-CTA kernel: rotation of the token tiles (push epilogue: a different one per rank)
     const float* bias;       // may be null
     float alpha;
     int64_t M, N, K;
@@ -1032,6 +1033,7 @@ struct EpilogueSpec {
     void* const* push_dest = nullptr;   // mode 3: per owning rank, where this rank's partial rows for that owner go
     int push_ranks = 0;
     int64_t push_rows = 0;              // token rows per owner
+    int push_first = 0;                 // the owner this rank's first tiles go to (ranks start at different owners)
 };
 
 // tensor maps of the push epilogue's destinations, cached like the output maps
@@ -1268,6 +1270,11 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
     // (16384 x 8192 at K = 8192: 510 -> 469 us; the SwiGLU block's down projection, K = 28672: 2035 -> 1727 us).
     // Bands of gm token tiles whose codes and scales take about 34 MB keep the band resident while the weights stream.
     p.push_rows = es ? es->push_rows : 0;
+    p.m_shift = 0;
+    if (es && es->epi == 3) {       // start at the first token tile of owner `push_first`
+        const int64_t tiles_m256 = (M + 255) / 256;
+        p.m_shift = ((int64_t)es->push_first * es->push_rows / 256) % tiles_m256;
+    }
     p.raster_gm = 0;
     if (g_raster_gm > 0) {
         p.raster_gm = g_raster_gm;
@@ -1441,7 +1448,8 @@ int gemm_mx8_out(const void* packedA, const void* sblkA, const void* packedB, co
 // (f32 or bf16) in owner o's memory (peer-mapped; dest[own rank] is local).  The stores are TMA stores issued by the
 // epilogue warps while the main loop runs; sum_slots on the owner completes the reduction.
 int gemm_push(const void* packedA, const void* sblkA, const void* packedB, const void* sblkB, float alpha, void* const* dest,
-              int n_dest, int64_t rows_per_dest, int64_t M, int64_t N, int64_t K, int out_dtype, cudaStream_t stream) {
+              int n_dest, int64_t rows_per_dest, int first_dest, int64_t M, int64_t N, int64_t K, int out_dtype,
+              cudaStream_t stream) {
     if (n_dest < 1 || n_dest > PUSH_MAX_RANKS || rows_per_dest <= 0 || (rows_per_dest % 32) != 0 || (int64_t)n_dest * rows_per_dest < M ||
         dest == nullptr || (out_dtype != OUT_F32 && out_dtype != OUT_BF16)) {
         fprintf(stderr, "thor_fp4: gemm_push needs 1..%d destinations, rows per destination a multiple of 32 covering M, f32 or bf16 partials\n",
@@ -1458,6 +1466,7 @@ int gemm_push(const void* packedA, const void* sblkA, const void* packedB, const
     es.push_dest = dest;
     es.push_ranks = n_dest;
     es.push_rows = rows_per_dest;
+    es.push_first = (first_dest >= 0 && first_dest < n_dest) ? first_dest : 0;
     return gemm_block_scaled_ws(0, packedA, sblkA, packedB, sblkB, alpha, nullptr, dest[0], M, N, K, out_dtype, stream, nullptr, &es);
 }
 

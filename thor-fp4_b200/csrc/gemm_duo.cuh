@@ -320,7 +320,10 @@ __device__ __forceinline__ uint32_t duo_kblock_mx(uint32_t on, uint32_t accumula
 // Tile index -> (token tile mt, feature tile nt).  gm <= 0: token tiles fastest (a wave of CTA pairs shares few weight
 // tiles and spreads over many token tiles).  gm > 0: bands of gm token tiles, feature tiles fastest inside a band, so a
 // wave covers about gm x (pairs / gm) tiles and every operand tile in flight is shared by several pairs.
-__device__ __forceinline__ void duo_tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int gm, int64_t& mt, int64_t& nt) {
+// m_shift rotates the token tiles (mt -> (mt + m_shift) mod tiles_m): the push epilogue gives every rank a different
+// rotation, so that at any time the ranks store into different owners' memory instead of all into the same one.
+__device__ __forceinline__ void duo_tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int gm, int64_t m_shift,
+                                                int64_t& mt, int64_t& nt) {
     if (gm <= 0) {
         nt = tile / tiles_m;
         mt = tile - nt * tiles_m;
@@ -332,6 +335,8 @@ __device__ __forceinline__ void duo_tile_coords(int64_t tile, int64_t tiles_m, i
         nt = r / rows;
         mt = m0 + (r - nt * rows);
     }
+    mt += m_shift;
+    if (mt >= tiles_m) mt -= tiles_m;
 }
 
 template <int V> struct IntTag { static constexpr int value = V; };
@@ -507,7 +512,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const uint32_t my_dst = (lane == 0) ? smem_u32(sX) : smem_u32(sWh);
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
             int64_t nt, mt;
-            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, p.m_shift, mt, nt);
             const int my_y = (lane == 0) ? (int)(mt * C::TILE_M + rank * 128) : (int)(nt * C::TILE_N + rank * 128);
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const uint32_t ph = (pmask >> s) & 1u;
@@ -628,7 +633,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         if constexpr (EPI == 0 || EPI == 3) {
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 int64_t nt, mt;
-            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, p.m_shift, mt, nt);
                 if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
                 tc_fence_after();
                 const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
@@ -694,7 +699,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const int64_t atoms_per_tile = ((p.N >> 5) + 3) >> 2;
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
                 int64_t nt, mt;
-            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, p.m_shift, mt, nt);
                 if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
                 tc_fence_after();
                 const int64_t row = mt * C::TILE_M + rank * 128 + q * 32 + lane;      // this thread's token
@@ -842,7 +847,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const uint32_t sf_base = smem_u32(sSF);
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
             int64_t nt, mt;
-            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, mt, nt);
+            duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, p.m_shift, mt, nt);
             const int64_t ta = 2 * mt + rank, tw = 2 * nt;
             const bool a_ok = ta < p.rows_a_tiles, w1_ok = tw + 1 < p.rows_w_tiles;
             const uint8_t* my_src = (lane == 0) ? p.sfA + ta * p.sf_tile_stride

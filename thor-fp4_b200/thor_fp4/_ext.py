@@ -61,8 +61,8 @@ SIGNATURES = {
     "tfc4f_sfd_bytes": (i64, [i64, i64]),
     "tfc4f_gemm": (c_int, [c_int, c_void, c_void, c_void, c_void, c_void, c_void, c_void, i64, i64, i64, c_float, c_void]),
     "tfp4_swiglu_gemm": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, c_void, c_void, i64, i64, i64, c_void]),
-    "tfp4_gemm_push": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, ctypes.POINTER(c_void), c_int, i64, i64, i64, i64,
-                               c_int, c_void]),
+    "tfp4_gemm_push": (c_int, [c_void, c_void, c_float, c_void, c_void, c_float, ctypes.POINTER(c_void), c_int, i64, c_int,
+                               i64, i64, i64, c_int, c_void]),
     "tfp4_sum_slots": (c_int, [c_void, c_int, i64, i64, c_int, c_void, c_int, c_void]),
     "tfp4_peer_alloc": (c_int, [ctypes.c_size_t, ctypes.POINTER(c_void), ctypes.c_char_p]),
     "tfp4_peer_open": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_void)]),

@@ -242,7 +242,8 @@ class TensorParallelGatedMLP(nn.Module):
         k = stg.turn
         stg.turn ^= 1
         rc = L.tfp4_gemm_push(hp.data_ptr(), hs.data_ptr(), 1.0, wd.packed.data_ptr(), wd.sblk.data_ptr(), float(wd.tensor_scale),
-                              stg.dest[k], self.world, rows, M, H, self.local_intermediate, _ext.OUT_DTYPE[m.out_dtype], _ext.stream())
+                              stg.dest[k], self.world, rows, (self.rank + 1) % self.world, M, H, self.local_intermediate,
+                              _ext.OUT_DTYPE[m.out_dtype], _ext.stream())
         assert rc == 0, f"tfp4_gemm_push rc={rc}"
         # every rank's stores have landed once every rank's GEMM has completed: a 4-byte collective in stream order
         dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
@@ -281,7 +282,11 @@ class TensorParallelGatedMLP(nn.Module):
             ev.record(main)
             side.wait_event(ev)
             n = (r1 - r0) // self.world
-            for o in range(self.world):                                 # owner o takes the o-th 1/P of the chunk
+            # owner o takes the o-th 1/P of the chunk.  Rank r sends to r+1, r+2, ... in turn: at every step each GPU
+            # sends one slice and receives one (all ranks starting with owner 0 would pile three to seven senders onto
+            # one receiver's links at a time: measured 400-450 GB/s out per rank instead of the link rate)
+            for j in range(1, self.world + 1):
+                o = (self.rank + j) % self.world
                 dst = stg.dest[k][o] + pos * row_bytes
                 src = y.data_ptr() + (r0 + o * n) * row_bytes
                 rc = L.tfp4_peer_copy(dst, src, n * row_bytes, side.cuda_stream)
