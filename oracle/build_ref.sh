@@ -10,8 +10,9 @@
 #
 # usage: oracle/build_ref.sh [path-to-reference-checkout]
 set -euo pipefail
-REF="${1:-${THOR_FP4_REFERENCE:-/root/reference}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
+# the checkout: first argument, else THOR_FP4_REFERENCE, else a directory `reference` beside this repository
+REF="${1:-${THOR_FP4_REFERENCE:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 SRC="$REF/csrc/thor_fp4_core.cu"
 if [ ! -f "$SRC" ]; then

@@ -16,7 +16,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("THOR_FP4_REFERENCE", "/root/reference"))
+# the checkout: first argument, else THOR_FP4_REFERENCE, else a directory `reference` beside this repository
+ref = Path(sys.argv[1] if len(sys.argv) > 1
+           else os.environ.get("THOR_FP4_REFERENCE", str(Path(__file__).resolve().parents[3] / "reference")))
 sys.path.insert(0, str(ref / "src"))
 from thor_fp4.quant import mx_fake_quant, nvfp4_fake_quant, two_level_scale  # noqa: E402
 
