@@ -51,6 +51,8 @@ def parse():
     ap.add_argument("--inter", type=int, default=28672, help="mlp workload: intermediate size")
     ap.add_argument("--reduce-dtype", default="f32", choices=["f32", "bf16"],
                     help="mlp workload on several ranks: type of the partial outputs that are all-reduced")
+    ap.add_argument("--exchange", default="all_reduce", choices=["all_reduce", "reduce_scatter", "push", "copy"],
+                    help="mlp workload on several ranks: how the partial outputs are exchanged")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-mlp", action="store_true", help="skip the SwiGLU-block measurement added to the line")
@@ -434,7 +436,8 @@ def run_mlp(args):
         dist.init_process_group("nccl", device_id=dev)
     M, H, I = args.M, args.K, args.inter
     torch.manual_seed(1234 + rank)
-    tp = TensorParallelGatedMLP(H, I, device=dev, reduce_dtype=args.reduce_dtype if world > 1 else "bf16", weight_std=0.02)
+    tp = TensorParallelGatedMLP(H, I, device=dev, reduce_dtype=args.reduce_dtype if world > 1 else "bf16", weight_std=0.02,
+                                exchange=args.exchange)
     tp.local.refresh_weight()
     xs = [torch.randn(M, H, device=dev).bfloat16() for _ in range(2)]
 
@@ -469,12 +472,13 @@ def run_mlp(args):
             "metric": "NVFP4 SwiGLU MLP block TFLOPS (hidden 8192, intermediate 28672, 16384 tokens)", "value": flop / (ms * 1e-3) / 1e12,
             "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
-            "config": {"workload": f"NVFP4 gated MLP: x bf16 [{M},{H}] -> quantize -> [Wg;Wu] GEMM ({2 * I // world} rows per rank) -> "
-                                   f"silu*up + quantize -> Wd GEMM (K = {I // world} per rank) -> "
-                                   + (f"all-reduce of {args.reduce_dtype} partials (NCCL), 4 token chunks overlapped" if world > 1 else "bf16 out"),
-                       "tensor_parallel": world, "l2": "activations 268 MB and the 1.9 GB gate/up output exceed the 126 MB L2"},
+            "config": {"workload": f"NVFP4 gated MLP: x bf16 [{M},{H}] -> quantize -> [Wg;Wu] GEMM ({2 * I // world} rows per rank) with "
+                                   f"silu*up + NVFP4 quantize in its epilogue -> Wd GEMM (K = {I // world} per rank) -> "
+                                   + (f"{args.reduce_dtype} partials, {tp.exchange_name()}" if world > 1 else "bf16 out"),
+                       "tensor_parallel": world, "l2": "activations (268 MB) and weights (396 MB) exceed the 126 MB L2; inputs alternate between two buffers"},
             "per_gpu_frac_of_4x_bf16_burst": flop / world / (ms * 1e-3) / 1e12 / (4.0 * pk["bf16"]),
-            "gpu_launches": 5 * args.steps, "clocks": clocks}))
+            "gpu_launches": 3 * args.steps, "clocks": clocks}))
+    tp.close()
     if world > 1:
         dist.destroy_process_group()
 

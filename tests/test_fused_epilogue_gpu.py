@@ -269,7 +269,8 @@ def test_act_quant_mx8_bias_reads_stay_inside_the_vector():
 # ------------------------------------------------------------------------------------------ push epilogue (one GPU)
 @gpu
 @pytest.mark.parametrize("od", ["f32", "bf16"])
-@pytest.mark.parametrize("M,N,K,owners", [(512, 384, 1024, 2), (1024, 1000, 512, 4), (768, 256, 256, 8), (300, 264, 512, 2)])
+@pytest.mark.parametrize("M,N,K,owners", [(512, 384, 1024, 2), (1024, 1000, 512, 4), (768, 256, 256, 8), (300, 264, 512, 2),
+                                          (8192, 2048, 1024, 8)])
 def test_gemm_push_fills_every_owners_staging_rows(od, M, N, K, owners):
     """tfp4_gemm_push on one GPU: the 'owners' are buffers of this process, so the destination logic (which 32-row
     block goes to which owner, at which row of its slot) is checked without NVLink: owner o must hold exactly the rows

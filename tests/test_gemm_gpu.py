@@ -404,3 +404,34 @@ def test_tile_order_does_not_change_a_bit(shape):
     assert torch.isfinite(outs[-1].float()).all()
     for gm, out in outs.items():
         assert torch.equal(out, outs[-1]), f"gm={gm}"
+
+
+@gpu
+@pytest.mark.parametrize("od", ["f32", "bf16"])
+def test_slow_epilogue_does_not_change_a_bit(od):
+    """Several tiles per CTA pair and an epilogue that holds the accumulator ~40k cycles per tile (test hook 64): the
+    main loop then runs into a full pipeline at every tile - all operand stages, scale stages and scale slots filled,
+    every producer parked - and restarts in a burst.  The hand-offs between the roles (scale stage back to its
+    producer, slot to the loaders, accumulator to the MMA issuer) must hold in that regime too: same bits."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = 8192, 4096, 3584
+    x, w = _operands(M, N, K, seed=5)
+    a = thor_fp4.NVFP4Tensor.from_float(x.float(), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(w, None)
+    L = _ext.core()
+    L.tfp4_set_pair_mode(2)
+    outs = []
+    try:
+        for dbg in (0, 64, 64 | 32):
+            L.tfp4_set_debug(dbg)
+            out = torch.full((M, N), float("nan"), dtype=_ext.OUT_TORCH[od], device="cuda")
+            ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, od)
+            torch.cuda.synchronize()
+            outs.append(out)
+    finally:
+        L.tfp4_set_debug(0)
+        L.tfp4_set_pair_mode(-1)
+    assert _ext.status() == 0
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])

@@ -82,7 +82,10 @@ struct GemmParams {
                              // the tiles after them are cut into `splits` K ranges (0: every tile is cut)
     float* ws;
     int64_t ws_n0;           // first output column of the cut tiles (a multiple of 128; 0 when every tile is cut)
-    int32_t debug;           // test hook: bit0 no stores, bit1 no scale copies, bit2 no MMA, bit3 no loads, bit4 no tmem loads
+    int32_t zero;            // always 0, but only known at run time: lets an address depend on loaded values (see the
+                             // scale loaders of the two-CTA kernel) without changing it
+    int32_t debug;           // test hook: bit0 no stores, bit1 no scale copies, bit2 no MMA, bit3 no loads, bit4 no tmem loads,
+                             // bit5 no look-ahead polls, bit6 slow epilogue (two-CTA kernel)
     int* status;             // host-visible status word (0 = ok)
     unsigned long long* stats;   // host-visible per-CTA cycle counters (debug bit 1024): 4 per CTA, then 2 more per CTA from entry 1024
 };
@@ -1059,9 +1062,9 @@ int push_maps(const PushMaps** out, const EpilogueSpec& es, int64_t M, int64_t N
             int64_t rows = M - (int64_t)o * es.push_rows;
             if (rows > es.push_rows) rows = es.push_rows;
             if (rows <= 0) { pm.m[o] = pm.m[0]; continue; }      // no token row of this owner exists: never selected
+            // one store = 32 rows x 128 bytes (two 32-column chunks of a 16-bit output, one of an f32 output), 128-byte swizzle
             int rc = encode_map(&pm.m[o], CU_TENSOR_MAP_DATA_TYPE_UINT8, es.push_dest[o], (uint64_t)(N * esize), (uint64_t)rows,
-                                (uint64_t)(N * esize), esize == 2 ? 64 : 128, 32,
-                                esize == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+                                (uint64_t)(N * esize), 128, 32, CU_TENSOR_MAP_SWIZZLE_128B);
             if (rc) return rc;
         }
         for (int o = es.push_ranks; o < PUSH_MAX_RANKS; ++o) pm.m[o] = pm.m[0];
@@ -1377,6 +1380,7 @@ int gemm_block_scaled_ws(int kind, const void* packedA, const void* sblkA, const
             }
         }
     }
+    p.zero = 0;
     p.debug = g_debug;
     p.status = ext ? ext->status : st->status_dev;
     p.stats = ext ? ext->stats : st->stats_dev;

@@ -427,6 +427,13 @@ struct PushMaps { CUtensorMap m[PUSH_MAX_RANKS]; };
 template <int EPI> struct DuoOutMaps { using type = CUtensorMap; };
 template <> struct DuoOutMaps<3> { using type = PushMaps; };
 
+// the output tensor map of owner o (push epilogue) or the one output map (every other mode)
+template <int EPI>
+__device__ __forceinline__ const CUtensorMap* duo_push_map(const typename DuoOutMaps<EPI>::type& t, int64_t o) {
+    if constexpr (EPI == 3) return &t.m[o];
+    else return &t;
+}
+
 template <int KIND, bool DBG, int EPI>
 __global__ void __launch_bounds__(DUO_THREADS, 1)
 gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -636,6 +643,12 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             duo_tile_coords(tile, tiles_m, tiles_n, p.raster_gm, p.m_shift, mt, nt);
                 if (!mbar_wait_sleep(smem_u32(tfull_bar), tcount & 1u, abort_flag, 4, wlim)) { ok = false; break; }
                 tc_fence_after();
+                if (dbg & 64) {
+                    // test hook: a slow epilogue (the accumulator is held ~40k cycles longer), so that the main loop
+                    // runs into a full pipeline at every tile
+                    const long long t0 = clock64();
+                    while (clock64() - t0 < 40000ll) {}
+                }
                 const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
                 const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
                 // One 32-column chunk: alpha, bias, cast, swizzled shared memory, TMA store.
@@ -658,18 +671,50 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                         // rows beyond M and bytes beyond the row end are clipped by the copy engine; a chunk that
                         // lies outside altogether still closes an (empty) group, so that the group counts above hold
                         if (row0 < p.M && nn < p.N && !(dbg & 1)) {
-                            if constexpr (EPI == 3) {
-                                // the owner of these 32 token rows (push_rows is a multiple of 32: a block has one owner)
-                                const int64_t o = row0 / p.push_rows;
-                                tma_store_2d(&tmO.m[o], (int)(nn * esize), (int)(row0 - o * p.push_rows), buf);
-                            } else {
-                                tma_store_2d(&tmO, (int)(nn * esize), (int)row0, buf);
-                            }
+                            // push epilogue: the owner of these 32 token rows (push_rows is a multiple of 32: a block has one owner)
+                            const int64_t o = (EPI == 3) ? row0 / p.push_rows : 0;
+                            tma_store_2d(duo_push_map<EPI>(tmO, o), (int)(nn * esize), (int)(row0 - o * p.push_rows), buf);
                         }
                         bulk_commit_group();
                     }
                     ++nstore;
                 };
+                // Push epilogue, 16-bit outputs: two chunks per store, so that a row written into the owner's memory is 128
+                // bytes.  Over NVLink the width of the written rows sets the rate: 64-byte rows left a rank at 400 GB/s, 128-byte
+                // rows at 600 (f32 chunks are 128 bytes already; 256-byte rows from an un-swizzled staging block were no faster).
+                auto emit_pair = [&](const uint32_t (&v0)[32], const uint32_t (&v1)[32], int c) {
+                    const int64_t nn = n0 + c;
+                    float f0[32], f1[32];
+                    duo_scale(v0, f0, nn, p.N, p.alpha, nullptr);
+                    duo_scale(v1, f1, nn + 32, p.N, p.alpha, nullptr);
+                    const int64_t o = p.push_rows > 0 ? row0 / p.push_rows : 0;
+                    if (lane == 0) bulk_wait_read_0();
+                    __syncwarp();
+                    duo_put16(f0, my_buf + (uint32_t)lane * 128u, 0, lane, bf16);
+                    duo_put16(f1, my_buf + (uint32_t)lane * 128u, 4, lane, bf16);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (row0 < p.M && nn < p.N && !(dbg & 1))
+                            tma_store_2d(duo_push_map<EPI>(tmO, o), (int)(nn * 2), (int)(row0 - o * p.push_rows), my_buf);
+                        bulk_commit_group();
+                    }
+                };
+                if (EPI == 3 && out16) {
+                    uint32_t va[32], vb[32];
+                    tc_ld32(t_lane, va);
+                    tc_ld32(t_lane + 32u, vb);
+                    tc_wait_ld();
+                    emit_pair(va, vb, 0);
+                    tc_ld32(t_lane + 64u, va);
+                    tc_ld32(t_lane + 96u, vb);
+                    tc_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster_relaxed(tempty_leader);      // this warp's columns are all in registers
+                    emit_pair(va, vb, 64);
+                    continue;
+                }
                 // The warp's 128 columns are four chunks.  Two are read at once; the third is read while the second is
                 // emitted and the fourth right after, so the accumulator goes back to the MMA issuer after two chunks'
                 // worth of arithmetic instead of three.
@@ -785,8 +830,17 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                     ld_shared_v4(src + C::SF_PART + 512 * j, &vw0[4 * j]);
                     ld_shared_v4(src + 2 * C::SF_PART + 512 * j, &vw1[4 * j]);
                 }
+                // The stage goes back to the scale producer here, before the values are used.  A shared-memory load has
+                // only been issued at this point: when the load/store queue of the SM is backed up (an epilogue writing
+                // with bank conflicts was enough), the arrival below overtook the last loads and the next copy into the
+                // stage changed what they returned.  So the barrier address is made to depend on every load (acc & 0):
+                // the arrival cannot issue before all of them have delivered their registers.
+                uint32_t acc = 0;
+#pragma unroll
+                for (int j = 0; j < 2 * ATOMS; ++j) acc |= va[4 * j] | vw0[4 * j] | vw1[4 * j];
+                acc &= (uint32_t)p.zero;
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sfree0 + 8 * st);
+                if (lane == 0) mbar_arrive(sfree0 + 8 * st + acc);
                 const int nkb = (2 * gi + 2 <= k_blocks) ? 2 : 1;
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
