@@ -56,9 +56,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-mlp", action="store_true", help="skip the SwiGLU-block measurement added to the line")
-    ap.add_argument("--graph", action="store_true",
-                    help="several ranks: also capture the SwiGLU block, with its NCCL reduce-scatter, in a CUDA graph and time the "
-                         "replay (on one rank the captured block is always timed)")
+    ap.add_argument("--graph", action="store_true", help="accepted for older command lines: the captured block is always timed")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="do not capture the SwiGLU block (with its NCCL all-reduce, and the push form) in a CUDA graph")
     ap.add_argument("--ablate", action="store_true",
                     help="time the GEMM with parts of the kernel switched off through the library's test hooks and print a table")
     ap.add_argument("--plain-launch", action="store_true",
@@ -658,24 +658,39 @@ def measure_mlp_block(args, dev, rank, world, steps):
         tp.close()
         tp.exchange = "all_reduce"
     # the per-rank block captured in a CUDA graph and replayed (the form the benchmark configuration names): one rank
-    # -> the three kernels; several ranks -> the reduce-scatter exchange, whose NCCL collective is captured with them
-    # (the push exchange's staging set alternates from call to call, which a captured graph cannot do)
+    # -> the three kernels; several ranks -> the block with its NCCL all-reduce (the configuration's own form) and the
+    # push form, whose staging set alternates from call to call: two blocks in a row are captured, so that a replay
+    # leaves the alternation where it found it
     graph = None
-    if args.graph or world == 1:
-        try:
-            if world > 1:
-                tp.exchange = "reduce_scatter"
+    if not args.no_graph:
+        def capture(exchange, blocks):
+            tp.exchange = exchange
             xg = xs[0].clone()
             for _ in range(2):
                 tp(xg)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                yg = tp(xg)
-            ms_g = timed(lambda i: g.replay(), steps)
-            graph = {"exchange": tp.exchange_name() if world > 1 else None, "ms_per_block": ms_g,
-                     "tflops": 6.0 * M * H * I / (ms_g * 1e-3) / 1e12}
+                for _ in range(blocks):
+                    yg = tp(xg)
+            ms_g = timed(lambda i: g.replay(), steps) / blocks
+            name = tp.exchange_name() if world > 1 else None
             del g, yg
+            return {"exchange": name, "ms_per_block": ms_g, "tflops": 6.0 * M * H * I / (ms_g * 1e-3) / 1e12,
+                    "blocks_per_graph": blocks}
+        try:
+            if world == 1:
+                graph = capture("all_reduce", 1)
+            else:
+                graph = capture("all_reduce", 1)
+                try:
+                    graph["push"] = capture("push", 2)
+                    torch.cuda.synchronize()
+                    if dist.is_initialized():
+                        dist.barrier()
+                    tp.close()
+                except Exception as e:  # noqa: BLE001
+                    graph["push"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         except Exception as e:  # noqa: BLE001
             graph = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         tp.exchange = "all_reduce"
