@@ -807,6 +807,31 @@ def run_ours(args):
     if _ext.status() != 0:
         raise RuntimeError(f"device status word {_ext.status()}: a GEMM wait expired")
 
+    # ---------------- what a plain device copy reaches in the quantizer's place: the same loop with the quantizer
+    # replaced by a copy that moves the quantizer's algorithmic bytes (half read, half written), right behind the GEMM,
+    # i.e. at the SM / L2 clock the power cap leaves after it and with the GEMM's output lines still dirty in L2
+    in_step_copy = None
+    if not args.profile:
+        q_bytes_i = int(M * K * (2 + 0.5 + 1.0 / 16))
+        half = (q_bytes_i // 2 + 255) // 256 * 256
+        srcs = [xs[j].view(torch.uint8).reshape(-1)[:half] for j in range(min(n_in, 3))]
+        dstc = torch.empty(half, dtype=torch.uint8, device=dev)
+        n_c = max(8, min(args.steps, 40))
+        cev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_c)]
+        for i in range(3 + n_c):
+            if i >= 3:
+                cev[i - 3][0].record()
+            dstc.copy_(srcs[i % len(srcs)])
+            if i >= 3:
+                cev[i - 3][1].record()
+            ops.gemm(packed, sblk, 1.0, w.packed, w.sblk, w.tensor_scale, out, M, N, K, "bf16")
+        torch.cuda.synchronize()
+        c_ms = float(np.mean([a.elapsed_time(b) for a, b in cev]))
+        in_step_copy = {"bytes_moved": 2 * half, "avg_ms": c_ms, "gbs": 2 * half / (c_ms * 1e-3) / 1e9,
+                        "note": "torch copy_ of half the quantizer's algorithmic bytes (read + write = the same total) timed "
+                                "between the GEMMs of the same loop"}
+        del dstc, srcs
+
     # ---------------- the activation quantizer alone on [16384, 8192] bf16 (the larger of the metric's two shapes)
     q_large = None
     if not args.profile:
@@ -927,7 +952,9 @@ def run_ours(args):
                                "avg_launch_ms": q_ms,
                                "algorithmic_bytes_per_launch": q_bytes,
                                "note": "inside the step, on [8192, 8192]; 'alone_large' is the same kernel timed alone on [16384, 8192]",
-                               "alone_large": (dict(q_large, frac=q_large["achieved"] / pk["hbm_gbs"]) if q_large else None)},
+                               "alone_large": (dict(q_large, frac=q_large["achieved"] / pk["hbm_gbs"]) if q_large else None),
+                               "in_step_copy": (dict(in_step_copy, quantizer_vs_copy=q_gbs / in_step_copy["gbs"])
+                                                if in_step_copy else None)},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
     }
