@@ -791,7 +791,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 emit(vb, IntTag<3>{});
                 if (n0 < p.N && !(dbg & 1)) {
                     const int64_t atom = (row >> 7) * atoms_per_tile + (n0 >> 7);     // 128 columns = 4 scale columns = one atom
-                    if (EPI == 1) {
+                    if constexpr (EPI == 1) {
                         if (row < Mpad) {
                             uint4* dst = reinterpret_cast<uint4*>(q_codes + row * code_ld + (n0 >> 2));
                             dst[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
