@@ -225,7 +225,10 @@ void tfp4_set_token_tile(int bn);
  * (cta_group::2) kernel for batches above 128 tokens with enough tiles, 0 = single-CTA kernel only, 1 or 2 = the
  * two-CTA kernel whenever the shape allows it; debug bits switch off parts of the GEMM kernel
  * for ablation timing (bit0 stores, bit1 scale copies, bit2 MMAs, bit3 loads, bit4 tensor-memory
- * reads; bit 1024 records per-CTA cycle counters read back with tfp4_debug_stats: 4 values per CTA). */
+ * reads, bit5 the MMA issuer's look-ahead polls; bit6 makes the two-CTA kernel's epilogue hold the accumulator about
+ * 40k cycles per tile, so that every tile starts from a stalled, full pipeline - results must not change; bit 512
+ * starves the consumers so that the bounded waits give up; bit 1024 records per-CTA cycle counters read back with
+ * tfp4_debug_stats: 4 values per CTA). */
 void tfp4_set_pair_mode(int mode);
 /* No counterpart in the reference.  1 (default): the GEMM kernels and the split-K reduction are launched with
  * programmatic stream serialization, so their prologue overlaps the tail of the kernel before them in the stream
