@@ -435,3 +435,31 @@ def test_slow_epilogue_does_not_change_a_bit(od):
     assert _ext.status() == 0
     assert torch.isfinite(outs[0].float()).all()
     assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])
+
+
+@gpu
+def test_slow_epilogue_does_not_change_a_bit_mx8():
+    """The same stalled-pipeline regime for the MXFP8 x MXFP4 instantiation (one scale atom per part and K block)."""
+    import thor_fp4
+    from thor_fp4 import ops, _ext
+    M, N, K = 8192, 2048, 2048
+    x = torch.randn(M, K, device="cuda")
+    w = torch.randn(N, K, device="cuda") * 0.05
+    a, b = thor_fp4.MXTensor.from_float(x, "mxfp8"), thor_fp4.MXTensor.from_float(w, "mxfp4")
+    L = _ext.core()
+    v = L.tfc4_variant_index(thor_fp4.linear.resolve_mx8_variant(K).encode())
+    outs = []
+    try:
+        L.tfp4_set_pair_mode(2)
+        for dbg in (0, 64):
+            L.tfp4_set_debug(dbg)
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.gemm_mx(v, a.packed, a.sblk, b.packed, b.sblk, out, M, N, K)
+            torch.cuda.synchronize()
+            outs.append(out)
+    finally:
+        L.tfp4_set_debug(0)
+        L.tfp4_set_pair_mode(-1)
+    assert _ext.status() == 0
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[0], outs[1])
