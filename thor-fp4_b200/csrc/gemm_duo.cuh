@@ -36,6 +36,9 @@
 // flight (bulk copies, global stores), measured at 500-1200 cycles per arrival.
 
 constexpr int DUO_THREADS = 480;
+// NVFP4 main loop: operand descriptors and scale addresses of every stage precomputed outside the tile loop (0.7 % at
+// 8192^3 against re-deriving them in every K block's statement)
+constexpr bool DUO_PRE = true;
 
 struct DuoCfg {
     static constexpr int TILE_M = 256, TILE_N = 256;
@@ -264,6 +267,51 @@ __device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate,
         "}"
         : "=r"(ready)
         : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf),
+          "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
+        : "memory");
+    return ready;
+}
+
+// duo_kblock with every address handed over: the low descriptor words of the four MMAs' operands and the eight scale
+// addresses are loop-invariant per stage, so the caller keeps them in registers instead of this statement re-deriving
+// them (13 additions) for every K block.
+__device__ __forceinline__ uint32_t duo_kblock_pre(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last, uint32_t d,
+                                                   const uint32_t (&a)[4], const uint32_t (&b)[4], uint32_t desc_hi,
+                                                   const uint32_t (&sfa)[4], const uint32_t (&sfb)[4],
+                                                   uint32_t full_next, uint32_t sf_next, uint32_t par_next,
+                                                   uint32_t empty_bar, uint32_t tfull_bar) {
+    uint32_t ready;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+        ".reg .b16 m;\n\t"
+        ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "setp.ne.b32 pa, %2, 0;\n\t"
+        "setp.gt.and.u32 q0, %3, 0, q;\n\t"
+        "setp.gt.and.u32 q1, %3, 1, q;\n\t"
+        "setp.gt.and.u32 q2, %3, 2, q;\n\t"
+        "setp.gt.and.u32 q3, %3, 3, q;\n\t"
+        "setp.ne.and.b32 ql, %4, 0, q;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b16 m, 3;\n\t"
+        "mov.b64 da0, {%6, %14};\n\tmov.b64 da1, {%7, %14};\n\tmov.b64 da2, {%8, %14};\n\tmov.b64 da3, {%9, %14};\n\t"
+        "mov.b64 db0, {%10, %14};\n\tmov.b64 db1, {%11, %14};\n\tmov.b64 db2, {%12, %14};\n\tmov.b64 db3, {%13, %14};\n\t"
+        "@q0 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %28, [%15], [%19], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%23], %25;\n\t"
+        "@q1 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %28, [%16], [%20], pt;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%24], %25;\n\t"
+        "@q2 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %28, [%17], [%21], pt;\n\t"
+        "@q3 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %28, [%18], [%22], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%26], m;\n\t"
+        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%27], m;\n\t"
+        "and.pred pf, pf, ps;\n\t"
+        "selp.u32 %0, 1, 0, pf;\n\t"
+        "}"
+        : "=r"(ready)
+        : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d),
+          "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(desc_hi),
+          "r"(sfa[0]), "r"(sfa[1]), "r"(sfa[2]), "r"(sfa[3]), "r"(sfb[0]), "r"(sfb[1]), "r"(sfb[2]), "r"(sfb[3]),
           "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
         : "memory");
     return ready;
@@ -566,6 +614,18 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             const uint32_t sf0 = tmem_base + C::SF_COL;
             const uint32_t tfull_a = smem_u32(tfull_bar);
             const uint32_t last_atoms = (dbg & 4) ? 0u : (uint32_t)p.last_atoms;
+            // per stage: the low descriptor words of the four MMAs' operands (32 bytes further into the swizzle span each)
+            // and their scale addresses (token scales 4 columns per MMA, feature scales 8)
+            uint32_t pre_a[C::OP_STAGES][4], pre_b[C::OP_STAGES][4], pre_sfa[C::OP_STAGES][4], pre_sfb[C::OP_STAGES][4];
+#pragma unroll
+            for (int u = 0; u < C::OP_STAGES; ++u)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    pre_a[u][j] = a_lo0 + u * (C::X_BYTES >> 4) + 2 * j;
+                    pre_b[u][j] = b_lo0 + u * (C::W_BYTES >> 4) + 2 * j;
+                    pre_sfa[u][j] = sf0 + u * TMEM_SF_SLOT_COLS + 4 * j;
+                    pre_sfb[u][j] = sf0 + u * TMEM_SF_SLOT_COLS + 16 + 8 * j;
+                }
             long long c_acc = 0, c_wait = 0, s_obs = 0, s_commit = 0;
             uint32_t n_miss = 0;
             const long long c_begin = clock64();
@@ -592,10 +652,17 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                             tc_fence_after();
                             const bool last = kb + 1 == k_blocks;
                             const int un = (u + 1) % C::OP_STAGES;         // the next K block's stage (also across tiles)
-                            const uint32_t ready = (KIND == 0 ? duo_kblock : duo_kblock_mx)(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
+                            uint32_t ready;
+                            if constexpr (KIND == 0 && DUO_PRE) {
+                                ready = duo_kblock_pre(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
+                                                       pre_a[u], pre_b[u], desc_hi, pre_sfa[u], pre_sfb[u],
+                                                       full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u, empty0 + 8 * u, tfull_a);
+                            } else {
+                                ready = (KIND == 0 ? duo_kblock : duo_kblock_mx)(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
                                            a_lo0 + u * (C::X_BYTES >> 4), b_lo0 + u * (C::W_BYTES >> 4), desc_hi,
                                            sf0 + u * TMEM_SF_SLOT_COLS, full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u,
                                            empty0 + 8 * u, tfull_a);
+                            }
                             peek = __all_sync(0xffffffffu, ready != 0u) && !(dbg & 32);
                         }
                     }
