@@ -26,10 +26,11 @@
 //               registers -> tcgen05.st into the scale slots of tensor memory
 //   warp 10     scale producer: bulk copies of the scale atoms, two K blocks per copy, running
 //               ahead of the operand pipeline
-// Barriers.  full[s] (leader: own bytes + the peer's relay; peer: own bytes), empty[s] / tfull:
-// local in each CTA, signalled by the leader's tcgen05.commit with a two-CTA mask.  sfl[i]: scale
-// atoms landed (local).  sfree[i]: the four loader warps have read scale stage i (local).
-// sffull[i]: in the leader, 8 arrivals (4 loader warps of each CTA); tempty: 16 (8 epilogue warps of each).  Every wait is bounded.
+// Barriers.  full[s] (leader: own bytes + the peer's relay + the 8 loader warps of both CTAs, i.e. "operands landed and
+// scales in tensor memory" is ONE barrier and one poll per K block for the MMA issuer - two barriers and two polls cost
+// 2 % at 8192^3; peer: own bytes), empty[s] / tfull: local in each CTA, signalled by the leader's tcgen05.commit with a
+// two-CTA mask.  sfl[i]: scale atoms landed (local).  sfree[i]: the four loader warps have read scale stage i (local).
+// tempty: 16 arrivals (8 epilogue warps of each CTA).  Every wait is bounded.
 // The MMA issuer polls with mbarrier.test_wait; every other warp waits with try_wait, which parks
 // the warp: ten warps spinning on shared-memory barriers slow the issuer's own polls down.  Arrivals on the other CTA's barriers are
 // relaxed: a releasing arrive at cluster scope first waits for everything its thread has in
@@ -230,12 +231,12 @@ __device__ __forceinline__ void duo_put32(const float (&f)[32], uint32_t row_add
 // had completed the polled phase.
 __device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last,
                                                uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t sf,
-                                               uint32_t full_next, uint32_t sf_next, uint32_t par_next,
+                                               uint32_t full_next, uint32_t par_next,
                                                uint32_t empty_bar, uint32_t tfull_bar) {
     uint32_t ready;
     asm volatile(
         "{\n\t"
-        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf;\n\t"
         ".reg .b16 m;\n\t"
         ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g0, g1, g2, g3;\n\t"
         ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
@@ -254,20 +255,18 @@ __device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate,
         "mov.b64 db0, {%7, %8};\n\tmov.b64 db1, {b1, %8};\n\tmov.b64 db2, {b2, %8};\n\tmov.b64 db3, {b3, %8};\n\t"
         "add.u32 f1, %9, 4;\n\tadd.u32 f2, %9, 8;\n\tadd.u32 f3, %9, 12;\n\t"
         "add.u32 g0, %9, 16;\n\tadd.u32 g1, %9, 24;\n\tadd.u32 g2, %9, 32;\n\tadd.u32 g3, %9, 40;\n\t"
-        "@q0 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %15, [%9], [g0], pa;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %12;\n\t"
-        "@q1 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %15, [f1], [g1], pt;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%11], %12;\n\t"
-        "@q2 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %15, [f2], [g2], pt;\n\t"
-        "@q3 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %15, [f3], [g3], pt;\n\t"
-        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], m;\n\t"
-        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%14], m;\n\t"
-        "and.pred pf, pf, ps;\n\t"
+        "@q0 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %14, [%9], [g0], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %11;\n\t"
+        "@q1 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %14, [f1], [g1], pt;\n\t"
+        "@q2 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %14, [f2], [g2], pt;\n\t"
+        "@q3 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %14, [f3], [g3], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], m;\n\t"
+        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], m;\n\t"
         "selp.u32 %0, 1, 0, pf;\n\t"
         "}"
         : "=r"(ready)
         : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf),
-          "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
+          "r"(full_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
         : "memory");
     return ready;
 }
@@ -278,12 +277,12 @@ __device__ __forceinline__ uint32_t duo_kblock(uint32_t on, uint32_t accumulate,
 __device__ __forceinline__ uint32_t duo_kblock_pre(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last, uint32_t d,
                                                    const uint32_t (&a)[4], const uint32_t (&b)[4], uint32_t desc_hi,
                                                    const uint32_t (&sfa)[4], const uint32_t (&sfb)[4],
-                                                   uint32_t full_next, uint32_t sf_next, uint32_t par_next,
+                                                   uint32_t full_next, uint32_t par_next,
                                                    uint32_t empty_bar, uint32_t tfull_bar) {
     uint32_t ready;
     asm volatile(
         "{\n\t"
-        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf;\n\t"
         ".reg .b16 m;\n\t"
         ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
         "setp.ne.b32 q, %1, 0;\n\t"
@@ -297,22 +296,20 @@ __device__ __forceinline__ uint32_t duo_kblock_pre(uint32_t on, uint32_t accumul
         "mov.b16 m, 3;\n\t"
         "mov.b64 da0, {%6, %14};\n\tmov.b64 da1, {%7, %14};\n\tmov.b64 da2, {%8, %14};\n\tmov.b64 da3, {%9, %14};\n\t"
         "mov.b64 db0, {%10, %14};\n\tmov.b64 db1, {%11, %14};\n\tmov.b64 db2, {%12, %14};\n\tmov.b64 db3, {%13, %14};\n\t"
-        "@q0 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %28, [%15], [%19], pa;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%23], %25;\n\t"
-        "@q1 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %28, [%16], [%20], pt;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%24], %25;\n\t"
-        "@q2 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %28, [%17], [%21], pt;\n\t"
-        "@q3 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %28, [%18], [%22], pt;\n\t"
-        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%26], m;\n\t"
-        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%27], m;\n\t"
-        "and.pred pf, pf, ps;\n\t"
+        "@q0 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da0, db0, %27, [%15], [%19], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%23], %24;\n\t"
+        "@q1 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da1, db1, %27, [%16], [%20], pt;\n\t"
+        "@q2 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da2, db2, %27, [%17], [%21], pt;\n\t"
+        "@q3 tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%5], da3, db3, %27, [%18], [%22], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%25], m;\n\t"
+        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%26], m;\n\t"
         "selp.u32 %0, 1, 0, pf;\n\t"
         "}"
         : "=r"(ready)
         : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d),
           "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(desc_hi),
           "r"(sfa[0]), "r"(sfa[1]), "r"(sfa[2]), "r"(sfa[3]), "r"(sfb[0]), "r"(sfb[1]), "r"(sfb[2]), "r"(sfb[3]),
-          "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
+          "r"(full_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC)
         : "memory");
     return ready;
 }
@@ -322,12 +319,12 @@ __device__ __forceinline__ uint32_t duo_kblock_pre(uint32_t on, uint32_t accumul
 // the scale address).
 __device__ __forceinline__ uint32_t duo_kblock_mx(uint32_t on, uint32_t accumulate, uint32_t n_mma, uint32_t last,
                                                   uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t sf,
-                                                  uint32_t full_next, uint32_t sf_next, uint32_t par_next,
+                                                  uint32_t full_next, uint32_t par_next,
                                                   uint32_t empty_bar, uint32_t tfull_bar) {
     uint32_t ready;
     asm volatile(
         "{\n\t"
-        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf, ps;\n\t"
+        ".reg .pred q, q0, q1, q2, q3, ql, pa, pt, pf;\n\t"
         ".reg .b16 m;\n\t"
         ".reg .b32 a1, a2, a3, b1, b2, b3, f1, f2, f3, g0, g1, g2, g3;\n\t"
         ".reg .b64 da0, da1, da2, da3, db0, db1, db2, db3;\n\t"
@@ -346,20 +343,18 @@ __device__ __forceinline__ uint32_t duo_kblock_mx(uint32_t on, uint32_t accumula
         "mov.b64 db0, {%7, %8};\n\tmov.b64 db1, {b1, %8};\n\tmov.b64 db2, {b2, %8};\n\tmov.b64 db3, {b3, %8};\n\t"
         "or.b32 f1, %9, 0x40000000;\n\tor.b32 f2, %9, 0x80000000;\n\tor.b32 f3, %9, 0xC0000000;\n\t"
         "add.u32 g0, %9, 16;\n\tor.b32 g1, g0, 0x40000000;\n\tor.b32 g2, g0, 0x80000000;\n\tor.b32 g3, g0, 0xC0000000;\n\t"
-        "@q0 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da0, db0, %15, [%9], [g0], pa;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %12;\n\t"
-        "@q1 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da1, db1, %16, [f1], [g1], pt;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 ps, [%11], %12;\n\t"
-        "@q2 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da2, db2, %17, [f2], [g2], pt;\n\t"
-        "@q3 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da3, db3, %18, [f3], [g3], pt;\n\t"
-        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], m;\n\t"
-        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%14], m;\n\t"
-        "and.pred pf, pf, ps;\n\t"
+        "@q0 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da0, db0, %14, [%9], [g0], pa;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 pf, [%10], %11;\n\t"
+        "@q1 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da1, db1, %15, [f1], [g1], pt;\n\t"
+        "@q2 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da2, db2, %16, [f2], [g2], pt;\n\t"
+        "@q3 tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%5], da3, db3, %17, [f3], [g3], pt;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], m;\n\t"
+        "@ql tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%13], m;\n\t"
         "selp.u32 %0, 1, 0, pf;\n\t"
         "}"
         : "=r"(ready)
         : "r"(on), "r"(accumulate), "r"(n_mma), "r"(last), "r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(sf),
-          "r"(full_next), "r"(sf_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC_MX),
+          "r"(full_next), "r"(par_next), "r"(empty_bar), "r"(tfull_bar), "n"(DuoCfg::IDESC_MX),
           "n"(DuoCfg::IDESC_MX1), "n"(DuoCfg::IDESC_MX2), "n"(DuoCfg::IDESC_MX3)
         : "memory");
     return ready;
@@ -498,8 +493,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     uint64_t* empty_bar = full_bar + C::OP_STAGES;           // [OP_STAGES]
     uint64_t* sfl_bar = empty_bar + C::OP_STAGES;            // [SF_STAGES]
     uint64_t* sfree_bar = sfl_bar + C::SF_STAGES;            // [SF_STAGES]
-    uint64_t* sffull_bar = sfree_bar + C::SF_STAGES;         // [NSLOT]      used in the leader
-    uint64_t* tfull_bar = sffull_bar + C::NSLOT;             // [1]
+    uint64_t* tfull_bar = sfree_bar + C::SF_STAGES;          // [1]
     uint64_t* tempty_bar = tfull_bar + 1;                    // [1]          used in the leader
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -510,14 +504,13 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::OP_STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), leader ? 2 : 1);
+            mbar_init(smem_u32(&full_bar[s]), leader ? 10 : 1);      // leader: own bytes, the peer's relay, 8 loader warps
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int s = 0; s < C::SF_STAGES; ++s) {
             mbar_init(smem_u32(&sfl_bar[s]), 1);
             mbar_init(smem_u32(&sfree_bar[s]), 4);
         }
-        for (int s = 0; s < C::NSLOT; ++s) mbar_init(smem_u32(&sffull_bar[s]), 8);
         mbar_init(smem_u32(tfull_bar), 1);
         mbar_init(smem_u32(tempty_bar), 16);
         *abort_flag = 0;
@@ -545,7 +538,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const int k_blocks = p.k_blocks;
     const int grans = (k_blocks + 1) >> 1;                   // scale granules (two K blocks) per tile
     const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
-    const uint32_t sfl0 = smem_u32(sfl_bar), sfree0 = smem_u32(sfree_bar), sffull0 = smem_u32(sffull_bar);
+    const uint32_t sfl0 = smem_u32(sfl_bar), sfree0 = smem_u32(sfree_bar);
     // test hooks (tfp4_set_debug) exist only in the DBG instantiation; the production one carries none of their branches
     const int dbg = DBG ? p.debug : 0;
     const bool prof = DBG && (dbg & 1024) != 0;
@@ -645,7 +638,6 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                             if (!peek) {
                                 // scales of this K block are in tensor memory of both CTAs; operands of both CTAs landed
                                 const long long t0 = prof ? clock64() : 0;
-                                if (!mbar_wait(sffull0 + 8 * u, ph, abort_flag, 5, wlim)) { ok = false; break; }
                                 if (!mbar_wait(full0 + 8 * u, ph, abort_flag, 3, wlim)) { ok = false; break; }
                                 if (prof) { c_wait += clock64() - t0; ++n_miss; }
                             }
@@ -656,11 +648,11 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                             if constexpr (KIND == 0 && DUO_PRE) {
                                 ready = duo_kblock_pre(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
                                                        pre_a[u], pre_b[u], desc_hi, pre_sfa[u], pre_sfb[u],
-                                                       full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u, empty0 + 8 * u, tfull_a);
+                                                       full0 + 8 * un, (mmask >> un) & 1u, empty0 + 8 * u, tfull_a);
                             } else {
                                 ready = (KIND == 0 ? duo_kblock : duo_kblock_mx)(on, kb > 0 ? 1u : 0u, last ? last_atoms : full_mma, last ? 1u : 0u, tmem_base,
                                            a_lo0 + u * (C::X_BYTES >> 4), b_lo0 + u * (C::W_BYTES >> 4), desc_hi,
-                                           sf0 + u * TMEM_SF_SLOT_COLS, full0 + 8 * un, sffull0 + 8 * un, (mmask >> un) & 1u,
+                                           sf0 + u * TMEM_SF_SLOT_COLS, full0 + 8 * un, (mmask >> un) & 1u,
                                            empty0 + 8 * u, tfull_a);
                             }
                             peek = __all_sync(0xffffffffu, ready != 0u) && !(dbg & 32);
@@ -880,7 +872,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const bool profl = false;
         long long c_sfl = 0, c_empty = 0, c_st = 0;
         const uint32_t sf_base = smem_u32(sSF);
-        const uint32_t sffull_leader = map_to_cta(sffull0, 0);
+        const uint32_t full_leader = map_to_cta(full0, 0);
         const uint32_t t_q = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_COL;
         for (int64_t tile = first; tile < total_tiles && ok; tile += stride) {
             for (int gi = 0; gi < grans && ok; ++gi, ++g) {
@@ -948,7 +940,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                         }
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster_relaxed(sffull_leader + 8 * slot);
+                        if (lane == 0) mbar_arrive_cluster_relaxed(full_leader + 8 * slot);
                         if (profl) c_st += clock64() - t0;
                         if (++slot == (uint32_t)C::NSLOT) slot = 0;
                     }
