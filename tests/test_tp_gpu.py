@@ -69,10 +69,20 @@ WORKER = textwrap.dedent('''
         good = good and ((tcopy.gather(yc, M) - yi).norm() / yi.norm()).item() < 1e-6
     torch.cuda.synchronize()
     tcopy.close()
+    # bf16 partials through the push epilogue (two 32-column chunks per TMA store): each partial is rounded once to bf16
+    # before the sum, so the result tracks the f32 exchange to a few bf16 ulps
+    tpb = TensorParallelGatedMLP(H, I, device="cuda", reduce_dtype="bf16", exchange="push")
+    tpb.load_full_weights(wg.cuda(), wu.cuda(), wd.cuda())
+    for it in range(2):
+        yb = tpb(x).float()
+        rows_b = tpb.owned_rows(M).cuda()
+        good = good and yb.shape == (M // 2, H) and ((yb - y[rows_b]).norm() / y[rows_b].norm()).item() < 8e-3
+    torch.cuda.synchronize()
     okp = torch.tensor([int(good)], device="cuda")
     dist.all_reduce(okp, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()
     tpush.close()
+    tpb.close()
     if rank == 0:
         print("PUSH_OK", int(okp.item()))
     dist.destroy_process_group()
