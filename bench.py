@@ -661,18 +661,20 @@ def measure_mlp_block(args, dev, rank, world, steps):
                     "rel_error_vs_unsharded_block": err_p,
                     "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * (4 if reduce_dtype == "f32" else 2)}
             if reduce_dtype == "f32":
-                # the same exchange with bf16 partials: half the bytes over NVLink, each partial rounded once before the sum
-                tp.local.out_dtype = "bf16"
-                try:
-                    yb = tp(xs[0])
-                    torch.cuda.synchronize()
-                    err_b = float((yb[:1024].float() - ref).norm() / ref.norm()) if rank == 0 else None
-                    ms_b = timed(lambda i: tp(xs[i % 2]), steps)
-                    push["bf16_partials"] = {"ms_per_block": ms_b, "tflops": 6.0 * M * H * I / (ms_b * 1e-3) / 1e12,
-                                             "rel_error_vs_unsharded_block": err_b,
-                                             "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * 2}
-                finally:
-                    tp.local.out_dtype = "f32"
+                # the same exchange with 16-bit partials: half the bytes over NVLink, each partial rounded once before the
+                # sum (f16: 2^-12 relative, needs the partials inside the f16 range; bf16: 2^-9)
+                for pd in ("f16", "bf16"):
+                    tp.local.out_dtype = pd
+                    try:
+                        yb = tp(xs[0])
+                        torch.cuda.synchronize()
+                        err_b = float((yb[:1024].float() - ref).norm() / ref.norm()) if rank == 0 else None
+                        ms_b = timed(lambda i: tp(xs[i % 2]), steps)
+                        push[pd + "_partials"] = {"ms_per_block": ms_b, "tflops": 6.0 * M * H * I / (ms_b * 1e-3) / 1e12,
+                                                  "rel_error_vs_unsharded_block": err_b,
+                                                  "nvlink_bytes_sent_per_rank": (world - 1) * (M // world) * H * 2}
+                    finally:
+                        tp.local.out_dtype = "f32"
         except RuntimeError as e:
             push = {"unavailable": str(e)[:300]}
         tp.close()

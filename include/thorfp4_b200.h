@@ -188,14 +188,16 @@ int tfp4_swiglu_gemm(const void* packedA, const void* sblkA, float tsA, const vo
  * row-parallel, with the transfer inside the GEMM.
  * tfp4_gemm_push: tfp4_gemm whose epilogue stores this rank's partial product (M, N), 32 token rows at a time, into the
  *   staging buffer of the rank that owns those rows: dest[o] (host array of n_dest <= 8 device pointers) = where this
- *   rank's rows for owner o go, a row-major (rows_per_dest, N) matrix of out_dtype (1 bf16 or 2 f32) in owner o's memory,
+ *   rank's rows for owner o go, a row-major (rows_per_dest, N) matrix of out_dtype (0 f16, 1 bf16 or 2 f32) in owner o's memory,
  *   mapped into this process (tfp4_peer_open; dest[own rank] is local memory).  Owner o holds token rows
  *   [o * rows_per_dest, (o + 1) * rows_per_dest); rows_per_dest % 32 == 0.  The stores are TMA stores issued by the
  *   epilogue warps while the tensor cores work on the next tile, so the NVLink transfer overlaps the GEMM.  first_dest:
  *   the owner whose token tiles this rank computes first (pass own rank + 1): every rank then walks the owners in a
  *   different rotation and no owner's links take every rank's stores at once.
  * tfp4_sum_slots: out (rows, N) = sum over the n staged partials stage[s] (s ascending: the same order on every rank),
- *   in_dtype 0 f32 / 2 bf16, out_dtype 0 f16 / 1 bf16 / 2 f32.  Run it after every rank's push has completed (a barrier
+ *   in_dtype 0 f32 / 1 f16 / 2 bf16, out_dtype 0 f16 / 1 bf16 / 2 f32.  16-bit partials halve the NVLink bytes: f16 rounds
+ *   each partial at 2^-12 relative (an 8-rank sum stays within 1e-3 of the f32 exchange, but a partial beyond 65504
+ *   overflows), bf16 at 2^-9 (about 2e-3 after the sum).  Run it after every rank's push has completed (a barrier
  *   on the host or a collective in stream order between the two calls).
  * tfp4_peer_alloc / _open / _close / _free: a device buffer with a 64-byte CUDA IPC handle that the other processes of
  *   the node open to obtain a pointer valid on their device.

@@ -268,7 +268,7 @@ def test_act_quant_mx8_bias_reads_stay_inside_the_vector():
 
 # ------------------------------------------------------------------------------------------ push epilogue (one GPU)
 @gpu
-@pytest.mark.parametrize("od", ["f32", "bf16"])
+@pytest.mark.parametrize("od", ["f32", "bf16", "f16"])
 @pytest.mark.parametrize("M,N,K,owners", [(512, 384, 1024, 2), (1024, 1000, 512, 4), (768, 256, 256, 8), (300, 264, 512, 2),
                                           (8192, 2048, 1024, 8)])
 def test_gemm_push_fills_every_owners_staging_rows(od, M, N, K, owners):
@@ -326,6 +326,6 @@ def test_gemm_push_argument_checks():
     args = lambda n, rows, od: (buf.data_ptr(), buf.data_ptr(), ctypes.c_float(1.0), buf.data_ptr(), buf.data_ptr(), ctypes.c_float(1.0),
                                 dest, n, rows, 0, 64, 64, 64, od, _ext.stream())
     assert L.tfp4_gemm_push(*args(2, 48, 2)) == -7        # rows per owner not a multiple of 32
-    assert L.tfp4_gemm_push(*args(2, 16 * 2, 0)) == -7    # f16 partials are not offered
+    assert L.tfp4_gemm_push(*args(2, 16 * 2, 7)) == -7    # no such output type
     assert L.tfp4_gemm_push(*args(1, 32, 2)) == -7        # one owner of 32 rows does not cover 64 tokens
     assert L.tfp4_gemm_push(*args(9, 32, 2)) == -7        # more owners than the kernel's map table holds

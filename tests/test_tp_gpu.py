@@ -77,12 +77,19 @@ WORKER = textwrap.dedent('''
         yb = tpb(x).float()
         rows_b = tpb.owned_rows(M).cuda()
         good = good and yb.shape == (M // 2, H) and ((yb - y[rows_b]).norm() / y[rows_b].norm()).item() < 8e-3
+    # ... and f16 partials: 2^-12 per partial, so the sum stays within 1e-3 of the f32 exchange
+    tph = TensorParallelGatedMLP(H, I, device="cuda", reduce_dtype="f16", exchange="push")
+    tph.load_full_weights(wg.cuda(), wu.cuda(), wd.cuda())
+    for it in range(2):
+        yh = tph(x).float()
+        good = good and yh.shape == (M // 2, H) and ((yh - y[rows_b]).norm() / y[rows_b].norm()).item() < 1e-3
     torch.cuda.synchronize()
     okp = torch.tensor([int(good)], device="cuda")
     dist.all_reduce(okp, op=dist.ReduceOp.MIN)
     torch.cuda.synchronize()
     tpush.close()
     tpb.close()
+    tph.close()
     if rank == 0:
         print("PUSH_OK", int(okp.item()))
     dist.destroy_process_group()

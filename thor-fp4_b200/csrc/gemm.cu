@@ -1449,14 +1449,14 @@ int gemm_mx8_out(const void* packedA, const void* sblkA, const void* packedB, co
 // Row-parallel GEMM of a tensor-parallel block with the first half of the reduce-scatter in its epilogue: this rank's
 // partial product (M, N) is stored, 32-row block by 32-row block, into the staging buffers of the ranks that own the
 // token rows - dest[o] = where this rank's rows for owner o go, a row-major (rows_per_dest, N) matrix of out_dtype
-// (f32 or bf16) in owner o's memory (peer-mapped; dest[own rank] is local).  The stores are TMA stores issued by the
+// (f32, f16 or bf16) in owner o's memory (peer-mapped; dest[own rank] is local).  The stores are TMA stores issued by the
 // epilogue warps while the main loop runs; sum_slots on the owner completes the reduction.
 int gemm_push(const void* packedA, const void* sblkA, const void* packedB, const void* sblkB, float alpha, void* const* dest,
               int n_dest, int64_t rows_per_dest, int first_dest, int64_t M, int64_t N, int64_t K, int out_dtype,
               cudaStream_t stream) {
     if (n_dest < 1 || n_dest > PUSH_MAX_RANKS || rows_per_dest <= 0 || (rows_per_dest % 32) != 0 || (int64_t)n_dest * rows_per_dest < M ||
-        dest == nullptr || (out_dtype != OUT_F32 && out_dtype != OUT_BF16)) {
-        fprintf(stderr, "thor_fp4: gemm_push needs 1..%d destinations, rows per destination a multiple of 32 covering M, f32 or bf16 partials\n",
+        dest == nullptr || (out_dtype != OUT_F32 && out_dtype != OUT_BF16 && out_dtype != OUT_F16)) {
+        fprintf(stderr, "thor_fp4: gemm_push needs 1..%d destinations, rows per destination a multiple of 32 covering M, f32, f16 or bf16 partials\n",
                 PUSH_MAX_RANKS);
         return TFP4_ERR_BAD_ARG;
     }

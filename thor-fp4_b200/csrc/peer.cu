@@ -2,6 +2,7 @@
 // processes of the node can map (CUDA IPC), and the sum over the staged partial products that completes the
 // reduce-scatter begun in the GEMM's push epilogue (gemm_duo.cuh, mode 3).  The reference project is single-GPU
 // and has no counterpart of this file.
+#include <type_traits>
 #include <cstring>
 
 #include "common.cuh"
@@ -15,7 +16,7 @@ namespace {
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 sum_slots_kernel(const TI* __restrict__ stage, int n, int64_t elems, TO* __restrict__ out) {
-    constexpr int V = 16 / sizeof(TI);      // elements per 16-byte load: 4 (f32) or 8 (bf16)
+    constexpr int V = 16 / sizeof(TI);      // elements per 16-byte load: 4 (f32) or 8 (f16, bf16)
     griddep_wait();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x * V;
     for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * V; i < elems; i += stride) {
@@ -31,8 +32,14 @@ sum_slots_kernel(const TI* __restrict__ stage, int n, int64_t elems, TO* __restr
                 const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] += __uint_as_float(w[j] << 16);
-                    acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+                    if constexpr (std::is_same<TI, __half>::value) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                        acc[2 * j] += f.x;
+                        acc[2 * j + 1] += f.y;
+                    } else {
+                        acc[2 * j] += __uint_as_float(w[j] << 16);
+                        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+                    }
                 }
             }
         }
@@ -68,13 +75,13 @@ int launch_sum(const void* stage, int n, int64_t elems, void* out, cudaStream_t 
 
 }  // namespace
 
-// stage: n slots of (rows, N) partial products, in_dtype 0 f32 / 2 bf16 (the library's input-type codes);
+// stage: n slots of (rows, N) partial products, in_dtype 0 f32 / 1 f16 / 2 bf16 (the library's input-type codes);
 // out (rows, N) of out_dtype 0 f16 / 1 bf16 / 2 f32.
 int sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dtype, void* out, int out_dtype, cudaStream_t stream) {
     const int64_t elems = rows * N;
-    if (!stage || !out || n < 1 || elems <= 0 || (elems % 8) != 0 || (in_dtype != IN_F32 && in_dtype != IN_BF16) ||
+    if (!stage || !out || n < 1 || elems <= 0 || (elems % 8) != 0 || (in_dtype != IN_F32 && in_dtype != IN_BF16 && in_dtype != IN_F16) ||
         out_dtype < 0 || out_dtype > 2 || (reinterpret_cast<uintptr_t>(stage) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) {
-        fprintf(stderr, "thor_fp4: tfp4_sum_slots bad argument (f32 or bf16 slots, rows * N %% 8 == 0, 16-byte aligned buffers)\n");
+        fprintf(stderr, "thor_fp4: tfp4_sum_slots bad argument (f32, f16 or bf16 slots, rows * N %% 8 == 0, 16-byte aligned buffers)\n");
         return TFP4_ERR_BAD_ARG;
     }
 #define TFP4_SUM(TI)                                                                         \
@@ -83,7 +90,7 @@ int sum_slots(const void* stage, int n, int64_t rows, int64_t N, int in_dtype, v
         case OUT_F16: return launch_sum<TI, __half>(stage, n, elems, out, stream);           \
         default: return launch_sum<TI, __nv_bfloat16>(stage, n, elems, out, stream);         \
     }
-    if (in_dtype == IN_F32) { TFP4_SUM(float) } else { TFP4_SUM(__nv_bfloat16) }
+    if (in_dtype == IN_F32) { TFP4_SUM(float) } else if (in_dtype == IN_F16) { TFP4_SUM(__half) } else { TFP4_SUM(__nv_bfloat16) }
 #undef TFP4_SUM
 }
 

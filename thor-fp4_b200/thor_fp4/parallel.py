@@ -108,8 +108,9 @@ class TensorParallelGatedMLP(nn.Module):
     """y = sum_p( down_p( nvfp4( silu(x Wg_p^T) * (x Wu_p^T) ) ) ), the sum taken over the ranks.
 
     `local` computes the rank's partial product; by default it is an NVFP4GatedMLP on
-    this rank's GPU (partials in `reduce_dtype`, f32 unless told otherwise, because
-    rounding each partial to bf16 before the sum costs ~1.6e-3 relative error).
+    this rank's GPU (partials in `reduce_dtype`, f32 unless told otherwise: rounding each
+    partial to bf16 before the sum costs ~2e-3 relative error; "f16" costs ~3e-4 at half the
+    bytes of f32, as long as no partial exceeds the f16 range).
     `group` defaults to the world group.
 
     exchange:
@@ -229,8 +230,8 @@ class TensorParallelGatedMLP(nn.Module):
             raise ValueError(f"exchange='push' needs the token count ({M}) to divide by 32 x world size ({32 * self.world})")
         rows = M // self.world
         dt = _ext.OUT_TORCH[m.out_dtype]
-        if dt not in (torch.float32, torch.bfloat16):
-            raise ValueError("exchange='push' stages f32 or bf16 partials")
+        if dt not in (torch.float32, torch.float16, torch.bfloat16):
+            raise ValueError("exchange='push' stages f32, f16 or bf16 partials")
         st = self._push.get((M, dt))
         if st is None:
             stg = _PushStaging(self.group, self.world, self.rank, rows, H, dt, x.device)
@@ -260,8 +261,8 @@ class TensorParallelGatedMLP(nn.Module):
             raise ValueError(f"exchange='copy' needs every token chunk to divide by the world size ({self.world})")
         rows = M // self.world
         dt = _ext.OUT_TORCH[m.out_dtype]
-        if dt not in (torch.float32, torch.bfloat16):
-            raise ValueError("exchange='copy' stages f32 or bf16 partials")
+        if dt not in (torch.float32, torch.float16, torch.bfloat16):
+            raise ValueError("exchange='copy' stages f32, f16 or bf16 partials")
         st = self._push.get((M, dt, "copy"))
         if st is None:
             stg = _PushStaging(self.group, self.world, self.rank, rows, H, dt, x.device)
