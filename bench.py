@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--inter", type=int, default=28672, help="mlp workload: intermediate size")
-    ap.add_argument("--reduce-dtype", default="f32", choices=["f32", "bf16"],
+    ap.add_argument("--reduce-dtype", default="f32", choices=["f32", "f16", "bf16"],
                     help="mlp workload on several ranks: type of the partial outputs that are all-reduced")
     ap.add_argument("--exchange", default="all_reduce", choices=["all_reduce", "reduce_scatter", "push", "copy"],
                     help="mlp workload on several ranks: how the partial outputs are exchanged")
@@ -631,7 +631,7 @@ def measure_mlp_block(args, dev, rank, world, steps):
     ms_xchg = None
     scatter = push = copy = None
     if world > 1:
-        buf = torch.zeros(M, H, dtype=torch.float32 if reduce_dtype == "f32" else torch.bfloat16, device=dev)
+        buf = torch.zeros(M, H, dtype={"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[reduce_dtype], device=dev)
         ms_xchg = timed(lambda i: dist.all_reduce(buf), steps)          # the exchange alone (NCCL all-reduce of the partials)
         del buf
         # the same block with the partial outputs reduce-scattered by token rows (each rank keeps M/P summed rows)
