@@ -2,7 +2,7 @@
 """Benchmark of the NVFP4 linear-layer hot path (activation quantizer + tcgen05 GEMM).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload linear|quant|gemm|mlp] [--M ..] [--N ..] [--K ..]
+                    [--workload linear|mlp|sweep|gemv|gemmloop|pushloop] [--M ..] [--N ..] [--K ..]
 
 Default workload: thor_fp4.Linear(8192, 8192, bias=False, out_dtype='bf16') on a
 bf16 activation [8192, 8192] ~N(0,1) (M = N = K = 8192, the shape the headline
@@ -44,7 +44,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "mlp", "sweep", "gemv"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "mlp", "sweep", "gemv", "gemmloop", "pushloop"])
     ap.add_argument("--M", type=int, default=8192)
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--K", type=int, default=8192)
@@ -59,6 +59,7 @@ def parse():
     ap.add_argument("--graph", action="store_true", help="accepted for older command lines: the captured block is always timed")
     ap.add_argument("--no-graph", action="store_true",
                     help="do not capture the SwiGLU block (with its NCCL all-reduce, and the push form) in a CUDA graph")
+    ap.add_argument("--debug-mask", type=int, default=0, help="gemmloop workload: test-hook mask of the GEMM kernel (tfp4_set_debug)")
     ap.add_argument("--ablate", action="store_true",
                     help="time the GEMM with parts of the kernel switched off through the library's test hooks and print a table")
     ap.add_argument("--plain-launch", action="store_true",
@@ -750,6 +751,106 @@ def measure_mlp_block(args, dev, rank, world, steps):
     return res
 
 
+def run_gemmloop(args):
+    """--workload gemmloop: the NVFP4 GEMM alone on fixed operands (--M/--N/--K, bf16 out; --debug-mask switches parts
+    of the kernel off through the library's test hooks), timed two ways: bursts of 20 launches after a pause (the clock
+    the power cap allows a short run) and a seconds-long loop (the last 1000 of 4000 launches)."""
+    import thor_fp4
+    from thor_fp4 import _ext, ops
+    M, N, K = args.M, args.N, args.K
+    L = _ext.core()
+    torch.manual_seed(0)
+    a = thor_fp4.NVFP4Tensor.from_float(torch.randn(M, K, device="cuda"), 1.0)
+    b = thor_fp4.NVFP4Tensor.from_float(torch.randn(N, K, device="cuda") * 0.02, None)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    call = lambda: ops.gemm(a.packed, a.sblk, 1.0, b.packed, b.sblk, b.tensor_scale, out, M, N, K, "bf16")
+
+    def loop(n_warm, n):
+        for _ in range(n_warm):
+            call()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+    L.tfp4_set_debug(args.debug_mask)
+    try:
+        bursts = []
+        for _ in range(3):
+            time.sleep(0.5)
+            bursts.append(loop(3, 20))
+        sustained = loop(3000, 1000)
+    finally:
+        L.tfp4_set_debug(0)
+        L.tfp4_clear_status()
+    print(json.dumps({"workload": f"NVFP4 GEMM {M} x {N} x {K}, bf16 out, fixed operands", "debug_mask": args.debug_mask,
+                      "burst_of_20_us": [round(t, 2) for t in bursts], "sustained_us": round(sustained, 2),
+                      "burst_tflops": 2.0 * M * N * K / (min(bursts) * 1e-6) / 1e12}))
+
+
+def run_pushloop(args):
+    """--workload pushloop (under torchrun, one rank per GPU): the push GEMM alone - 16384 tokens x 8192 features, K = --K
+    per rank, partial rows stored into the owning ranks' staging buffers - for f32, f16 and bf16 partials, beside the same
+    GEMM with a local output; max over ranks, NVLink bytes leaving a rank per second."""
+    import torch.distributed as dist
+    import thor_fp4
+    from thor_fp4 import _ext, ops
+    from thor_fp4.parallel import _PushStaging
+    rank, local, world = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    L = _ext.device_lib()
+    M, H, I = 16384, 8192, (args.K if args.K != 8192 else 28672 // world)
+    torch.manual_seed(rank)
+    a = thor_fp4.NVFP4Tensor.from_float(torch.randn(M, I, device=dev), 1.0)
+    w = thor_fp4.NVFP4Tensor.from_float(torch.randn(H, I, device=dev) * 0.02, None)
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+    res = {"workload": f"push GEMM {M} x {H} x {I} per rank, {world} ranks"}
+    rows = M // world
+    for od, dt in (("f32", torch.float32), ("f16", torch.float16), ("bf16", torch.bfloat16)):
+        out = torch.empty(M, H, dtype=dt, device=dev)
+        ms_local = timed(lambda: ops.gemm(a.packed, a.sblk, 1.0, w.packed, w.sblk, w.tensor_scale, out, M, H, I, od))
+        stg = _PushStaging(None, world, rank, rows, H, dt, dev)
+
+        def push():
+            rc = L.tfp4_gemm_push(a.packed.data_ptr(), a.sblk.data_ptr(), 1.0, w.packed.data_ptr(), w.sblk.data_ptr(),
+                                  float(w.tensor_scale), stg.dest[0], world, rows, (rank + 1) % world, M, H, I,
+                                  _ext.OUT_DTYPE[od], _ext.stream())
+            assert rc == 0
+        ms_push = timed(push)
+        ys = torch.empty(rows, H, dtype=dt, device=dev)
+        ms_sum = timed(lambda: L.tfp4_sum_slots(stg.local_set[0], world, rows, H, _ext.IN_DTYPE[dt], ys.data_ptr(),
+                                                _ext.OUT_DTYPE[od], _ext.stream()))
+        sent = (world - 1) * rows * H * (4 if od == "f32" else 2)
+        res[od] = {"ms_local_output": ms_local, "ms_push": ms_push, "ms_sum_slots": ms_sum,
+                   "nvlink_gbs_out_per_rank": sent / (ms_push * 1e-3) / 1e9}
+        torch.cuda.synchronize()
+        dist.barrier()
+        stg.close()
+        del out, ys
+    if rank == 0:
+        print(json.dumps(res))
+    dist.destroy_process_group()
+
+
 def n_inputs(args):
     """Input buffers a run rotates over so that together they exceed the 126 MB L2 (> 256 MB of bf16 activations)."""
     return max(2, int(np.ceil(300e6 / (args.M * args.K * 2))))
@@ -1033,6 +1134,12 @@ def main():
         return
     if args.workload == "gemv":
         run_gemv(args)
+        return
+    if args.workload == "gemmloop":
+        run_gemmloop(args)
+        return
+    if args.workload == "pushloop":
+        run_pushloop(args)
         return
     if args.workload == "mlp":
         if args.M == 8192 and args.K == 8192 and args.N == 8192:
