@@ -1010,7 +1010,7 @@ int out_map(const CUtensorMap** map, void* out, int64_t M, int64_t N, int esize,
     if (it == g_out_maps.end()) {
         CUtensorMap m;
         int rc = encode_map(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, out, (uint64_t)(N * esize), (uint64_t)M, (uint64_t)(N * esize),
-                            esize == 2 ? 64 : 128, 32, esize == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+                            128, 32, CU_TENSOR_MAP_SWIZZLE_128B);   // one store = 32 rows x 128 bytes: 64 16-bit or 32 f32 columns
         if (rc) return rc;
         if (g_out_maps.size() > 4096) g_out_maps.clear();
         it = g_out_maps.emplace(key, m).first;

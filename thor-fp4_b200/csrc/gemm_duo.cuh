@@ -19,7 +19,7 @@
 //   warp 1      leader: MMA issuer.  peer: relays "my operands landed" to the leader's barrier
 //   warps 2-5,  epilogue, two warps per tensor-memory lane quarter (columns 0-127 and 128-255):
 //   11-14       tcgen05.ld 32 columns -> alpha, bias, cast -> swizzled shared memory -> one TMA store
-//               per warp and 32 x 32 block of the output; the accumulator is handed back as soon as a
+//               per warp and 32 rows x 128 bytes of the output (32 f32 or 64 16-bit columns); the accumulator is handed back as soon as a
 //               warp's last columns are in registers (fma + convert + st.shared of a 128 x 256 tile
 //               take one warp per quarter ~2200 cycles, which no MMA can overlap)
 //   warps 6-9   scale loaders: scale atoms of two K blocks at a time, shared memory ->
@@ -51,7 +51,7 @@ struct DuoCfg {
     static constexpr int SF_STAGE_BYTES = 3 * SF_PART;        // own tokens, feature rows 0-127, feature rows 128-255
     static constexpr int NSLOT = 5;                           // scale slots in tensor memory: one per operand stage
     static constexpr int SF_COL = 256;                        // behind the 256 accumulator columns
-    static constexpr int EPI_BUF = 32 * 128;                  // per epilogue warp: 2 x (32 rows x 64 bytes) or 1 x (32 x 128)
+    static constexpr int EPI_BUF = 32 * 128;                  // per epilogue warp: 32 rows x 128 bytes
     static constexpr int EPI_BYTES = 8 * EPI_BUF;             // eight epilogue warps
     static constexpr int BAR_BYTES = 512;
     static constexpr int SMEM_BYTES =
@@ -189,28 +189,6 @@ __device__ __forceinline__ void duo_put16(const float (&f)[32], uint32_t row_add
 #pragma unroll
     for (int c = 0; c < 4; ++c)
         st_shared_v4(row_addr + (uint32_t)(((chunk0 + c) ^ (row & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
-}
-// 32 columns as 16-bit values into a 32-row x 64-byte block: four 16-byte chunks per row, chunk index
-// XOR ((row >> 1) & 3) (the 64-byte swizzle the TMA store expects)
-__device__ __forceinline__ void duo_put16_64(const float (&f)[32], uint32_t buf, int row, bool bf16) {
-    uint32_t h[16];
-    if (bf16) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-            h[i] = *reinterpret_cast<uint32_t*>(&t);
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-            h[i] = *reinterpret_cast<uint32_t*>(&t);
-        }
-    }
-    const uint32_t row_addr = buf + (uint32_t)row * 64u;
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-        st_shared_v4(row_addr + (uint32_t)((c ^ ((row >> 1) & 3)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
 }
 __device__ __forceinline__ void duo_put32(const float (&f)[32], uint32_t row_addr, int row) {
 #pragma unroll
@@ -689,12 +667,11 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         // ------------------------------------------------------------ epilogue (warps 2..5 and 11..14, both CTAs)
         const int q = warp & 3;                              // tensor-memory lane quarter this warp may read
         const int half = warp >= 11 ? 1 : 0;                 // which 128 of the 256 accumulator columns
-        uint32_t tcount = 0, nstore = 0;
+        uint32_t tcount = 0;
         bool ok = true;
         const uint32_t tempty_leader = map_to_cta(smem_u32(tempty_bar), 0);
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 128);
         const bool out16 = p.out_dtype != OUT_F32, bf16 = p.out_dtype == OUT_BF16;
-        const int esize = out16 ? 2 : 4;
         const uint32_t my_buf = smem_u32(sEpi) + (uint32_t)(half * 4 + q) * C::EPI_BUF;
         if constexpr (EPI == 0 || EPI == 3) {
             for (int64_t tile = first; tile < total_tiles && ok; tile += stride, ++tcount) {
@@ -710,20 +687,14 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                 }
                 const int64_t row0 = mt * C::TILE_M + rank * 128 + q * 32;     // first of this warp's 32 token rows
                 const int64_t n0 = nt * C::TILE_N + half * 128;                // first of this warp's 128 feature columns
-                // One 32-column chunk: alpha, bias, cast, swizzled shared memory, TMA store.
+                // One 32-column chunk of an f32 output: alpha, bias, swizzled shared memory (32 rows x 128 bytes), TMA store.
                 auto emit = [&](const uint32_t (&v)[32], int c) {
                     const int64_t nn = n0 + c;
-                    // 16-bit outputs alternate between two 2 KB blocks; f32 outputs have one 4 KB block
-                    const uint32_t buf = my_buf + (out16 ? (nstore & 1u) * (C::EPI_BUF / 2) : 0u);
-                    if (lane == 0) {
-                        if (out16) bulk_wait_read_1();       // the store issued from this block two chunks ago has read it
-                        else bulk_wait_read_0();
-                    }
+                    if (lane == 0) bulk_wait_read_0();       // the store issued from this block one chunk ago has read it
                     __syncwarp();
                     float f[32];
                     duo_scale(v, f, nn, p.N, p.alpha, p.bias);
-                    if (out16) duo_put16_64(f, buf, lane, bf16);
-                    else duo_put32(f, buf + (uint32_t)lane * 128u, lane);
+                    duo_put32(f, my_buf + (uint32_t)lane * 128u, lane);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
@@ -732,20 +703,20 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                         if (row0 < p.M && nn < p.N && !(dbg & 1)) {
                             // push epilogue: the owner of these 32 token rows (push_rows is a multiple of 32: a block has one owner)
                             const int64_t o = (EPI == 3) ? row0 / p.push_rows : 0;
-                            tma_store_2d(duo_push_map<EPI>(tmO, o), (int)(nn * esize), (int)(row0 - o * p.push_rows), buf);
+                            tma_store_2d(duo_push_map<EPI>(tmO, o), (int)(nn * 4), (int)(row0 - o * p.push_rows), my_buf);
                         }
                         bulk_commit_group();
                     }
-                    ++nstore;
                 };
-                // Push epilogue, 16-bit outputs: two chunks per store, so that a row written into the owner's memory is 128
-                // bytes.  Over NVLink the width of the written rows sets the rate: 64-byte rows left a rank at 400 GB/s, 128-byte
-                // rows at 600 (f32 chunks are 128 bytes already; 256-byte rows from an un-swizzled staging block were no faster).
+                // 16-bit outputs: two chunks per store, so that a stored row is 128 bytes (32 rows x 128 bytes, 128-byte
+                // swizzle).  Over NVLink (push epilogue) the width of the written rows sets the rate: 64-byte rows left a rank
+                // at 400 GB/s, 128-byte rows at 600 (256-byte rows of f32 from an un-swizzled staging block were no faster);
+                // to local memory half as many stores took 1 % off the 8192^3 GEMM.
                 auto emit_pair = [&](const uint32_t (&v0)[32], const uint32_t (&v1)[32], int c) {
                     const int64_t nn = n0 + c;
                     float f0[32], f1[32];
-                    duo_scale(v0, f0, nn, p.N, p.alpha, nullptr);
-                    duo_scale(v1, f1, nn + 32, p.N, p.alpha, nullptr);
+                    duo_scale(v0, f0, nn, p.N, p.alpha, EPI == 0 ? p.bias : nullptr);
+                    duo_scale(v1, f1, nn + 32, p.N, p.alpha, EPI == 0 ? p.bias : nullptr);
                     const int64_t o = p.push_rows > 0 ? row0 / p.push_rows : 0;
                     if (lane == 0) bulk_wait_read_0();
                     __syncwarp();
@@ -759,7 +730,7 @@ gemm_duo_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
                         bulk_commit_group();
                     }
                 };
-                if (EPI == 3 && out16) {
+                if (out16) {
                     uint32_t va[32], vb[32];
                     tc_ld32(t_lane, va);
                     tc_ld32(t_lane + 32u, vb);
